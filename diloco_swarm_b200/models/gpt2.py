@@ -1,0 +1,268 @@
+"""GPT-2 in plain PyTorch: the numerical oracle and the CPU/gloo stage.
+
+Architecture as in the reference (src/model.py:13-152): learned positions,
+pre-LayerNorm blocks (eps 1e-5), fused QKV projection, causal attention with
+scale 1/sqrt(head_size), exact-erf GELU MLP of width 4d, final LayerNorm and
+a bias-free LM head; weights N(0, 0.02), residual output projections
+N(0, 0.02/sqrt(2*n_layer)), biases zero.
+
+Unlike the reference (src/train.py:376-377, every rank builds the whole model
+and throws most of it away) a stage builds only its own tensors.  Every tensor
+is drawn from its own generator seeded by (seed, global tensor name), so any
+S x R split starts from exactly the single-process model.
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+from dataclasses import dataclass
+from typing import Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPT2Config:
+    block_size: int = 1024
+    vocab_size: int = 50304
+    n_layer: int = 12
+    n_head: int = 12
+    n_embd: int = 768
+    dropout: float = 0.0
+    bias: bool = True
+    parameter_sharing: bool = False
+
+
+def split_layers(n_layer: int, num_stages: int, mode: str = "even",
+                 n_embd: int = 768, vocab_size: int = 50304) -> List[List[int]]:
+    """Block indices per stage.
+
+    "even": n_layer // S each, remainder to the first stages (src/model.py:195-198).
+    "balanced": gives the last stage fewer blocks to make room for the LM head
+    (its 2*d*V flops per token equal V/(12 d) blocks) and the first for the embedding.
+    "a,b,c": explicit counts.
+    """
+    S = num_stages
+    if mode == "even":
+        counts = [n_layer // S + (1 if i < n_layer % S else 0) for i in range(S)]
+    elif mode == "balanced":
+        head_blocks = vocab_size / (12.0 * n_embd)
+        per = (n_layer + head_blocks) / S
+        counts = [0] * S
+        left = n_layer
+        for s in range(S - 1, -1, -1):
+            want = per - (head_blocks if s == S - 1 else 0.0)
+            c = int(round(want)) if s > 0 else left
+            c = max(1 if left - (s) >= 1 else 0, min(c, left - s))
+            counts[s] = c
+            left -= c
+        if sum(counts) != n_layer:
+            counts[0] += n_layer - sum(counts)
+    else:
+        counts = [int(x) for x in mode.split(",")]
+        if len(counts) != S or sum(counts) != n_layer:
+            raise ValueError(f"layer_split {mode!r} does not cover {n_layer} layers over {S} stages")
+    out, start = [], 0
+    for c in counts:
+        out.append(list(range(start, start + c)))
+        start += c
+    return out
+
+
+def tensor_seed(seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
+
+
+def init_tensor(name: str, shape: Sequence[int], seed: int, n_layer: int) -> torch.Tensor:
+    """Deterministic fp32 initial value of the tensor with the given GLOBAL name."""
+    leaf = name.rsplit(".", 1)[-1]
+    if leaf == "bias":
+        return torch.zeros(*shape)
+    if ".ln_" in name or name.startswith("transformer.ln_f"):
+        return torch.ones(*shape)
+    std = 0.02 / math.sqrt(2 * n_layer) if name.endswith("c_proj.weight") else 0.02
+    g = torch.Generator(device="cpu")
+    g.manual_seed(tensor_seed(seed, name))
+    return torch.empty(*shape).normal_(0.0, std, generator=g)
+
+
+def block_param_shapes(d: int, bias: bool = True) -> List[Tuple[str, Tuple[int, ...]]]:
+    names = [("ln_1.weight", (d,)), ("ln_1.bias", (d,)),
+             ("attn.c_attn.weight", (3 * d, d)), ("attn.c_attn.bias", (3 * d,)),
+             ("attn.c_proj.weight", (d, d)), ("attn.c_proj.bias", (d,)),
+             ("ln_2.weight", (d,)), ("ln_2.bias", (d,)),
+             ("mlp.c_fc.weight", (4 * d, d)), ("mlp.c_fc.bias", (4 * d,)),
+             ("mlp.c_proj.weight", (d, 4 * d)), ("mlp.c_proj.bias", (d,))]
+    return [(n, s) for n, s in names if bias or not n.endswith(".bias")]
+
+
+def stage_param_specs(cfg: GPT2Config, layers: Sequence[int], first: bool, last: bool
+                      ) -> List[Tuple[str, str, Tuple[int, ...]]]:
+    """(local state-dict key, global name, shape) of a stage, in the reference's
+    parameter order.  Local keys number the blocks from 0 within the stage, as
+    the reference's ``ShardedGPT2.state_dict()`` does (src/model.py:187)."""
+    d = cfg.n_embd
+    specs: List[Tuple[str, str, Tuple[int, ...]]] = []
+    if first:
+        specs.append(("transformer.wte.weight", "transformer.wte.weight", (cfg.vocab_size, d)))
+        specs.append(("transformer.wpe.weight", "transformer.wpe.weight", (cfg.block_size, d)))
+    for li, gi in enumerate(layers):
+        for n, shp in block_param_shapes(d, cfg.bias):
+            specs.append((f"transformer.h.{li}.{n}", f"transformer.h.{gi}.{n}", shp))
+    if last:
+        specs.append(("transformer.ln_f.weight", "transformer.ln_f.weight", (d,)))
+        if cfg.bias:
+            specs.append(("transformer.ln_f.bias", "transformer.ln_f.bias", (d,)))
+        tied = cfg.parameter_sharing and first
+        if not tied:
+            # untied, or tied but on another rank: the head has its own tensor.
+            # With tying requested and S > 1 both copies start equal (same
+            # global name) and then drift, as in the reference.
+            gname = "transformer.wte.weight" if cfg.parameter_sharing else "lm_head.weight"
+            specs.append(("lm_head.weight", gname, (cfg.vocab_size, d)))
+    return specs
+
+
+class _LayerNorm(nn.Module):
+    def __init__(self, d: int, bias: bool):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d))
+        self.bias = nn.Parameter(torch.zeros(d)) if bias else None
+
+    def forward(self, x):
+        return F.layer_norm(x, self.weight.shape, self.weight, self.bias, 1e-5)
+
+
+class _Attention(nn.Module):
+    def __init__(self, d: int, n_head: int, bias: bool):
+        super().__init__()
+        self.n_head = n_head
+        self.c_attn = nn.Linear(d, 3 * d, bias=bias)
+        self.c_proj = nn.Linear(d, d, bias=bias)
+
+    def forward(self, x):
+        B, T, C = x.shape
+        hs = C // self.n_head
+        q, k, v = (t.view(B, T, self.n_head, hs).transpose(1, 2) for t in self.c_attn(x).split(C, dim=2))
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.c_proj(y.transpose(1, 2).reshape(B, T, C))
+
+
+class _MLP(nn.Module):
+    def __init__(self, d: int, bias: bool):
+        super().__init__()
+        self.c_fc = nn.Linear(d, 4 * d, bias=bias)
+        self.c_proj = nn.Linear(4 * d, d, bias=bias)
+
+    def forward(self, x):
+        return self.c_proj(F.gelu(self.c_fc(x)))
+
+
+class _Block(nn.Module):
+    def __init__(self, d: int, n_head: int, bias: bool):
+        super().__init__()
+        self.ln_1 = _LayerNorm(d, bias)
+        self.attn = _Attention(d, n_head, bias)
+        self.ln_2 = _LayerNorm(d, bias)
+        self.mlp = _MLP(d, bias)
+
+    def forward(self, x):
+        x = x + self.attn(self.ln_1(x))
+        return x + self.mlp(self.ln_2(x))
+
+
+class _Transformer(nn.Module):
+    pass
+
+
+class TorchStage(nn.Module):
+    """One pipeline stage on library ops with autograd (reference: ShardedGPT2,
+    src/model.py:177-209).  With ``num_stages == 1`` it is the whole model."""
+
+    def __init__(self, cfg: GPT2Config, stage: int = 0, num_stages: int = 1, seed: int = 42,
+                 layer_split: str = "even"):
+        super().__init__()
+        self.config = cfg
+        self.stage, self.num_stages = stage, num_stages
+        self.is_first, self.is_last = stage == 0, stage == num_stages - 1
+        self.layers = split_layers(cfg.n_layer, num_stages, layer_split, cfg.n_embd, cfg.vocab_size)[stage]
+        d = cfg.n_embd
+        t = _Transformer()
+        if self.is_first:
+            t.wte = nn.Embedding(cfg.vocab_size, d)
+            t.wpe = nn.Embedding(cfg.block_size, d)
+        t.h = nn.ModuleList([_Block(d, cfg.n_head, cfg.bias) for _ in self.layers])
+        if self.is_last:
+            t.ln_f = _LayerNorm(d, cfg.bias)
+        self.transformer = t
+        if self.is_last:
+            self.lm_head = nn.Linear(d, cfg.vocab_size, bias=False)
+            if cfg.parameter_sharing and self.is_first:
+                self.lm_head.weight = t.wte.weight
+        self.specs = stage_param_specs(cfg, self.layers, self.is_first, self.is_last)
+        sd = dict(self.named_parameters())
+        with torch.no_grad():
+            for key, gname, shape in self.specs:
+                sd[key].copy_(init_tensor(gname, shape, seed, cfg.n_layer))
+
+    # -- pieces (reference: encode_tokens / forward_layers / forward_logits) --
+    def encode_tokens(self, input_ids: torch.Tensor) -> torch.Tensor:
+        pos = torch.arange(input_ids.size(1), device=input_ids.device)
+        return self.transformer.wte(input_ids) + self.transformer.wpe(pos)
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None,
+                hidden_states: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = self.encode_tokens(input_ids) if self.is_first else hidden_states
+        for blk in self.transformer.h:
+            x = blk(x)
+        if self.is_last:
+            x = self.lm_head(self.transformer.ln_f(x))
+        return x
+
+    def num_parameters(self, exclude_positional: bool = True) -> int:
+        n = sum(p.numel() for p in self.parameters())
+        if exclude_positional and self.is_first:
+            n -= self.transformer.wpe.weight.numel()
+        return n
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,
+                 top_k: Optional[int] = None, eos_token_id: Optional[int] = None,
+                 generator: Optional[torch.Generator] = None) -> torch.Tensor:
+        """Single-process sampler (reference: GPT2.generate, src/model.py:160-175)."""
+        assert self.num_stages == 1
+        for _ in range(max_new_tokens):
+            ctx = input_ids[:, -self.config.block_size:]
+            logits = self(input_ids=ctx)[:, -1, :].float()
+            nxt = sample_next(logits, temperature, top_k, generator)
+            input_ids = torch.cat([input_ids, nxt], dim=1)
+            if eos_token_id is not None and bool((nxt == eos_token_id).all()):
+                break
+        return input_ids
+
+
+def sample_next(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None,
+                generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """Temperature / top-k sampling of one token per row.  The reference's
+    distributed sampler ignores both knobs (src/train.py:64-65); here they apply."""
+    if temperature <= 0:
+        return logits.argmax(dim=-1, keepdim=True)
+    logits = logits / temperature
+    if top_k is not None and top_k > 0:
+        kth = torch.topk(logits, min(top_k, logits.size(-1))).values[:, -1:]
+        logits = logits.masked_fill(logits < kth, float("-inf"))
+    probs = F.softmax(logits, dim=-1)
+    return torch.multinomial(probs, num_samples=1, generator=generator)
+
+
+def num_parameters(cfg: GPT2Config, exclude_positional: bool = True) -> int:
+    d = cfg.n_embd
+    n = cfg.n_layer * sum(math.prod(s) for _, s in block_param_shapes(d, cfg.bias))
+    n += cfg.vocab_size * d * (1 if cfg.parameter_sharing else 2)
+    n += d * (2 if cfg.bias else 1)
+    if not exclude_positional:
+        n += cfg.block_size * d
+    return n

@@ -1,0 +1,55 @@
+"""Learning-rate schedule and the library-op optimiser scheme (inner AdamW,
+DiLoCo outer SGD-Nesterov) used by the autograd stage.
+
+Reference: get_optimizer / get_scheduler (src/utils.py:59-85) and the DiLoCo
+helpers (src/utils.py:195-226).  The sm_100a stage implements the same maths
+in fused kernels (ops/optim.py); this file is also their oracle.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def lr_factor(step_index: int, sched, num_steps: int) -> float:
+    """Multiplier of the base learning rate for the ``step_index``-th optimiser
+    step (0-based), i.e. what ``LambdaLR.get_last_lr()`` returns before that
+    step in the reference (src/train.py:256).  Linear warm-up from 0, then
+    constant (src/utils.py:78-85) or the cosine variant (src/utils.py:67-76)."""
+    if not sched.enable:
+        return 1.0
+    w = sched.num_warmup_steps
+    if step_index < w:
+        return step_index / max(1, w)
+    if sched.type == "constant":
+        return 1.0
+    progress = (step_index - w) / max(1, num_steps - w)
+    progress = min(1.0, progress)
+    cos = 0.5 * (1.0 + math.cos(math.pi * sched.num_cycles * 2.0 * progress))
+    return sched.min_lr_factor + (1.0 - sched.min_lr_factor) * cos
+
+
+def make_inner_optimizer(params: Iterable[torch.nn.Parameter], cfg) -> torch.optim.Optimizer:
+    """One parameter group: weight decay applies to every tensor, biases,
+    LayerNorm and embeddings included, as in the reference (src/utils.py:61)."""
+    if cfg.type == "AdamW":
+        return torch.optim.AdamW(params, lr=cfg.lr, weight_decay=cfg.weight_decay,
+                                 betas=tuple(cfg.betas), eps=cfg.eps)
+    if cfg.type == "SGD":
+        return torch.optim.SGD(params, lr=cfg.lr, momentum=cfg.momentum, nesterov=cfg.nesterov)
+    raise ValueError(f"Invalid optimizer type: {cfg.type}")
+
+
+def nesterov_reference(theta_g: torch.Tensor, delta: torch.Tensor, buf: Optional[torch.Tensor],
+                       lr: float, momentum: float, nesterov: bool = True):
+    """torch.optim.SGD's update written out: buf <- mu*buf + g (buf = g on the
+    first step), theta <- theta - lr*(g + mu*buf) with Nesterov, else
+    theta <- theta - lr*buf.  Returns (theta, buf)."""
+    if momentum == 0:
+        return theta_g - lr * delta, buf
+    buf = delta.clone() if buf is None else momentum * buf + delta
+    upd = delta + momentum * buf if nesterov else buf
+    return theta_g - lr * upd, buf

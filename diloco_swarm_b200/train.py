@@ -1,0 +1,358 @@
+"""DiLoCo-SWARM training entry point.
+
+    torchrun --nproc_per_node 8 -m diloco_swarm_b200.train --swarm.num_stages 2 \
+        --model @configs/model/gpt2-small.toml --data @configs/data/synthetic-zipf.toml \
+        --train.inner_optimizer @configs/optimizer/adamw.toml \
+        --train.outer_optimizer @configs/optimizer/none.toml
+
+Same flags and run phases as the reference's ``src/train.py`` (sample and
+evaluate before training, train, evaluate/sample every n steps, final test and
+sample; src/train.py:283-349).  What differs is how a step runs: a precomputed
+plan instead of a polling event loop, device-side transfers instead of host
+staging, fused kernels for the optimiser and the two stage-wide
+synchronisations.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .config import Config, config_from_argv
+from .models.gpt2 import GPT2Config, sample_next
+from .optim import lr_factor
+from .parallel import schedule
+from .parallel.comm import InferenceComm, PipelineComm, StepTimeout, sync_outputs
+from .parallel.schedule import BWD, FWD, FWD_BWD
+from .utils import data as D
+from .utils.ckpt import Checkpoint
+from .utils.logger import Level, Logger
+from .utils.metrics import Outputs, eval_metrics, train_metrics
+from .utils.misc import format_float, format_int, get_device, seed_everything
+from .world import World
+
+
+def make_engine(config: Config, world: World, device: torch.device):
+    mc = config.model
+    gcfg = GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer,
+                      n_head=mc.n_head, n_embd=mc.n_embd, dropout=mc.dropout, bias=mc.bias,
+                      parameter_sharing=mc.parameter_sharing)
+    kind = config.engine
+    if kind == "auto":
+        kind = "b200" if device.type == "cuda" else "torch"
+    if kind == "b200":
+        from .models.engine_b200 import B200Engine
+        return B200Engine(gcfg, world, config, device)
+    from .models.engine_torch import TorchEngine
+    return TorchEngine(gcfg, world, config, device)
+
+
+class Trainer:
+    """Owns the world, the stage engine, the pipeline transport and the step logic."""
+
+    def __init__(self, config: Config, world: Optional[World] = None, logger: Optional[Logger] = None):
+        self.config = config
+        dev_type = (config.device or ("cuda" if torch.cuda.is_available() else "cpu")).split(":")[0]
+        if dev_type == "cuda":
+            os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+        self.world = world or World(config.swarm.num_stages, device_type=dev_type,
+                                    timeout_s=max(60.0, 10 * config.train.step_timeout))
+        w = self.world
+        self.device = get_device(config.device, w.local_rank)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        self.logger = logger or Logger(w, config.logging)
+        seed_everything(config.train.seed)
+        torch.set_float32_matmul_precision(config.amp.precision)
+        self.engine = make_engine(config, w, self.device)
+        tc = config.train
+        self.seq = config.data.seq_length
+        self.mbs = tc.micro_batch_size
+        self.num_micro = max(1, tc.batch_size // tc.micro_batch_size)
+        # reference: num_micro_steps // |last stage|, at least 1 (src/train.py:168)
+        self.micro_per_device = max(1, self.num_micro // len(w.last_stage_ranks))
+        self.loss_scale = 1.0 / self.micro_per_device
+        self.routing_seed = config.swarm.routing_seed if config.swarm.routing_seed is not None else tc.seed
+        self.comm = PipelineComm(w, (self.mbs, self.seq, config.model.n_embd), self.engine.act_dtype,
+                                 self.device, prefetch=2)
+        self.comm.warmup()
+        self.alive: Optional[List[bool]] = None
+        self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
+        self.num_train_steps = 0
+        self.ckpt = Checkpoint(self.logger.checkpoint_dir)
+        self.ckpt.setup(w)
+        self.last_step_device_ms: Optional[float] = None
+
+    # ------------------------------------------------------------------
+    def _plan(self, step: int, phase: int, forward_only: bool):
+        w = self.world
+        # phase separates the routing streams of train / eval / test steps
+        path = schedule.route(self.routing_seed + 7919 * phase, step, w.num_stages, w.world_size,
+                              self.num_micro, self.alive)
+        cap = self.config.train.max_micro_batches
+        return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
+
+    def _stage_batch(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Move what this stage needs of the global batch to the device."""
+        eng, out = self.engine, {}
+        if eng.is_first:
+            out["input_ids"] = batch["input_ids"].to(self.device, non_blocking=True)
+        if eng.is_last:
+            out["target_ids"] = batch["target_ids"].to(self.device, non_blocking=True)
+            out["attention_mask"] = batch["attention_mask"].to(self.device, non_blocking=True)
+        return out
+
+    # ------------------------------------------------------------------
+    def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Optional[Outputs]]:
+        cfg, w, eng, comm = self.config, self.world, self.engine, self.comm
+        start = time.time()
+        eng.train()
+        eng.zero_grad()
+        _, ops = self._plan(step, 0, forward_only=False)
+        dev = self._stage_batch(batch)
+        tokens_per_mb = self.mbs * self.seq
+        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        n_local = 0
+        comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
+        try:
+            for i, op in enumerate(ops):
+                rows = D.micro_batch_rows(op.mb, self.mbs)
+                if op.kind == BWD:
+                    dy = comm.recv(i)
+                    dx = eng.backward(op.mb, dy)
+                    if op.prev >= 0:
+                        comm.send_backward(dx, op.prev)
+                    continue
+                n_local += 1
+                ids = dev["input_ids"][rows] if eng.is_first else None
+                hidden = comm.recv(i) if op.prev >= 0 else None
+                if op.kind == FWD:
+                    y = eng.forward(op.mb, ids, hidden)
+                    comm.send_forward(y, op.next)
+                else:
+                    loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
+                                                    dev["attention_mask"][rows], self.loss_scale)
+                    loss_acc += loss
+                    if op.prev >= 0:
+                        comm.send_backward(dx, op.prev)
+            comm.end_step()
+        except StepTimeout:
+            self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
+            comm.abandon_step()
+
+        H = cfg.swarm.sync_every_n_steps
+        do_sync = (H > 0 and step % H == 0) or step == self.num_train_steps
+        if do_sync and not eng.has_outer:
+            eng.sync_gradients()
+        lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
+        norm = eng.optimizer_step(lr, cfg.train.max_norm)
+        self.opt_steps += 1
+        if do_sync and eng.has_outer:
+            eng.outer_step()
+        loss_val = float(loss_acc.item())      # the step's one device-to-host read
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        eng.check_status()
+        step_time = time.time() - start
+        local = Outputs(step=step, lr=lr, loss=loss_val, tokens=n_local * tokens_per_mb, norm=float(norm),
+                        time=step_time, micro_step_time=step_time / self.micro_per_device,
+                        num_micro_batches=n_local)
+        stage = sync_outputs(w, local, self.device) if do_sync else None
+        return local, stage
+
+    # ------------------------------------------------------------------
+    @torch.no_grad()
+    def eval_step(self, step: int, eval_type: str, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Outputs]:
+        w, eng, comm = self.world, self.engine, self.comm
+        start = time.time()
+        eng.eval()
+        _, ops = self._plan(step, 1 if eval_type == "eval" else 2, forward_only=True)
+        dev = self._stage_batch(batch)
+        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        n_local = 0
+        comm.begin_step(ops)
+        for i, op in enumerate(ops):
+            rows = D.micro_batch_rows(op.mb, self.mbs)
+            n_local += 1
+            ids = dev["input_ids"][rows] if eng.is_first else None
+            hidden = comm.recv(i) if op.prev >= 0 else None
+            if eng.is_last:
+                loss_acc += eng.forward_loss(ids, hidden, dev["target_ids"][rows],
+                                             dev["attention_mask"][rows], self.loss_scale)
+            else:
+                comm.send_forward(eng.forward(op.mb, ids, hidden, keep=False), op.next)
+        comm.end_step()
+        loss_val = float(loss_acc.item())
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        local = Outputs(step=step, time=time.time() - start, loss=loss_val,
+                        tokens=n_local * self.mbs * self.seq, num_micro_batches=n_local)
+        return local, sync_outputs(w, local, self.device)
+
+    def eval_loop(self, eval_type: str, loader: D.BatchLoader, metrics) -> Dict[str, float]:
+        metrics.reset()
+        limit = self.config.eval.max_steps
+        for step, batch in enumerate(loader, start=1):
+            if 0 < limit < step:
+                break
+            _, stage = self.eval_step(step, eval_type, batch)
+            if self.world.is_master:
+                metrics.update(stage)
+        return metrics.compute()
+
+    # ------------------------------------------------------------------
+    @torch.no_grad()
+    def sample_loop(self, tokenizer) -> List[str]:
+        """Autoregressive sampling through the stage leaders with whole-sequence
+        recompute per token, as in the reference (src/train.py:46-74).  Hidden
+        states travel leader to leader; the new ids and the stop flag come back
+        in one broadcast from the last leader, so every rank ends with the final
+        ids.  Temperature and top-k are applied (the reference ignores them)."""
+        sc, w, eng = self.config.sample, self.world, self.engine
+        eng.eval()
+        prompt_len = len(tokenizer.encode(sc.prompt))
+        total = min(prompt_len + sc.max_new_tokens, self.config.model.block_size)
+        ids = D.tokenize(sc.prompt, tokenizer, max_length=total)["input_ids"].repeat(sc.num_samples, 1)
+        # last column carries the stop flag
+        state = torch.cat([ids, torch.zeros(sc.num_samples, 1, dtype=torch.long)], dim=1).to(self.device)
+        ring = InferenceComm(w, self.device)
+        d = self.config.model.n_embd
+        gen = torch.Generator(device=self.device).manual_seed(self.config.train.seed + 17)
+        multi = w.world_size > 1
+        for pos in range(prompt_len, total):
+            if w.is_leader:
+                hidden = None
+                if not w.is_first_stage:
+                    hidden = ring.recv_hidden((sc.num_samples, total, d), torch.float32)
+                out = eng.forward_infer(state[:, :total] if w.is_first_stage else None, hidden)
+                if w.is_last_stage:
+                    nxt = sample_next(out[:, pos - 1, :].float(), sc.temperature, sc.top_k, gen)
+                    state[:, pos] = nxt.squeeze(1)
+                    if bool((nxt == tokenizer.eos_token_id).all()):
+                        state[:, total] = 1
+                else:
+                    ring.send_hidden(out)
+            if multi:
+                dist.broadcast(state, src=w.last_stage_leader)
+            if bool(state[0, total].item()):
+                break
+        return [tokenizer.decode(row, skip_special_tokens=True) for row in state[:, :total].cpu()]
+
+    # ------------------------------------------------------------------
+    def save_checkpoint(self, step: int) -> None:
+        eng = self.engine
+        self.ckpt.save(step, eng)
+        self.ckpt.save_extra(step, "optim", {"engine": eng.optim_state(), "opt_steps": self.opt_steps})
+        outer = eng.outer_state()
+        if outer is not None:
+            self.ckpt.save_extra(step, "outer", outer)
+        if self.world.is_master:
+            self.ckpt.save_meta(step, {
+                "step": step, "opt_steps": self.opt_steps, "world_size": self.world.world_size,
+                "num_stages": self.world.num_stages, "routing_seed": self.routing_seed,
+                "engine": eng.name, "config": self.config.model_dump()})
+        self.world.barrier()
+
+    def load_checkpoint(self, step: Optional[int] = None) -> int:
+        step = step if step is not None else self.ckpt.get_latest_step()
+        if step is None:
+            return 0
+        self.engine.load_state_dict(self.ckpt.load(step))
+        opt = self.ckpt.load_extra(step, "optim")
+        if opt is not None:
+            self.engine.load_optim_state(opt["engine"])
+            self.opt_steps = int(opt["opt_steps"])
+        self.engine.load_outer_state(self.ckpt.load_extra(step, "outer"))
+        self.world.barrier()
+        return step
+
+    # ------------------------------------------------------------------
+    def train_loop(self, train_loader: D.BatchLoader, eval_loader: Optional[D.BatchLoader], tokenizer,
+                   num_train_steps: int) -> Dict[str, float]:
+        cfg, w, log = self.config, self.world, self.logger
+        self.num_train_steps = num_train_steps
+        local_m, global_m, eval_m = train_metrics("train/local"), train_metrics("train/global"), eval_metrics("eval")
+        start_step = 0
+        if cfg.ckpt.resume:
+            start_step = self.load_checkpoint(cfg.ckpt.step)
+            log.log_message(f"Resumed from step {start_step}", master=True, level=Level.INFO)
+        if cfg.sample.enable and start_step == 0:
+            log.log_samples(self.sample_loop(tokenizer), step=0)
+        if cfg.eval.enable and start_step == 0:
+            log.log_metrics(self.eval_loop("eval", eval_loader, eval_m), step=0, master=True)
+        last: Dict[str, float] = {}
+        it = iter(train_loader)
+        for _ in range(start_step):      # sequential loader: skip what was consumed
+            next(it)
+        step = start_step
+        for step in range(start_step + 1, num_train_steps + 1):
+            batch = next(it)
+            local, stage = self.train_step(step, batch)
+            local_m.update(local)
+            log.log_metrics(local_m.compute(), step=step, master=False)
+            if w.is_master and stage is not None:
+                global_m.update(stage)
+                last = global_m.compute()
+                log.log_metrics(last, step=step, master=True)
+                g = last
+                log.log_message(
+                    f"[TRAIN] Step: {step} - Time: {g['train/global/time/current']:.2f}s - "
+                    f"Loss: {g['train/global/loss/current']:.4f} - Norm: {g['train/global/norm/current'] or 0:.4f} - "
+                    f"Perplexity: {g['train/global/perplexity/current']:.1f} - "
+                    f"Throughput: {g['train/global/throughput/current']:.1f}", master=True, level=Level.INFO)
+            if cfg.sample.enable and cfg.sample.every_n_steps > 0 and step % cfg.sample.every_n_steps == 0:
+                log.log_samples(self.sample_loop(tokenizer), step=step)
+            if cfg.eval.enable and cfg.eval.every_n_steps > 0 and step % cfg.eval.every_n_steps == 0:
+                log.log_metrics(self.eval_loop("eval", eval_loader, eval_m), step=step, master=True)
+            if cfg.ckpt.enable and cfg.ckpt.every_n_steps > 0 and step % cfg.ckpt.every_n_steps == 0:
+                self.save_checkpoint(step)
+        if cfg.eval.enable:
+            out = self.eval_loop("test", eval_loader, eval_m)
+            log.log_metrics(out, step=step, master=True)
+            if w.is_master:
+                log.log_message(f"[TEST] Avg. Loss: {out['eval/loss/average']:.4f}, "
+                                f"Avg. Perplexity: {out['eval/perplexity/average']:.1f}", master=True, level=Level.INFO)
+        if cfg.sample.enable:
+            log.log_samples(self.sample_loop(tokenizer), step=step)
+        if cfg.ckpt.enable:
+            self.save_checkpoint(step)
+        return last
+
+
+def main(config: Config) -> Dict[str, float]:
+    trainer = Trainer(config)
+    w, log = trainer.world, trainer.logger
+    log.log_message(f"Starting process {w.local_rank}", master=False, level=Level.INFO)
+    log.log_config(config)
+    log.log_world(w)
+    log.log_message(f"Using device {trainer.device}, engine {trainer.engine.name}", master=False, level=Level.INFO)
+    log.log_message(f"Initialized stage model ({format_int(trainer.engine.num_parameters(), 2)} parameters)",
+                    master=False, level=Level.INFO)
+    tokenizer = D.get_tokenizer()
+    log.log_message(f"Loaded tokenizer ({format_int(len(tokenizer), 0)} vocab size)", master=True, level=Level.INFO)
+    data = D.get_dataset(config.data, tokenizer, seed=config.train.seed)
+    train_data, val_data = data.train_test_split(config.eval.eval_size, seed=config.train.seed)
+    log.log_message(f"Split dataset {config.data.path} into {format_int(len(train_data))} train, "
+                    f"{format_int(len(val_data))} validation examples", master=True, level=Level.INFO)
+    bs = config.train.batch_size
+    train_loader = D.BatchLoader(train_data, bs, config.data.pin_memory)
+    eval_loader = D.BatchLoader(val_data, bs, config.data.pin_memory)
+    num_steps = D.get_num_steps(config.train.max_steps, config.train.max_epochs, len(train_data), bs)
+    setup = D.get_train_setup(num_steps, bs, config.data.seq_length, config.train.micro_batch_size, len(train_data))
+    log.log_message("Train setup:\t" + "\t".join(
+        f"{k.replace('_', ' ').title()}: {format_int(v, 1) if isinstance(v, int) else format_float(v)}"
+        for k, v in setup.items()), master=True, level=Level.INFO)
+    out = trainer.train_loop(train_loader, eval_loader, tokenizer, num_steps)
+    w.barrier()
+    log.close()
+    w.destroy()
+    return out
+
+
+if __name__ == "__main__":
+    os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
+    main(config_from_argv())

@@ -1,0 +1,214 @@
+"""Tokenizer, datasets, batching and the microbatch partition.
+
+The reference loads the GPT-2 tokenizer and its datasets from the Hugging Face
+hub (src/utils.py:54-57,88-100).  Both are used when reachable; offline the
+package falls back to a byte-level tokenizer and to built-in generators:
+
+* ``mikasenghaas/memorize`` / ``memorize``: one sentence repeated 1000 times
+  (the reference's memorisation set, tests/test_memorize.py:80);
+* ``synthetic:zipf``: token ids iid Zipf(s) over [0, vocab_limit) from a seed.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+MEMORIZE_SENTENCE = "I am a large language model and I can memorize this sentence."
+
+
+class ByteTokenizer:
+    """Byte-level stand-in with the GPT-2 special-token convention (eos = pad = 50256)."""
+    eos_token_id = 50256
+    pad_token_id = 50256
+
+    def __len__(self) -> int:
+        return 50257
+
+    def encode(self, text: str) -> List[int]:
+        return list(text.encode("utf-8"))
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        out = bytearray()
+        for i in (ids.tolist() if hasattr(ids, "tolist") else ids):
+            if i < 256:
+                out.append(i)
+            elif not skip_special_tokens:
+                out.extend(b"<|endoftext|>")
+        return out.decode("utf-8", errors="replace")
+
+
+class HFTokenizer:
+    def __init__(self, tok):
+        self.tok = tok
+        self.tok.pad_token = self.tok.eos_token
+        self.eos_token_id = tok.eos_token_id
+        self.pad_token_id = tok.eos_token_id
+
+    def __len__(self) -> int:
+        return len(self.tok)
+
+    def encode(self, text: str) -> List[int]:
+        return self.tok(text)["input_ids"]
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        return self.tok.decode(ids, skip_special_tokens=skip_special_tokens)
+
+
+def get_tokenizer(prefer_hf: bool = True):
+    if prefer_hf and os.environ.get("DSWARM_OFFLINE_TOKENIZER", "0") != "1":
+        try:
+            os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
+            from transformers import AutoTokenizer
+            tok = AutoTokenizer.from_pretrained("openai-community/gpt2", local_files_only=True)
+            return HFTokenizer(tok)
+        except Exception:
+            pass
+    return ByteTokenizer()
+
+
+def tokenize(text: str, tokenizer, max_length: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """Encode one string; with ``max_length`` truncate / right-pad with eos and
+    return the matching attention mask (reference: src/utils.py:102-105)."""
+    ids = tokenizer.encode(text)
+    if max_length is None:
+        return {"input_ids": torch.tensor([ids], dtype=torch.long),
+                "attention_mask": torch.ones(1, len(ids), dtype=torch.long)}
+    ids = ids[:max_length]
+    n = len(ids)
+    mask = [1] * n + [0] * (max_length - n)
+    ids = ids + [tokenizer.pad_token_id] * (max_length - n)
+    return {"input_ids": torch.tensor([ids], dtype=torch.long),
+            "attention_mask": torch.tensor([mask], dtype=torch.long)}
+
+
+class TokenDataset:
+    """Pre-tokenised sequences of length seq_length + 1 with their masks."""
+
+    def __init__(self, input_ids: torch.Tensor, attention_mask: torch.Tensor):
+        assert input_ids.shape == attention_mask.shape
+        self.input_ids, self.attention_mask = input_ids, attention_mask
+
+    def __len__(self) -> int:
+        return self.input_ids.size(0)
+
+    def select(self, idx) -> "TokenDataset":
+        return TokenDataset(self.input_ids[idx], self.attention_mask[idx])
+
+    def train_test_split(self, test_size: float, seed: int, shuffle: bool = True
+                         ) -> Tuple["TokenDataset", "TokenDataset"]:
+        n = len(self)
+        n_test = max(1, int(round(n * test_size))) if test_size > 0 else 0
+        g = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(n, generator=g) if shuffle else torch.arange(n)
+        return self.select(perm[n_test:]), self.select(perm[:n_test])
+
+
+def zipf_tokens(num: int, length: int, vocab: int, s: float, seed: int) -> torch.Tensor:
+    """iid Zipf(s) ids over [0, vocab): P(k) proportional to (k+1)^-s."""
+    w = torch.arange(1, vocab + 1, dtype=torch.float64).pow(-s)
+    cdf = torch.cumsum(w / w.sum(), 0)
+    g = torch.Generator().manual_seed(seed)
+    u = torch.rand(num, length, generator=g, dtype=torch.float64)
+    return torch.searchsorted(cdf, u).clamp_(max=vocab - 1).to(torch.long)
+
+
+def get_dataset(cfg, tokenizer, seed: int, split: str = "train") -> TokenDataset:
+    """Build or load the dataset named by ``cfg.path`` as token tensors of
+    width ``seq_length + 1`` (inputs and shifted targets share it)."""
+    width = cfg.seq_length + 1
+    path = cfg.path
+    if path.startswith("synthetic:zipf"):
+        n = cfg.num_examples or 4096
+        ids = zipf_tokens(n, width, cfg.vocab_limit, cfg.zipf_s, seed)
+        ds = TokenDataset(ids, torch.ones_like(ids))
+    elif path in ("memorize", "mikasenghaas/memorize", "synthetic:memorize"):
+        n = cfg.num_examples or 1000
+        t = tokenize(MEMORIZE_SENTENCE, tokenizer, max_length=width)
+        ds = TokenDataset(t["input_ids"].repeat(n, 1), t["attention_mask"].repeat(n, 1))
+    else:
+        ds = _load_hf(cfg, tokenizer, width, split)
+    if cfg.subset_size < 1.0:
+        ds = ds.select(torch.arange(int(len(ds) * cfg.subset_size)))
+    return ds
+
+
+def _load_hf(cfg, tokenizer, width: int, split: str) -> TokenDataset:
+    try:
+        from datasets import load_dataset, load_from_disk
+    except Exception as e:  # pragma: no cover - depends on the box
+        raise RuntimeError(f"dataset {cfg.path!r} needs the `datasets` package: {e}")
+    cache = os.path.join(os.environ.get("PERSISTENT_DIR", os.path.expanduser("~/.cache")), "huggingface", cfg.path)
+    try:
+        dd = load_from_disk(cache)
+    except Exception:
+        dd = load_dataset(cfg.path)
+        os.makedirs(os.path.dirname(cache), exist_ok=True)
+        dd.save_to_disk(cache)
+    data = dd[split]
+    if cfg.tokenize:
+        rows = [tokenize(x["text"], tokenizer, width) for x in data]
+        ids = torch.cat([r["input_ids"] for r in rows])
+        mask = torch.cat([r["attention_mask"] for r in rows])
+    else:
+        ids = torch.tensor(data["input_ids"], dtype=torch.long)[:, :width]
+        mask = torch.tensor(data["attention_mask"], dtype=torch.long)[:, :width]
+    return TokenDataset(ids, mask)
+
+
+def collate(ds: TokenDataset, lo: int, hi: int) -> Dict[str, torch.Tensor]:
+    """inputs = ids[:, :-1], targets = ids[:, 1:], mask = mask[:, :-1] (src/utils.py:107-115)."""
+    ids, mask = ds.input_ids[lo:hi], ds.attention_mask[lo:hi]
+    return {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(),
+            "attention_mask": mask[:, :-1].contiguous()}
+
+
+class BatchLoader:
+    """Sequential, drop-last batches (reference: DataLoader(shuffle=False,
+    drop_last=True), src/utils.py:117-118).  With ``pin_memory`` the batch lives
+    in page-locked memory so the per-step host-to-device copy is asynchronous."""
+
+    def __init__(self, ds: TokenDataset, batch_size: int, pin_memory: bool = False):
+        self.ds, self.batch_size = ds, batch_size
+        self.pin = pin_memory and torch.cuda.is_available()
+
+    def __len__(self) -> int:
+        return len(self.ds) // self.batch_size
+
+    def __iter__(self) -> Iterator[Dict[str, torch.Tensor]]:
+        for i in range(len(self)):
+            b = collate(self.ds, i * self.batch_size, (i + 1) * self.batch_size)
+            if self.pin:
+                b = {k: v.pin_memory() for k, v in b.items()}
+            yield b
+
+
+def micro_batch_rows(mb: int, micro_batch_size: int) -> slice:
+    """Rows of the global batch that form microbatch ``mb``.  Microbatch
+    ``k*R0 + i`` is the k-th chunk of first-stage replica i, exactly the
+    reference's round-robin chunks ``[k*R0*mbs + i*mbs, +mbs)`` (src/sampler.py:35-38)."""
+    return slice(mb * micro_batch_size, (mb + 1) * micro_batch_size)
+
+
+def get_num_steps(max_steps: int, max_epochs: int, num_examples: int, batch_size: int) -> int:
+    """Whichever of max_steps / max_epochs is reached first (src/utils.py:145-152)."""
+    if num_examples < batch_size:
+        raise ValueError("Number of examples must be at least batch size")
+    if not (max_steps > 0 or max_epochs > 0):
+        raise ValueError("Specify at least one of `max_steps` and `max_epochs`")
+    per_epochs = num_examples // batch_size * max_epochs
+    if max_epochs == -1:
+        return max_steps
+    if max_steps == -1:
+        return per_epochs
+    return min(max_steps, per_epochs)
+
+
+def get_train_setup(steps: int, batch_size: int, seq_length: int, micro_batch_size: int, num_examples: int):
+    tokens_per_step = batch_size * seq_length
+    return {"steps": steps, "batch_size": batch_size, "seq_length": seq_length,
+            "micro_batch_size": micro_batch_size, "tokens_per_step": tokens_per_step,
+            "total_tokens": steps * tokens_per_step,
+            "avg_token_repetitions": steps * tokens_per_step / max(1, num_examples * seq_length),
+            "grad_accumulation_steps": batch_size // micro_batch_size if micro_batch_size > 0 else 1}
