@@ -1,0 +1,223 @@
+"""Headline benchmark: GPT-2 small DiLoCo-SWARM training tokens/s.
+
+    python bench.py [--gpus N --steps K --warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Config (the one the reference's headline names): GPT-2 small (12 layers, d 768,
+12 heads, vocab 50304, seq 1024), global batch 512 sequences, microbatch 16,
+bf16 compute with fp32 master weights, AdamW inner, SGD-Nesterov outer
+(lr 0.7, momentum 0.9), synthetic Zipf(1.0) token ids, random init.
+Topology per N: 1 -> 1 stage x 1, 2 -> 2 x 1, 4 -> 2 x 2, 8 -> 2 x 4.
+The global batch is fixed, so this is strong scaling.  The outer sync runs
+once inside the timed region (H = min(50, K)).
+
+Two timed regions of K steps each, both on the device with CUDA events between
+a barrier + synchronize on both sides, max over ranks:
+  value  batches already resident on the device;
+  e2e    through ``Trainer.train_step`` with each step's batch in pinned host
+         memory (copied host-to-device inside the step) and the loss read back.
+One step touches several GB of weights and activations, far more than the
+126 MB L2, so no explicit L2 flush is done between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOPOLOGY = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
+SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="small")
+    ap.add_argument("--batch", type=int, default=512)
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--cap", type=int, default=4, help="max_micro_batches (in-flight microbatches per rank)")
+    ap.add_argument("--layer-split", default="even")
+    ap.add_argument("--collective", default="fused")
+    ap.add_argument("--no-outer", action="store_true", help="plain SWARM (per-step gradient all-reduce)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    def __init__(self, enabled: bool):
+        self.proc, self.path = None, None
+        if not enabled:
+            return
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                c = [x.strip() for x in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    clk, mx, pw = float(c[1]), float(c[2]), float(c[3])
+                except ValueError:
+                    continue
+                smax.append(mx)
+                power.append(pw)
+                if pw > 300:                      # samples under load
+                    sm.append(clk)
+                for n, v in zip(names, c[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples_under_load": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def build_config(args, S: int):
+    from diloco_swarm_b200.config import Config, load_toml
+    model = load_toml(os.path.join(ROOT, "configs", "model", f"gpt2-{args.model}.toml"))
+    H = max(1, min(50, args.steps))
+    outer = {"type": "None", "lr": 0.0} if args.no_outer else {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
+    return Config(
+        model=model,
+        data={"path": "synthetic:zipf", "seq_length": args.seq, "num_examples": args.batch * 2, "pin_memory": True},
+        train={"micro_batch_size": args.micro_batch, "batch_size": args.batch, "max_steps": 10 ** 6,
+               "max_micro_batches": args.cap, "step_timeout": 600,
+               "inner_optimizer": {"type": "AdamW", "lr": 6e-4},
+               "outer_optimizer": outer,
+               "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
+        swarm={"num_stages": S, "sync_every_n_steps": 1 if args.no_outer else H, "layer_split": args.layer_split,
+               "collective": args.collective},
+        eval={"enable": False}, sample={"enable": False},
+        logging={"log_dir": os.path.join(tempfile.gettempdir(), "dswarm_bench"), "run_id": f"bench{os.getpid()}",
+                 "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"}},
+        engine="b200"), H
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from diloco_swarm_b200.ops import _lib
+    from diloco_swarm_b200.train import Trainer
+    from diloco_swarm_b200.utils import data as D
+
+    N = args.gpus
+    S, R = TOPOLOGY.get(N, (2 if N % 2 == 0 else 1, N // 2 if N % 2 == 0 else N))
+    world_size = int(os.environ.get("WORLD_SIZE", "1"))
+    if world_size != N:
+        raise SystemExit(f"--gpus {N} needs {N} ranks (launch with torch.distributed.run); WORLD_SIZE={world_size}")
+    cfg, H = build_config(args, S)
+    tr = Trainer(cfg)
+    tr.num_train_steps = 10 ** 6
+    rank = tr.world.rank
+    dev = tr.device
+
+    tok = D.ByteTokenizer()
+    ds = D.get_dataset(cfg.data, tok, seed=0)
+    host = [{k: v.pin_memory() for k, v in D.collate(ds, i * args.batch, (i + 1) * args.batch).items()} for i in range(2)]
+    resident = [{k: v.to(dev) for k, v in b.items()} for b in host]
+    h2d = 0
+    if tr.engine.is_first:
+        h2d += host[0]["input_ids"].numel() * 8
+    if tr.engine.is_last:
+        h2d += (host[0]["target_ids"].numel() + host[0]["attention_mask"].numel()) * 8
+    step_no = [0]
+
+    def one(batches):
+        step_no[0] += 1
+        local, _ = tr.train_step(step_no[0], batches[step_no[0] % 2])
+        return local
+
+    def timed(batches, steps):
+        tr.world.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count()
+        e0.record()
+        last = None
+        for _ in range(steps):
+            last = one(batches)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        tr.world.barrier()
+        if world_size > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), _lib.launch_count() - l0, last
+
+    for _ in range(args.warmup):
+        one(resident)
+    sampler = ClockSampler(rank == 0)
+    ms_dev, launches, last = timed(resident, args.steps)
+    for _ in range(1):
+        one(host)
+    ms_e2e, _, last_e2e = timed(host, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    tokens = args.batch * args.seq * args.steps
+    value = tokens / (ms_dev / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+    out = {
+        "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic Zipf(1.0) token ids, random-init weights",
+        "impl": "ours",
+        "config": {"model": f"gpt2-{args.model}", "global_batch": args.batch, "seq_len": args.seq,
+                   "micro_batch": args.micro_batch, "parallelism": f"{S} stages x {R} replicas",
+                   "algorithm": "swarm" if args.no_outer else f"diloco-swarm H={H}",
+                   "max_micro_batches": args.cap, "layer_split": args.layer_split, "collective": args.collective,
+                   "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+        "gpu_launches": launches,
+        "loss": last.loss if last else None,
+    }
+    tr.world.barrier()
+    tr.logger.close()
+    tr.world.destroy()
+    return out if rank == 0 else {}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline.run_reference import run_reference
+        out = run_reference(args)
+    else:
+        out = run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

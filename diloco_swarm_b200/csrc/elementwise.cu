@@ -1,0 +1,424 @@
+// Memory-bound kernels of the GPT-2 stage: LayerNorm forward/backward,
+// bias-gradient column sums, embedding forward/backward, fused masked
+// cross-entropy (loss + logits gradient in place), casts.
+//
+// Reference call sites: F.layer_norm (src/model.py:31), nn.Embedding
+// (src/model.py:134-139), boolean-mask filter + nn.CrossEntropyLoss
+// (src/utils.py:184-193, src/train.py:217-218) and their autograd backward.
+// All are bandwidth-bound; each streams its operands once with 16-byte
+// accesses and keeps statistics in fp32.
+#include "ptx.cuh"
+#include "dswarm.h"
+
+namespace dsw {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16(w[j]);
+    f[2 * j] = t.x; f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) =
+      make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// ------------------------------------------------------------------ LayerNorm
+// One warp per row; the row stays in registers (d <= 8 * 256 = 2048).
+constexpr int LN_MAX_CHUNKS_ALL = 8;
+
+template <int LN_MAX_CHUNKS>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                     const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                     float* __restrict__ rstd_out, int M, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int nch = (d + 255) / 256;
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
+    const __nv_bfloat16* xr = x + (long long)row * d;
+    float v[LN_MAX_CHUNKS][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+        load8(xr + col, v[c]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[c][j];
+      }
+    }
+    const float mean = warp_sum(s) / d;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float t = v[c][j] - mean; q += t * t; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / d + eps);
+    if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+    __nv_bfloat16* yr = y + (long long)row * d;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+        float g[8], b[8], o[8];
+        load8f(gamma + col, g);
+        if (beta) load8f(beta + col, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[c][j] - mean) * rstd * g[j] + (beta ? b[j] : 0.f);
+        store8(yr + col, o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres); dgamma += sum dy*xhat; dbeta += sum dy.
+// Column sums are accumulated per block in shared memory (fp32) and flushed with one atomicAdd per column.
+template <int LN_MAX_CHUNKS>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const float* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta, int M,
+                     int d) {
+  extern __shared__ float sh[];       // [2][d]
+  float* sg = sh;
+  float* sb = sh + d;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) sh[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int nch = (d + 255) / 256;
+  float ag[LN_MAX_CHUNKS][8], ab[LN_MAX_CHUNKS][8];
+#pragma unroll
+  for (int c = 0; c < LN_MAX_CHUNKS; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; }
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
+    const long long off = (long long)row * d;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[LN_MAX_CHUNKS][8], gy[LN_MAX_CHUNKS][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+        float xv[8], dv[8], g[8];
+        load8(x + off + col, xv);
+        load8(dy + off + col, dv);
+        load8f(gamma + col, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[c][j] = (xv[j] - mean) * rstd;
+          gy[c][j] = dv[j] * g[j];
+          s1 += gy[c][j];
+          s2 += gy[c][j] * xh[c][j];
+          ag[c][j] += dv[j] * xh[c][j];
+          ab[c][j] += dv[j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / d;
+    s2 = warp_sum(s2) / d;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+        float o[8], r[8];
+        if (dres) load8(dres + off + col, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
+        store8(dx + off + col, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+    const int col = c * 256 + lane * 8;
+    if (c < nch && col < d) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { atomicAdd(&sg[col + j], ag[c][j]); atomicAdd(&sb[col + j], ab[c][j]); }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    atomicAdd(&dgamma[i], sg[i]);
+    if (dbeta) atomicAdd(&dbeta[i], sb[i]);
+  }
+}
+
+// ------------------------------------------------------------------ column sum (bias gradients)
+// out[n] += sum_m x[m, n].  Block = 32 column groups of 8 x 8 row lanes.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restrict__ out, int M, int N) {
+  __shared__ float sh[8][256];
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + cg * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < N) {
+    for (int row = blockIdx.y * 8 + rl; row < M; row += gridDim.y * 8) {
+      float v[8];
+      load8(x + (long long)row * ld + col, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sh[rl][cg * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.x * 256 + c < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s += sh[r][c];
+    atomicAdd(&out[blockIdx.x * 256 + c], s);
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+// y[b,t,:] = bf16(wte[ids[b,t],:] + wpe[t,:]) from the fp32 master tables.
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const long long* __restrict__ ids, const float* __restrict__ wte,
+                     const float* __restrict__ wpe, __nv_bfloat16* __restrict__ y, int BT, int T, int d, int V,
+                     int* status) {
+  const int per_row = d / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)BT * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int row = int(i / per_row), col = int(i % per_row) * 8;
+    long long id = ids[row];
+    if (id < 0 || id >= V) { if (status) atomicCAS(status, 0, ST_BAD_ARG); id = 0; }
+    float a[8], b[8], o[8];
+    load8f(wte + id * d + col, a);
+    load8f(wpe + (long long)(row % T) * d + col, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = a[j] + b[j];
+    store8(y + (long long)row * d + col, o);
+  }
+}
+// dwte[ids[r], :] += dx[r, :] (fp32 atomics); dwpe[t, :] += sum_b dx[b, t, :].
+__global__ void __launch_bounds__(256)
+embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dx,
+                     float* __restrict__ dwte, float* __restrict__ dwpe, int B, int T, int d, int V) {
+  const int per_row = d / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)T * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / per_row), col = int(i % per_row) * 8;
+    float pos[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int b = 0; b < B; ++b) {
+      const int row = b * T + t;
+      float v[8];
+      load8(dx + (long long)row * d + col, v);
+      long long id = ids[row];
+      if (id < 0 || id >= V) id = 0;
+      float* w = dwte + id * d + col;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { atomicAdd(w + j, v[j]); pos[j] += v[j]; }
+    }
+    float* p = dwpe + (long long)t * d + col;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] += pos[j];
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy
+// count[0] = number of rows with mask != 0
+__global__ void mask_count_kernel(const long long* __restrict__ mask, int M, float* __restrict__ count) {
+  __shared__ float sh[32];
+  float c = 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M; i += gridDim.x * blockDim.x) c += mask[i] != 0;
+  c = warp_sum(c);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    c = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    c = warp_sum(c);
+    if (threadIdx.x == 0) atomicAdd(count, c);
+  }
+}
+
+// One block per row.  loss_acc += scale/count * (lse - logit[target]) for kept
+// rows; with write_grad the row is overwritten by scale/count * (softmax - onehot)
+// (zeros for masked rows).  Two passes over the row; the second hits L2.
+__global__ void __launch_bounds__(512)
+cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                     const long long* __restrict__ mask, const float* __restrict__ count, float scale,
+                     float* __restrict__ loss_acc, int M, int V, int write_grad, int* status) {
+  __shared__ float shm[16], shs[16];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  __nv_bfloat16* lr = logits + (long long)row * ld;
+  const bool keep = mask == nullptr || mask[row] != 0;
+  const int nv = V / 8;
+  if (!keep) {
+    if (write_grad)
+      for (int i = threadIdx.x; i < nv; i += blockDim.x) *reinterpret_cast<uint4*>(lr + i * 8) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  float mx = -INFINITY, sm = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float v[8];
+    load8(lr + i * 8, v);
+    float m8 = v[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) m8 = fmaxf(m8, v[j]);
+    const float nm = fmaxf(mx, m8);
+    float s8 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s8 += __expf(v[j] - nm);
+    sm = sm * __expf(mx - nm) + s8;
+    mx = nm;
+  }
+  // block reduce (max, sum)
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float gm = warp_max(mx);
+  sm = warp_sum(sm * __expf(mx - gm));
+  if (lane == 0) { shm[w] = gm; shs[w] = sm; }
+  __syncthreads();
+  float bm = -INFINITY;
+  for (int i = 0; i < nw; ++i) bm = fmaxf(bm, shm[i]);
+  float bs = 0.f;
+  for (int i = 0; i < nw; ++i) bs += shs[i] * __expf(shm[i] - bm);
+  long long tgt = targets[row];
+  if (tgt < 0 || tgt >= V) { if (status && threadIdx.x == 0) atomicCAS(status, 0, ST_BAD_ARG); tgt = 0; }
+  const float cnt = count ? fmaxf(count[0], 1.f) : 1.f;
+  const float k = scale / cnt;
+  if (threadIdx.x == 0) {
+    const float lt = __bfloat162float(lr[tgt]);
+    atomicAdd(loss_acc, k * (logf(bs) + bm - lt));
+  }
+  if (!write_grad) return;
+  __syncthreads();      // the target logit was read before anyone overwrites it
+  const float inv = k / bs;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float v[8];
+    load8(lr + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = __expf(v[j] - bm) * inv;
+      v[j] = (i * 8 + j == tgt) ? p - k : p;
+    }
+    store8(lr + i * 8, v);
+  }
+}
+
+// ------------------------------------------------------------------ casts
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long n8 = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8f(src + i * 8, v);
+    store8(dst + i * 8, v);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - n8 * 8) dst[n8 * 8 + threadIdx.x] = __float2bfloat16(src[n8 * 8 + threadIdx.x]);
+}
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __bfloat162float(src[i]);
+}
+
+static inline int grid_for(long long work, int block, int cap = 148 * 8) {
+  long long g = (work + block - 1) / block;
+  return int(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace dsw
+
+using namespace dsw;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int dsw_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean,
+                                 float* rstd, int M, int d, float eps, cudaStream_t st) {
+  if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
+  const int grid = grid_for(M, 8);
+#define LN_FWD(NCH) layernorm_fwd_kernel<NCH><<<grid, 256, 0, st>>>((const bf16*)x, gamma, beta, (bf16*)y, mean, rstd, M, d, eps)
+  switch ((d + 255) / 256) {
+    case 1: LN_FWD(1); break; case 2: LN_FWD(2); break; case 3: LN_FWD(3); break; case 4: LN_FWD(4); break;
+    case 5: LN_FWD(5); break; case 6: LN_FWD(6); break; case 7: LN_FWD(7); break; default: LN_FWD(8); break;
+  }
+#undef LN_FWD
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean,
+                                 const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta, int M,
+                                 int d, cudaStream_t st) {
+  if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
+  const int grid = grid_for(M, 8 * 8, 148 * 2);
+#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 2 * d * sizeof(float), st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, dgamma, dbeta, M, d)
+  switch ((d + 255) / 256) {
+    case 1: LN_BWD(1); break; case 2: LN_BWD(2); break; case 3: LN_BWD(3); break; case 4: LN_BWD(4); break;
+    case 5: LN_BWD(5); break; case 6: LN_BWD(6); break; case 7: LN_BWD(7); break; default: LN_BWD(8); break;
+  }
+#undef LN_BWD
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_colsum_accum(const void* x, long long ld, float* out, int M, int N, cudaStream_t st) {
+  if (N % 8 || ld % 8) return -10;
+  dim3 grid((N + 255) / 256, M >= 4096 ? 64 : (M >= 256 ? 16 : 1));
+  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, ld, out, M, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_embedding_fwd(const long long* ids, const float* wte, const float* wpe, void* y, int B, int T,
+                                 int d, int V, int* status, cudaStream_t st) {
+  if (d % 8) return -10;
+  embedding_fwd_kernel<<<grid_for((long long)B * T * (d / 8), 256), 256, 0, st>>>(ids, wte, wpe, (bf16*)y, B * T, T, d,
+                                                                                V, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_embedding_bwd(const long long* ids, const void* dx, float* dwte, float* dwpe, int B, int T, int d,
+                                 int V, cudaStream_t st) {
+  if (d % 8) return -10;
+  embedding_bwd_kernel<<<grid_for((long long)T * (d / 8), 256), 256, 0, st>>>(ids, (const bf16*)dx, dwte, dwpe, B, T, d,
+                                                                             V);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// count must be zeroed by the caller before dsw_mask_count.
+extern "C" int dsw_mask_count(const long long* mask, int M, float* count, cudaStream_t st) {
+  mask_count_kernel<<<grid_for(M, 256, 64), 256, 0, st>>>(mask, M, count);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_cross_entropy(void* logits, long long ld, const long long* targets, const long long* mask,
+                                 const float* count, float scale, float* loss_acc, int M, int V, int write_grad,
+                                 int* status, cudaStream_t st) {
+  if (V % 8 || ld % 8) return -10;
+  cross_entropy_kernel<<<M, 512, 0, st>>>((bf16*)logits, ld, targets, mask, count, scale, loss_acc, M, V, write_grad,
+                                          status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t st) {
+  cast_f32_bf16_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, st>>>(src, (bf16*)dst, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+extern "C" int dsw_cast_bf16_f32(const void* src, float* dst, long long n, cudaStream_t st) {
+  cast_bf16_f32_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)src, dst, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,382 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[M,N] = op(A) * op(B), fp32
+// accumulation in tensor memory, operands staged in shared memory by TMA.
+//
+// Replaces the library GEMMs behind the reference's nn.Linear calls and their
+// autograd backward (src/model.py:44-45,83-84,118 and src/model.py:205-209):
+//   forward   y  = x  W^T      A = x  [M,K] K-major,  B = W [N,K] K-major
+//   dgrad     dx = dy W        A = dy [M,K] K-major,  B = W [K,N] N-major
+//   wgrad     dW = dy^T x      A = dy [K,M] M-major,  B = x [K,N] N-major
+// with the elementwise work fused into the epilogue (bias, exact GELU and its
+// derivative, residual add, fp32 accumulation into the main gradient).
+//
+// Structure: persistent CTAs (one per SM), 192 threads.
+//   warp 0      TMA producer: fills a ring of NSTAGE {A,B} k-blocks
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, math, stores
+// Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap
+// the main loop of tile i+1.  No thread-block clusters and no multicast loads.
+#include <cuda.h>
+#include <cstdio>
+#include <mutex>
+#include "ptx.cuh"
+#include "dswarm.h"
+
+namespace dsw {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum EpiMode : int {
+  EPI_STORE = 0,        // out = acc (+ bias)
+  EPI_GELU = 1,         // aux_out = acc + bias ; out = gelu(aux_out)
+  EPI_RESID = 2,        // out = acc + bias + resid
+  EPI_DGELU = 3,        // out = acc * gelu'(aux_in)
+  EPI_ATOMIC_F32 = 4,   // out_f32 += acc   (split-K safe)
+  EPI_STORE_F32 = 5,    // out_f32 = acc
+};
+
+struct GemmArgs {
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int mode;
+  int split_k;
+  void* out; long long ldo;
+  const float* bias;
+  const __nv_bfloat16* resid; long long ldr;
+  __nv_bfloat16* aux_out; const __nv_bfloat16* aux_in; long long ldaux;
+  int* status;
+};
+
+template <int BN, int NSTAGE>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = NSTAGE * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + alignment slack
+};
+
+template <int BN, int NSTAGE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
+  using L = SmemLayout<BN, NSTAGE>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + NSTAGE;
+  uint64_t* acc_full = empty_bar + NSTAGE;      // [2]
+  uint64_t* acc_empty = acc_full + 2;           // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (g.M + BM - 1) / BM;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  const int kb_total = (g.K + BK - 1) / BK;
+  const int splits = g.split_k > 1 ? g.split_k : 1;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  const int num_tiles = tiles_m * tiles_n * splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int ks = tile / (tiles_m * tiles_n);
+        const int rem = tile - ks * tiles_m * tiles_n;
+        const int m0 = (rem % tiles_m) * BM;
+        const int n0 = (rem / tiles_m) * BN;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, g.status)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!g.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmap_a, &full_bar[s], m0 + 64 * c, k0);
+          }
+          if (!g.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tmap_b, &full_bar[s], n0 + 64 * c, k0);
+          }
+        }
+      }
+      if (!ok) {
+        // give loads that are still in flight a bounded chance to land before the CTA exits
+        for (int s = 0; s < NSTAGE; ++s) {
+          for (int spin = 0; spin < 100000; ++spin)
+            if (mbar_try_wait(&full_bar[s], 0) || mbar_try_wait(&full_bar[s], 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, g.a_mn_major, g.b_mn_major);
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int ks = tile / (tiles_m * tiles_n);
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(kb_total, kb0 + kb_per_split);
+        const int ab = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&acc_empty[ab], aph ^ 1, abort_flag, g.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        uint32_t accumulate = 0;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 elements = 32 bytes further along the swizzled row.
+            // MN-major: 16 k-rows of 128 bytes further down.
+            const uint64_t da = g.a_mn_major ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                             : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = g.b_mn_major ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                             : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(&empty_bar[s]);      // frees the smem stage when these MMAs retire
+        }
+        if (ok) umma_commit(&acc_full[ab]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int ks = tile / (tiles_m * tiles_n);
+      const int rem = tile - ks * tiles_m * tiles_n;
+      const int m0 = (rem % tiles_m) * BM;
+      const int n0 = (rem / tiles_m) * BN;
+      const int ab = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      const int kb0 = ks * kb_per_split;
+      const bool has_k = kb0 < kb_total;
+      if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < g.M;
+      const uint32_t t_base = tmem_base + ab * BN + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_base + c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= BN) {
+          // all TMEM reads of this accumulator are done: hand it back early
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[ab]);
+        }
+        const int col0 = n0 + c0;
+        if (!row_ok || col0 >= g.N || !has_k) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        if (g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32) {
+          float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            if (col0 + i < g.N) {
+              if (g.mode == EPI_ATOMIC_F32) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + i), "f"(v[i]), "f"(v[i + 1]),
+                             "f"(v[i + 2]), "f"(v[i + 3])
+                             : "memory");
+              } else {
+                *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+              }
+            }
+          }
+          continue;
+        }
+        if (g.bias) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            if (col0 + i < g.N) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
+              v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
+            }
+          }
+        }
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          if (col0 + i >= g.N) break;
+          float* w = v + i;
+          if (g.mode == EPI_GELU) {
+            uint4 pre = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]),
+                                   pack_bf16(w[6], w[7]));
+            *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0 + i) = pre;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = gelu_erf(w[j]);
+          } else if (g.mode == EPI_RESID) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(g.resid + (long long)row * g.ldr + col0 + i);
+            const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16(ru[j]);
+              w[2 * j] += f.x; w[2 * j + 1] += f.y;
+            }
+          } else if (g.mode == EPI_DGELU) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0 + i);
+            const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16(ru[j]);
+              w[2 * j] *= gelu_erf_grad(f.x); w[2 * j + 1] *= gelu_erf_grad(f.y);
+            }
+          }
+          *reinterpret_cast<uint4*>(o + i) = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]),
+                                                        pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements.
+int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld,
+                      int box_inner, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+static int g_num_sms = 0;
+
+template <int BN, int NSTAGE>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int max_ctas, cudaStream_t st) {
+  using L = SmemLayout<BN, NSTAGE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_kernel<BN, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
+        cudaSuccess)
+      return -2;
+    attr_set = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * (g.split_k > 1 ? g.split_k : 1);
+  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_kernel<BN, NSTAGE><<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace dsw
+
+using namespace dsw;
+
+// A: [M,K] row-major (a_mn_major = 0) or [K,M] row-major (1); lda = row pitch in
+// elements.  B: [N,K] (b_mn_major = 0) or [K,N] (1).  All pitches and the
+// contiguous extents must be multiples of 8 elements; pointers 16-byte aligned.
+// bn = 128 or 256 selects the tile width; max_ctas > 0 caps the grid (to leave
+// SMs to a concurrent kernel).  Returns 0 or a negative error code.
+extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
+                             int b_mn_major, int M, int N, int K, int mode, int split_k, void* out, long long ldo,
+                             const float* bias, const void* resid, long long ldr, void* aux_out, const void* aux_in,
+                             long long ldaux, int bn, int max_ctas, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda | ldb | ldo) % 8 || N % 8 || (a_mn_major ? M % 8 : K % 8) || (b_mn_major ? N % 8 : K % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return -11;
+  if (bn != 128 && bn != 256) return -12;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn_major) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  else             rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn_major) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
+  else             rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K;
+  g.a_mn_major = a_mn_major; g.b_mn_major = b_mn_major;
+  g.mode = mode; g.split_k = split_k;
+  g.out = out; g.ldo = ldo; g.bias = bias;
+  g.resid = reinterpret_cast<const __nv_bfloat16*>(resid); g.ldr = ldr;
+  g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in); g.ldaux = ldaux;
+  g.status = status;
+  if (bn == 256) return launch<256, 4>(ta, tb, g, max_ctas, stream);
+  return launch<128, 6>(ta, tb, g, max_ctas, stream);
+}

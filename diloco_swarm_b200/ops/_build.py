@@ -21,7 +21,7 @@ CUDA_LIB = os.path.join(PKG_DIR, "libdswarm_cuda.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
     "--expt-relaxed-constexpr",
 ]
 

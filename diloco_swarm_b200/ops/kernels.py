@@ -1,0 +1,200 @@
+"""Python entry points of the sm_100a kernels (csrc/*.cu).
+
+Each function takes torch CUDA tensors, checks shapes/dtypes on the host and
+launches on the current stream.  None of them synchronises or allocates beyond
+its outputs.  The docstrings name the reference call site each one replaces.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from ._lib import Status, check, cuda_lib, ptr, stream_ptr
+
+BF16, F32 = torch.bfloat16, torch.float32
+
+EPI_STORE, EPI_GELU, EPI_RESID, EPI_DGELU, EPI_ATOMIC_F32, EPI_STORE_F32 = range(6)
+
+_NUM_SMS = 148
+
+
+def _pick_bn(M: int, N: int, splits: int = 1) -> int:
+    """Tile width: 256 unless the narrower tile fills the SMs clearly better."""
+    def waves(bn):
+        tiles = math.ceil(M / 128) * math.ceil(N / bn) * splits
+        w = math.ceil(tiles / _NUM_SMS)
+        return tiles / (w * _NUM_SMS)          # fraction of SM-time doing work
+    if N <= 128:
+        return 128
+    return 256 if waves(256) >= waves(128) * 0.93 else 128
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = True, mode: int = EPI_STORE,
+         out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         resid: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
+         aux_in: Optional[torch.Tensor] = None, split_k: int = 1, bn: int = 0, max_ctas: int = 0,
+         status: Optional[Status] = None) -> torch.Tensor:
+    """D = op(A) @ op(B) on tcgen05 (replaces nn.Linear's GEMMs and their
+    backward, src/model.py:44-45,83-84,118).
+
+    ``a`` is [M,K] (or [K,M] with ``a_t``), ``b`` is [N,K] with ``b_t`` (the
+    nn.Linear weight layout) or [K,N] without.  bf16 in, fp32 accumulate.
+    """
+    assert a.dtype == BF16 and b.dtype == BF16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if a_t:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_t:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    f32_out = mode in (EPI_ATOMIC_F32, EPI_STORE_F32)
+    if out is None:
+        assert mode != EPI_ATOMIC_F32
+        out = torch.empty(M, N, dtype=F32 if f32_out else BF16, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype == (F32 if f32_out else BF16)
+    if mode == EPI_GELU:
+        assert aux_out is not None and aux_out.shape == (M, N) and aux_out.dtype == BF16
+    if mode == EPI_DGELU:
+        assert aux_in is not None and aux_in.shape == (M, N) and aux_in.dtype == BF16
+    if mode == EPI_RESID:
+        assert resid is not None and resid.shape == (M, N) and resid.dtype == BF16
+    if bias is not None:
+        assert bias.dtype == F32 and bias.numel() == N
+    kb_total = math.ceil(K / 64)
+    split_k = max(1, min(split_k, kb_total))
+    if split_k > 1:
+        assert mode == EPI_ATOMIC_F32, "split-K needs the accumulating epilogue"
+        per = math.ceil(kb_total / split_k)
+        split_k = math.ceil(kb_total / per)       # no empty split
+    if bn == 0:
+        bn = _pick_bn(M, N, split_k)
+    aux = aux_out if aux_out is not None else aux_in
+    rc = cuda_lib().dsw_gemm_bf16(
+        a.data_ptr(), a.stride(0), 1 if a_t else 0, b.data_ptr(), b.stride(0), 0 if b_t else 1, M, N, K, mode,
+        split_k, out.data_ptr(), out.stride(0), ptr(bias), ptr(resid), resid.stride(0) if resid is not None else 0,
+        ptr(aux_out), ptr(aux_in), aux.stride(0) if aux is not None else 0, bn, max_ctas,
+        status.ptr if status is not None else None, stream_ptr())
+    check(rc, "dsw_gemm_bf16")
+    return out
+
+
+def wgrad_split(M: int, N: int, K: int) -> int:
+    """Split-K factor for dW[M,N] = dy^T x with K = tokens: enough splits to
+    give every SM a tile."""
+    tiles = math.ceil(M / 128) * math.ceil(N / 256)
+    if tiles >= _NUM_SMS:
+        return 1
+    return max(1, min(_NUM_SMS // tiles, math.ceil(K / 64) // 4))
+
+
+def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float = 1e-5
+                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """y, mean, rstd of F.layer_norm (src/model.py:31); bf16 in/out, fp32 statistics."""
+    M, d = x.shape
+    assert x.dtype == BF16 and x.is_contiguous() and gamma.dtype == F32
+    y = torch.empty_like(x)
+    mean = torch.empty(M, dtype=F32, device=x.device)
+    rstd = torch.empty(M, dtype=F32, device=x.device)
+    check(cuda_lib().dsw_layernorm_fwd(x.data_ptr(), gamma.data_ptr(), ptr(beta), y.data_ptr(), mean.data_ptr(),
+                                       rstd.data_ptr(), M, d, eps, stream_ptr()), "dsw_layernorm_fwd")
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
+                  dgamma: torch.Tensor, dbeta: Optional[torch.Tensor], dres: Optional[torch.Tensor] = None
+                  ) -> torch.Tensor:
+    """dx of LayerNorm plus ``dres`` (the gradient arriving on the residual
+    branch); accumulates dgamma / dbeta (fp32) in place."""
+    M, d = x.shape
+    assert dy.shape == x.shape and dy.is_contiguous() and x.is_contiguous()
+    dx = torch.empty_like(x)
+    check(cuda_lib().dsw_layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                       ptr(dres), dx.data_ptr(), dgamma.data_ptr(), ptr(dbeta), M, d, stream_ptr()),
+          "dsw_layernorm_bwd")
+    return dx
+
+
+def colsum_accum(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] += sum_m x[m,n] (bias gradients)."""
+    M, N = x.shape
+    assert x.dtype == BF16 and x.stride(1) == 1 and out.dtype == F32 and out.numel() == N
+    check(cuda_lib().dsw_colsum_accum(x.data_ptr(), x.stride(0), out.data_ptr(), M, N, stream_ptr()), "dsw_colsum_accum")
+
+
+def embedding_fwd(ids: torch.Tensor, wte: torch.Tensor, wpe: torch.Tensor, status: Optional[Status] = None
+                  ) -> torch.Tensor:
+    """bf16(wte[ids] + wpe[pos]) from the fp32 tables (src/model.py:134-139)."""
+    B, T = ids.shape
+    V, d = wte.shape
+    assert ids.dtype == torch.long and ids.is_contiguous() and wte.dtype == F32 and wpe.dtype == F32
+    y = torch.empty(B * T, d, dtype=BF16, device=ids.device)
+    check(cuda_lib().dsw_embedding_fwd(ids.data_ptr(), wte.data_ptr(), wpe.data_ptr(), y.data_ptr(), B, T, d, V,
+                                       status.ptr if status else None, stream_ptr()), "dsw_embedding_fwd")
+    return y
+
+
+def embedding_bwd(ids: torch.Tensor, dx: torch.Tensor, dwte: torch.Tensor, dwpe: torch.Tensor) -> None:
+    B, T = ids.shape
+    V, d = dwte.shape
+    assert dx.dtype == BF16 and dx.is_contiguous() and dwte.dtype == F32
+    check(cuda_lib().dsw_embedding_bwd(ids.data_ptr(), dx.data_ptr(), dwte.data_ptr(), dwpe.data_ptr(), B, T, d, V,
+                                       stream_ptr()), "dsw_embedding_bwd")
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, mask: Optional[torch.Tensor], scale: float,
+                  loss_acc: torch.Tensor, count_buf: torch.Tensor, write_grad: bool = True,
+                  status: Optional[Status] = None) -> None:
+    """Masked mean cross-entropy times ``scale`` added to ``loss_acc``; with
+    ``write_grad`` the logits are overwritten by their gradient (reference:
+    filter_logits_targets + CrossEntropyLoss, src/utils.py:184-193)."""
+    M, V = logits.shape
+    assert logits.dtype == BF16 and logits.stride(1) == 1
+    assert targets.dtype == torch.long and targets.numel() == M
+    lib = cuda_lib()
+    cnt = None
+    if mask is not None:
+        assert mask.dtype == torch.long and mask.numel() == M
+        count_buf.zero_()
+        check(lib.dsw_mask_count(mask.data_ptr(), M, count_buf.data_ptr(), stream_ptr()), "dsw_mask_count")
+        cnt = count_buf.data_ptr()
+    else:
+        count_buf.fill_(float(M))
+        cnt = count_buf.data_ptr()
+    check(lib.dsw_cross_entropy(logits.data_ptr(), logits.stride(0), targets.data_ptr(), ptr(mask), cnt, scale,
+                                loss_acc.data_ptr(), M, V, 1 if write_grad else 0,
+                                status.ptr if status else None, stream_ptr()), "dsw_cross_entropy")
+
+
+def cast_to_bf16(src: torch.Tensor, dst: torch.Tensor) -> None:
+    assert src.dtype == F32 and dst.dtype == BF16 and src.numel() == dst.numel()
+    check(cuda_lib().dsw_cast_f32_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), stream_ptr()), "dsw_cast_f32_bf16")
+
+
+def grad_norm_and_clip(grad: torch.Tensor, stats: torch.Tensor, max_norm: float) -> None:
+    """stats = [sum of squares, norm, clip coefficient] on the device
+    (clip_grad_norm_ over the stage shard, src/train.py:255)."""
+    stats.zero_()
+    lib = cuda_lib()
+    check(lib.dsw_sumsq(grad.data_ptr(), grad.numel(), stats.data_ptr(), stream_ptr()), "dsw_sumsq")
+    check(lib.dsw_clip_coef(stats.data_ptr(), max_norm, stream_ptr()), "dsw_clip_coef")
+
+
+def adamw_step(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, p16: Optional[torch.Tensor],
+               lr: float, betas, eps: float, wd: float, step: int, coef: Optional[torch.Tensor],
+               zero_grad: bool = True) -> None:
+    """Fused clip-scale + AdamW + bf16 weight refresh + gradient clear (src/utils.py:61)."""
+    check(cuda_lib().dsw_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), ptr(p16), p.numel(), lr,
+                               betas[0], betas[1], eps, wd, step, coef[2:].data_ptr() if coef is not None else None,
+                               1 if zero_grad else 0, stream_ptr()), "dsw_adamw")
+
+
+def sgd_step(p, g, buf, p16, lr: float, mu: float, nesterov: bool, coef, zero_grad: bool = True) -> None:
+    check(cuda_lib().dsw_sgd(p.data_ptr(), g.data_ptr(), ptr(buf), ptr(p16), p.numel(), lr, mu, 1 if nesterov else 0,
+                             coef[2:].data_ptr() if coef is not None else None, 1 if zero_grad else 0, stream_ptr()),
+          "dsw_sgd")

@@ -1,0 +1,104 @@
+"""Symmetric (peer-mapped) device buffers for a stage's replicas.
+
+Every replica allocates a buffer of the same size with cudaMalloc, exports a
+CUDA IPC handle, and opens the handles of the other replicas of its stage
+(all on one NVSwitch node), which yields R device pointers to the same logical
+buffer.  The fused collectives (csrc/collectives.cu) take these pointers and
+issue plain peer loads and stores.  The reference has no counterpart: it
+copies through host memory and gloo (src/comm.py:38,117-123).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops._lib import check, cuda_lib
+
+MAX_PEERS = 8
+FLAG_BLOCKS = 148          # csrc/dswarm.h: DSW_MAX_COLL_BLOCKS
+FLAG_WORDS = FLAG_BLOCKS * MAX_PEERS
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ carrier so torch can view raw device memory."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+        self._owner = owner
+
+
+class SymmetricBuffer:
+    """``nbytes`` of device memory on every rank of ``group`` plus pointers to
+    the peers' copies.  ``local`` is this rank's buffer as a uint8 tensor."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None, ranks: Optional[Sequence[int]] = None):
+        lib = cuda_lib()
+        self.device = device
+        self.nbytes = (nbytes + 255) // 256 * 256
+        p = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            check(lib.dsw_symm_alloc(self.nbytes, ctypes.byref(p)), "dsw_symm_alloc")
+        self.ptr = p.value
+        self._imported: List[int] = []
+        self.local = torch.as_tensor(_CudaArray(self.ptr, self.nbytes, self), device=device)
+        R = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
+        self.rank_in_group = dist.get_rank(group) if R > 1 else 0
+        self.peer_ptrs: List[int] = [self.ptr]
+        if R > 1:
+            if R > MAX_PEERS:
+                raise ValueError(f"at most {MAX_PEERS} replicas per stage")
+            handle = (ctypes.c_char * 64)()
+            check(lib.dsw_symm_export(self.ptr, handle), "dsw_symm_export")
+            mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(device)
+            gathered = [torch.empty_like(mine) for _ in range(R)]
+            dist.all_gather(gathered, mine, group=group)
+            self.peer_ptrs = []
+            for j, h in enumerate(gathered):
+                if j == self.rank_in_group:
+                    self.peer_ptrs.append(self.ptr)
+                    continue
+                raw = bytes(h.cpu().numpy().tobytes())
+                q = ctypes.c_void_p()
+                with torch.cuda.device(device):
+                    check(lib.dsw_symm_import(raw, ctypes.byref(q)), "dsw_symm_import")
+                self._imported.append(q.value)
+                self.peer_ptrs.append(q.value)
+        self.R = R
+        self._table = (ctypes.c_void_p * MAX_PEERS)(*[ctypes.c_void_p(x) for x in self.peer_ptrs])
+
+    @property
+    def table(self):
+        """Host array of R device pointers in replica order (launcher argument)."""
+        return self._table
+
+    def view(self, dtype: torch.dtype, numel: Optional[int] = None, byte_offset: int = 0) -> torch.Tensor:
+        t = self.local[byte_offset:].view(dtype)
+        return t if numel is None else t[:numel]
+
+    def close(self) -> None:
+        lib = cuda_lib()
+        for q in self._imported:
+            lib.dsw_symm_unimport(q)
+        self._imported = []
+        if self.ptr:
+            self.local = None
+            lib.dsw_symm_free(self.ptr)
+            self.ptr = 0
+
+
+class LocalPeerSet:
+    """R buffers on ONE GPU standing in for R replicas.  Used to check the
+    collective kernels' arithmetic with sequential launches (one per emulated
+    replica, barriers off): kernels that wait on one another must not share a GPU."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor]):
+        self.tensors = list(tensors)
+        self.R = len(tensors)
+        self._table = (ctypes.c_void_p * MAX_PEERS)(*[ctypes.c_void_p(t.data_ptr()) for t in tensors])
+
+    @property
+    def table(self):
+        return self._table

@@ -1,0 +1,95 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def _close(out, ref, what):
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs().max().item()
+    tol = 2e-2 * ref.abs().max().item() + 1e-3
+    assert err <= tol, f"{what}: max abs err {err} > {tol}"
+
+
+SHAPES = [(128, 256, 64), (256, 512, 768), (200, 264, 200), (1024, 768, 3072), (384, 2304, 768), (129, 136, 72)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_nt(M, N, K, bn):
+    from diloco_swarm_b200.ops import kernels as Kn
+    from diloco_swarm_b200.ops._lib import Status
+    st = Status(torch.device("cuda"))
+    a, b = _mk((M, K), seed=1), _mk((N, K), seed=2)
+    out = Kn.gemm(a, b, bn=bn, status=st)
+    torch.cuda.synchronize()
+    st.raise_if_set()
+    _close(out, a.float() @ b.float().t(), f"NT {M}x{N}x{K} bn{bn}")
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_nn_dgrad(M, N, K):
+    """A K-major, B [K,N] N-major (dx = dy @ W)."""
+    from diloco_swarm_b200.ops import kernels as Kn
+    from diloco_swarm_b200.ops._lib import Status
+    st = Status(torch.device("cuda"))
+    a, b = _mk((M, K), seed=3), _mk((K, N), seed=4)
+    out = Kn.gemm(a, b, b_t=False, status=st)
+    torch.cuda.synchronize()
+    st.raise_if_set()
+    _close(out, a.float() @ b.float(), f"NN {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("split", [1, 3])
+def test_gemm_tn_wgrad(M, N, K, split):
+    """A [K,M] M-major, B [K,N] N-major, fp32 accumulate (dW += dy^T @ x)."""
+    from diloco_swarm_b200.ops import kernels as Kn
+    from diloco_swarm_b200.ops._lib import Status
+    st = Status(torch.device("cuda"))
+    a, b = _mk((K, M), seed=5), _mk((K, N), seed=6)
+    base = torch.randn(M, N, device="cuda")
+    out = base.clone()
+    Kn.gemm(a, b, a_t=True, b_t=False, mode=Kn.EPI_ATOMIC_F32, out=out, split_k=split, status=st)
+    torch.cuda.synchronize()
+    st.raise_if_set()
+    _close(out, base + a.float().t() @ b.float(), f"TN {M}x{N}x{K} split{split}")
+
+
+def test_gemm_epilogues():
+    from diloco_swarm_b200.ops import kernels as Kn
+    M, N, K = 512, 768, 256
+    a, b = _mk((M, K), seed=7), _mk((N, K), 0.05, seed=8)
+    bias = torch.randn(N, device="cuda")
+    acc = a.float() @ b.float().t() + bias
+    out = Kn.gemm(a, b, bias=bias)
+    _close(out, acc, "bias")
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    out = Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias, aux_out=pre)
+    _close(pre, acc, "gelu pre-activation")
+    _close(out, torch.nn.functional.gelu(acc), "gelu")
+    res = _mk((M, N), seed=9)
+    out = Kn.gemm(a, b, mode=Kn.EPI_RESID, bias=bias, resid=res)
+    _close(out, acc + res.float(), "residual")
+    aux = _mk((M, N), seed=10)
+    x = aux.float().requires_grad_(True)
+    torch.nn.functional.gelu(x).sum().backward()
+    out = Kn.gemm(a, b, mode=Kn.EPI_DGELU, aux_in=aux)
+    _close(out, (a.float() @ b.float().t()) * x.grad, "gelu backward")
+    out32 = Kn.gemm(a, b, mode=Kn.EPI_STORE_F32)
+    _close(out32, a.float() @ b.float().t(), "fp32 store")
+
+
+def test_gemm_persistent_many_tiles():
+    """More tiles than SMs, so CTAs loop over tiles and both accumulators are reused."""
+    from diloco_swarm_b200.ops import kernels as Kn
+    M, N, K = 4096, 2304, 768
+    a, b = _mk((M, K), seed=11), _mk((N, K), 0.05, seed=12)
+    _close(Kn.gemm(a, b), a.float() @ b.float().t(), "persistent")
+    _close(Kn.gemm(a, b, max_ctas=7), a.float() @ b.float().t(), "persistent capped grid")
