@@ -293,14 +293,15 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lon
   }
   // block reduce (max, sum)
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  // threads (and whole warps) that saw no element carry max = -inf, sum = 0: skip them
   float gm = warp_max(mx);
-  sm = warp_sum(sm * __expf(mx - gm));
+  sm = warp_sum(mx == -INFINITY ? 0.f : sm * __expf(mx - gm));
   if (lane == 0) { shm[w] = gm; shs[w] = sm; }
   __syncthreads();
   float bm = -INFINITY;
   for (int i = 0; i < nw; ++i) bm = fmaxf(bm, shm[i]);
   float bs = 0.f;
-  for (int i = 0; i < nw; ++i) bs += shs[i] * __expf(shm[i] - bm);
+  for (int i = 0; i < nw; ++i) bs += shm[i] == -INFINITY ? 0.f : shs[i] * __expf(shm[i] - bm);
   long long tgt = targets[row];
   if (tgt < 0 || tgt >= V) { if (status && threadIdx.x == 0) atomicCAS(status, 0, ST_BAD_ARG); tgt = 0; }
   const float cnt = count ? fmaxf(count[0], 1.f) : 1.f;

@@ -46,7 +46,7 @@ def test_gemm_nn_dgrad(M, N, K):
     _close(out, a.float() @ b.float(), f"NN {M}x{N}x{K}")
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("M,N,K", SHAPES[:-1] + [(136, 136, 72)])
 @pytest.mark.parametrize("split", [1, 3])
 def test_gemm_tn_wgrad(M, N, K, split):
     """A [K,M] M-major, B [K,N] N-major, fp32 accumulate (dW += dy^T @ x)."""
