@@ -95,28 +95,29 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
   }
 }
 
-// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres); dgamma += sum dy*xhat; dbeta += sum dy.
-// Column sums are accumulated per block in shared memory (fp32) and flushed with one atomicAdd per column.
+// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres).
+// Column sums (dgamma = sum dy*xhat, dbeta = sum dy, and optionally the column
+// sum of dres, which is the bias gradient of the linear layer that produced the
+// residual branch) are accumulated in registers per thread, combined per block
+// in shared memory and written to a scratch array partial[block][3][d]; a
+// second small kernel adds the per-block partials into the fp32 gradients.
 template <int LN_MAX_CHUNKS>
 __global__ void __launch_bounds__(256)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                     __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta, int M,
-                     int d) {
-  extern __shared__ float sh[];       // [2][d]
-  float* sg = sh;
-  float* sb = sh + d;
-  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) sh[i] = 0.f;
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int want_res_sum, int M, int d) {
+  extern __shared__ float sh[];       // [3][d]
+  for (int i = threadIdx.x; i < 3 * d; i += blockDim.x) sh[i] = 0.f;
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int nch = (d + 255) / 256;
-  float ag[LN_MAX_CHUNKS][8], ab[LN_MAX_CHUNKS][8];
+  float ag[LN_MAX_CHUNKS][8], ab[LN_MAX_CHUNKS][8], ar[LN_MAX_CHUNKS][8];
 #pragma unroll
   for (int c = 0; c < LN_MAX_CHUNKS; ++c)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; }
+    for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; ar[c][j] = 0.f; }
   for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
     const long long off = (long long)row * d;
     const float mean = mean_in[row], rstd = rstd_in[row];
@@ -150,7 +151,10 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
         float o[8], r[8];
         if (dres) load8(dres + off + col, r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
+        for (int j = 0; j < 8; ++j) {
+          o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
+          if (dres) ar[c][j] += r[j];
+        }
         store8(dx + off + col, o);
       }
     }
@@ -160,14 +164,31 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     const int col = c * 256 + lane * 8;
     if (c < nch && col < d) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { atomicAdd(&sg[col + j], ag[c][j]); atomicAdd(&sb[col + j], ab[c][j]); }
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&sh[col + j], ag[c][j]);
+        atomicAdd(&sh[d + col + j], ab[c][j]);
+        if (want_res_sum) atomicAdd(&sh[2 * d + col + j], ar[c][j]);
+      }
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    atomicAdd(&dgamma[i], sg[i]);
-    if (dbeta) atomicAdd(&dbeta[i], sb[i]);
-  }
+  float* out = partial + (long long)blockIdx.x * 3 * d;
+  for (int i = threadIdx.x; i < 3 * d; i += blockDim.x) out[i] = sh[i];
+}
+
+// dgamma[c] += sum_b partial[b][0][c], dbeta[c] += sum_b partial[b][1][c],
+// dres_sum[c] += sum_b partial[b][2][c] (when requested).
+__global__ void __launch_bounds__(256)
+layernorm_bwd_finish_kernel(const float* __restrict__ partial, int nblocks, int d, float* __restrict__ dgamma,
+                            float* __restrict__ dbeta, float* __restrict__ dres_sum) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 3 * d) return;
+  const int which = i / d, c = i - which * d;
+  float* dst = which == 0 ? dgamma : (which == 1 ? dbeta : dres_sum);
+  if (!dst) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 3 * d + i];
+  dst[c] += s;
 }
 
 // ------------------------------------------------------------------ column sum (bias gradients)
@@ -363,17 +384,26 @@ extern "C" int dsw_layernorm_fwd(const void* x, const float* gamma, const float*
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Number of blocks dsw_layernorm_bwd launches for M rows = rows of scratch it needs.
+extern "C" int dsw_layernorm_bwd_blocks(int M) { return grid_for(M, 8 * 8, 296); }
+
+// scratch: fp32 [dsw_layernorm_bwd_blocks(M)][3][d], contents irrelevant on entry.
+// dres_sum (optional): fp32 [d] += column sum of dres.
 extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean,
-                                 const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta, int M,
-                                 int d, cudaStream_t st) {
+                                 const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
+                                 float* dres_sum, float* scratch, int M, int d, cudaStream_t st) {
   if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
-  const int grid = grid_for(M, 8 * 8, 148 * 2);
-#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 2 * d * sizeof(float), st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, dgamma, dbeta, M, d)
+  const int grid = dsw_layernorm_bwd_blocks(M);
+  const int want = dres_sum != nullptr && dres != nullptr;
+#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 3 * d * sizeof(float), st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, scratch, want, M, d)
   switch ((d + 255) / 256) {
     case 1: LN_BWD(1); break; case 2: LN_BWD(2); break; case 3: LN_BWD(3); break; case 4: LN_BWD(4); break;
     case 5: LN_BWD(5); break; case 6: LN_BWD(6); break; case 7: LN_BWD(7); break; default: LN_BWD(8); break;
   }
 #undef LN_BWD
+  if (cudaGetLastError() != cudaSuccess) return -3;
+  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, grid, d, dgamma, dbeta,
+                                                                  want ? dres_sum : nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -179,7 +179,6 @@ class B200Engine:
         x, ln1, mu1, rs1, actx, att, x1, ln2, mu2, rs2, h, g = saved
         Mtok = x.shape[0]
         d = x.shape[1]
-        K.colsum_accum(dx2, b.dpr_b)
         dh = K.gemm(dx2, b.pr_w, b_t=False, mode=K.EPI_DGELU, aux_in=h, status=st)
         K.gemm(dx2, g, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dpr_w,
                split_k=K.wgrad_split(d, 4 * d, Mtok), status=st)
@@ -187,8 +186,8 @@ class B200Engine:
         dln2 = K.gemm(dh, b.fc_w, b_t=False, status=st)
         K.gemm(dh, ln2, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dfc_w,
                split_k=K.wgrad_split(4 * d, d, Mtok), status=st)
-        dx1 = K.layernorm_bwd(dln2, x1, b.ln2_w, mu2, rs2, b.dln2_w, b.dln2_b, dres=dx2)
-        K.colsum_accum(dx1, b.do_b)
+        # the column sum of dx2 (bias gradient of mlp.c_proj) rides along with the LayerNorm backward
+        dx1 = K.layernorm_bwd(dln2, x1, b.ln2_w, mu2, rs2, b.dln2_w, b.dln2_b, dres=dx2, dres_sum=b.dpr_b)
         datt = K.gemm(dx1, b.o_w, b_t=False, status=st)
         K.gemm(dx1, att, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.do_w,
                split_k=K.wgrad_split(d, d, Mtok), status=st)
@@ -197,7 +196,7 @@ class B200Engine:
         dln1 = K.gemm(dqkv, b.qkv_w, b_t=False, status=st)
         K.gemm(dqkv, ln1, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dqkv_w,
                split_k=K.wgrad_split(3 * d, d, Mtok), status=st)
-        return K.layernorm_bwd(dln1, x, b.ln1_w, mu1, rs1, b.dln1_w, b.dln1_b, dres=dx1)
+        return K.layernorm_bwd(dln1, x, b.ln1_w, mu1, rs1, b.dln1_w, b.dln1_b, dres=dx1, dres_sum=b.do_b)
 
     def _body_fwd(self, input_ids, hidden, keep: bool):
         if self.is_first:

@@ -24,7 +24,8 @@ _SIGS = {
                       c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
     "dsw_layernorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "dsw_layernorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_int, c_int, c_void_p],
+                          c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "dsw_layernorm_bwd_blocks": [c_int],
     "dsw_colsum_accum": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p],
     "dsw_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "dsw_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

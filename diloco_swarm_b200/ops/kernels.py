@@ -106,17 +106,30 @@ def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Ten
     return y, mean, rstd
 
 
+_ln_scratch = {}
+
+
 def layernorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor,
-                  dgamma: torch.Tensor, dbeta: Optional[torch.Tensor], dres: Optional[torch.Tensor] = None
-                  ) -> torch.Tensor:
+                  dgamma: torch.Tensor, dbeta: Optional[torch.Tensor], dres: Optional[torch.Tensor] = None,
+                  dres_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """dx of LayerNorm plus ``dres`` (the gradient arriving on the residual
-    branch); accumulates dgamma / dbeta (fp32) in place."""
+    branch); accumulates dgamma / dbeta (fp32) in place and, when ``dres_sum``
+    is given, adds the column sum of ``dres`` to it (the bias gradient of the
+    projection whose output was added to the residual stream)."""
     M, d = x.shape
     assert dy.shape == x.shape and dy.is_contiguous() and x.is_contiguous()
     dx = torch.empty_like(x)
-    check(cuda_lib().dsw_layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
-                                       ptr(dres), dx.data_ptr(), dgamma.data_ptr(), ptr(dbeta), M, d, stream_ptr()),
-          "dsw_layernorm_bwd")
+    lib = cuda_lib()
+    nblk = lib.dsw_layernorm_bwd_blocks(M)
+    key = (x.device.index, nblk, d)
+    scratch = _ln_scratch.get(key)
+    if scratch is None:
+        # per-block partial column sums; reused by every call of this shape (same stream order)
+        scratch = torch.empty(nblk * 3 * d, dtype=F32, device=x.device)
+        _ln_scratch[key] = scratch
+    check(lib.dsw_layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                ptr(dres), dx.data_ptr(), dgamma.data_ptr(), ptr(dbeta), ptr(dres_sum),
+                                scratch.data_ptr(), M, d, stream_ptr()), "dsw_layernorm_bwd")
     return dx
 
 

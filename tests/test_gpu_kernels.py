@@ -30,7 +30,10 @@ def test_layernorm_fwd_bwd(M, d):
     dres = _bf(torch.randn(M, d, device=DEV))
     yr.backward(dy.float())
     dg, db = torch.zeros(d, device=DEV), torch.zeros(d, device=DEV)
-    dx = K.layernorm_bwd(dy, x, g, mean, rstd, dg, db, dres=dres)
+    rs = torch.ones(d, device=DEV)
+    dx = K.layernorm_bwd(dy, x, g, mean, rstd, dg, db, dres=dres, dres_sum=rs)
+    ref_rs = 1 + dres.float().sum(0)
+    assert (rs - ref_rs).abs().max() < 1e-2 * ref_rs.abs().max() + 1e-2
     ref_dx = xr.grad + dres.float()
     assert (dx.float() - ref_dx).abs().max() < 3e-2 * ref_dx.abs().max()
     assert (dg - gr.grad).abs().max() < 2e-2 * gr.grad.abs().max() + 1e-2
