@@ -201,6 +201,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
         "loss": last.loss if last else None,
+        "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
     }
     tr.world.barrier()
     tr.logger.close()

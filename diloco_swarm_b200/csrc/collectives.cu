@@ -285,3 +285,12 @@ extern "C" int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* 
   else           grad_allreduce_f32_kernel<<<blocks, 512, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+extern "C" int dsw_load_collectives() {
+  cudaFuncAttributes a;
+  int bad = 0;
+  bad |= cudaFuncGetAttributes(&a, outer_sync_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, grad_allreduce_f32_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, grad_allreduce_bf16_kernel) != cudaSuccess;
+  return bad ? -1 : 0;
+}

@@ -95,29 +95,24 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
   }
 }
 
-// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres).
-// Column sums (dgamma = sum dy*xhat, dbeta = sum dy, and optionally the column
-// sum of dres, which is the bias gradient of the linear layer that produced the
-// residual branch) are accumulated in registers per thread, combined per block
-// in shared memory and written to a scratch array partial[block][3][d]; a
-// second small kernel adds the per-block partials into the fp32 gradients.
+// LayerNorm backward in two kernels.
+// (A) row kernel: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres);
+//     one warp per row, the row stays in registers.
+// (B) column kernel: dgamma = sum_rows dy*xhat, dbeta = sum_rows dy and optionally the
+//     column sum of dres (the bias gradient of the linear layer that fed the residual
+//     branch).  A thread owns 8 columns and walks rows; the operands were just touched
+//     by (A) so most of this pass is served from L2.  Per-block partials go to a
+//     scratch array partial[row_block][3][d]; a finish kernel adds them into the fp32
+//     gradients (no atomics, deterministic order).
 template <int LN_MAX_CHUNKS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int want_res_sum, int M, int d) {
-  extern __shared__ float sh[];       // [3][d]
-  for (int i = threadIdx.x; i < 3 * d; i += blockDim.x) sh[i] = 0.f;
-  __syncthreads();
+                     __nv_bfloat16* __restrict__ dx, int M, int d) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int nch = (d + 255) / 256;
-  float ag[LN_MAX_CHUNKS][8], ab[LN_MAX_CHUNKS][8], ar[LN_MAX_CHUNKS][8];
-#pragma unroll
-  for (int c = 0; c < LN_MAX_CHUNKS; ++c)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; ar[c][j] = 0.f; }
   for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
     const long long off = (long long)row * d;
     const float mean = mean_in[row], rstd = rstd_in[row];
@@ -127,18 +122,16 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
       const int col = c * 256 + lane * 8;
       if (c < nch && col < d) {
-        float xv[8], dv[8], g[8];
-        load8(x + off + col, xv);
-        load8(dy + off + col, dv);
+        float g[8];
+        load8(x + off + col, xh[c]);
+        load8(dy + off + col, gy[c]);
         load8f(gamma + col, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[c][j] = (xv[j] - mean) * rstd;
-          gy[c][j] = dv[j] * g[j];
+          xh[c][j] = (xh[c][j] - mean) * rstd;
+          gy[c][j] *= g[j];
           s1 += gy[c][j];
           s2 += gy[c][j] * xh[c][j];
-          ag[c][j] += dv[j] * xh[c][j];
-          ab[c][j] += dv[j];
         }
       }
     }
@@ -151,29 +144,56 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
         float o[8], r[8];
         if (dres) load8(dres + off + col, r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
-          if (dres) ar[c][j] += r[j];
-        }
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
         store8(dx + off + col, o);
       }
     }
   }
+}
+
+// Block = 32 column groups of 8 columns x 8 row lanes; grid = (ceil(d/256), row blocks).
+__global__ void __launch_bounds__(256)
+layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                          const __nv_bfloat16* __restrict__ dres, float* __restrict__ partial, int M, int d) {
+  __shared__ float sh[8][256];
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + cg * 8;
+  float ag[8], ab[8], ar[8];
 #pragma unroll
-  for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
-    const int col = c * 256 + lane * 8;
-    if (c < nch && col < d) {
+  for (int j = 0; j < 8; ++j) { ag[j] = 0.f; ab[j] = 0.f; ar[j] = 0.f; }
+  if (col < d) {
+    for (int row = blockIdx.y * 8 + rl; row < M; row += gridDim.y * 8) {
+      const long long off = (long long)row * d + col;
+      const float mean = mean_in[row], rstd = rstd_in[row];
+      float xv[8], dv[8];
+      load8(x + off, xv);
+      load8(dy + off, dv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(&sh[col + j], ag[c][j]);
-        atomicAdd(&sh[d + col + j], ab[c][j]);
-        if (want_res_sum) atomicAdd(&sh[2 * d + col + j], ar[c][j]);
+      for (int j = 0; j < 8; ++j) { ag[j] += dv[j] * (xv[j] - mean) * rstd; ab[j] += dv[j]; }
+      if (dres) {
+        float r[8];
+        load8(dres + off, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ar[j] += r[j];
       }
     }
   }
-  __syncthreads();
-  float* out = partial + (long long)blockIdx.x * 3 * d;
-  for (int i = threadIdx.x; i < 3 * d; i += blockDim.x) out[i] = sh[i];
+  float* out = partial + (long long)blockIdx.y * 3 * d;
+  for (int which = 0; which < 3; ++which) {
+    const float* src = which == 0 ? ag : (which == 1 ? ab : ar);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sh[rl][cg * 8 + j] = src[j];
+    __syncthreads();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < d) {
+      float s = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) s += sh[r][threadIdx.x];
+      out[which * d + c] = s;
+    }
+  }
 }
 
 // dgamma[c] += sum_b partial[b][0][c], dbeta[c] += sum_b partial[b][1][c],
@@ -384,8 +404,8 @@ extern "C" int dsw_layernorm_fwd(const void* x, const float* gamma, const float*
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// Number of blocks dsw_layernorm_bwd launches for M rows = rows of scratch it needs.
-extern "C" int dsw_layernorm_bwd_blocks(int M) { return grid_for(M, 8 * 8, 296); }
+// Row blocks of the column pass of dsw_layernorm_bwd = rows of scratch it needs.
+extern "C" int dsw_layernorm_bwd_blocks(int M) { return M >= 8192 ? 128 : (M >= 512 ? 32 : 4); }
 
 // scratch: fp32 [dsw_layernorm_bwd_blocks(M)][3][d], contents irrelevant on entry.
 // dres_sum (optional): fp32 [d] += column sum of dres.
@@ -393,23 +413,27 @@ extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gam
                                  const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
                                  float* dres_sum, float* scratch, int M, int d, cudaStream_t st) {
   if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
-  const int grid = dsw_layernorm_bwd_blocks(M);
+  const int grid = grid_for(M, 8, 148 * 16);
   const int want = dres_sum != nullptr && dres != nullptr;
-#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 3 * d * sizeof(float), st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, scratch, want, M, d)
+#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, M, d)
   switch ((d + 255) / 256) {
     case 1: LN_BWD(1); break; case 2: LN_BWD(2); break; case 3: LN_BWD(3); break; case 4: LN_BWD(4); break;
     case 5: LN_BWD(5); break; case 6: LN_BWD(6); break; case 7: LN_BWD(7); break; default: LN_BWD(8); break;
   }
 #undef LN_BWD
   if (cudaGetLastError() != cudaSuccess) return -3;
-  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, grid, d, dgamma, dbeta,
+  const int rb = dsw_layernorm_bwd_blocks(M);
+  layernorm_bwd_cols_kernel<<<dim3((d + 255) / 256, rb), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd,
+                                                                        want ? (const bf16*)dres : nullptr, scratch, M, d);
+  if (cudaGetLastError() != cudaSuccess) return -3;
+  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, rb, d, dgamma, dbeta,
                                                                   want ? dres_sum : nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int dsw_colsum_accum(const void* x, long long ld, float* out, int M, int N, cudaStream_t st) {
   if (N % 8 || ld % 8) return -10;
-  dim3 grid((N + 255) / 256, M >= 4096 ? 64 : (M >= 256 ? 16 : 1));
+  dim3 grid((N + 255) / 256, M >= 4096 ? 128 : (M >= 256 ? 16 : 1));
   colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, ld, out, M, N);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -452,4 +476,18 @@ extern "C" int dsw_cast_f32_bf16(const float* src, void* dst, long long n, cudaS
 extern "C" int dsw_cast_bf16_f32(const void* src, float* dst, long long n, cudaStream_t st) {
   cast_bf16_f32_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)src, dst, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_load_elementwise() {
+  cudaFuncAttributes a;
+  int bad = 0;
+#define L(f) bad |= cudaFuncGetAttributes(&a, f) != cudaSuccess
+  L(layernorm_fwd_kernel<1>); L(layernorm_fwd_kernel<2>); L(layernorm_fwd_kernel<3>); L(layernorm_fwd_kernel<4>);
+  L(layernorm_fwd_kernel<5>); L(layernorm_fwd_kernel<6>); L(layernorm_fwd_kernel<7>); L(layernorm_fwd_kernel<8>);
+  L(layernorm_bwd_kernel<1>); L(layernorm_bwd_kernel<2>); L(layernorm_bwd_kernel<3>); L(layernorm_bwd_kernel<4>);
+  L(layernorm_bwd_kernel<5>); L(layernorm_bwd_kernel<6>); L(layernorm_bwd_kernel<7>); L(layernorm_bwd_kernel<8>);
+  L(layernorm_bwd_finish_kernel); L(layernorm_bwd_cols_kernel); L(colsum_kernel); L(embedding_fwd_kernel); L(embedding_bwd_kernel);
+  L(mask_count_kernel); L(cross_entropy_kernel); L(cast_f32_bf16_kernel); L(cast_bf16_f32_kernel);
+#undef L
+  return bad ? -1 : 0;
 }

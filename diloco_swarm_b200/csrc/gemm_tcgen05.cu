@@ -380,3 +380,11 @@ extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const
   if (bn == 256) return launch<256, 4>(ta, tb, g, max_ctas, stream);
   return launch<128, 6>(ta, tb, g, max_ctas, stream);
 }
+
+// Force the module that holds these kernels to load now (see dsw_load_all).
+extern "C" int dsw_load_gemm() {
+  cudaFuncAttributes a;
+  if (cudaFuncGetAttributes(&a, gemm_kernel<256, 4>) != cudaSuccess) return -1;
+  if (cudaFuncGetAttributes(&a, gemm_kernel<128, 6>) != cudaSuccess) return -1;
+  return 0;
+}

@@ -134,3 +134,13 @@ extern "C" int dsw_sgd(float* p, float* g, float* buf, void* p16, long long n, f
   sgd_kernel<<<148 * 4, 512, 0, st>>>(p, g, buf, (__nv_bfloat16*)p16, n, lr, mu, nesterov, coef, zero_grad);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+extern "C" int dsw_load_optim() {
+  cudaFuncAttributes a;
+  int bad = 0;
+  bad |= cudaFuncGetAttributes(&a, sumsq_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, clip_coef_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, adamw_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, sgd_kernel) != cudaSuccess;
+  return bad ? -1 : 0;
+}

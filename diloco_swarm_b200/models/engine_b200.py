@@ -26,7 +26,7 @@ import torch.distributed as dist
 
 from .gpt2 import GPT2Config, init_tensor, split_layers, stage_param_specs
 from ..ops import kernels as K
-from ..ops._lib import Status
+from ..ops._lib import Status, load_all_kernels
 from ..ops.attention import attention_bwd, attention_fwd
 from ..parallel.collectives import GradSync, OuterSync
 from ..parallel.symm import SymmetricBuffer
@@ -97,6 +97,7 @@ class B200Engine:
         self.stash: Dict[int, dict] = {}
         self.training = True
         self._build_views()
+        load_all_kernels()
 
     # ------------------------------------------------------------------ views
     def _slice(self, buf: torch.Tensor, key: str) -> torch.Tensor:
@@ -156,6 +157,38 @@ class B200Engine:
 
     def check_status(self) -> None:
         self.status.raise_if_set()
+
+    def warmup(self, B: int, T: int) -> None:
+        """Run every code path of a step once on dummy data of the real shape, then
+        put the state back.  Library kernels (attention, copies) are loaded on first
+        use, and a first use that happens while a pipeline receive is spinning on the
+        device can wait forever; after this pass nothing is loaded inside a step."""
+        dev, d = self.device, self.cfg.n_embd
+        theta0 = self.theta.clone()
+        ids = torch.zeros(B, T, dtype=torch.long, device=dev) if self.is_first else None
+        hidden = torch.zeros(B, T, d, dtype=BF16, device=dev) if not self.is_first else None
+        tg = torch.zeros(B, T, dtype=torch.long, device=dev)
+        mask = torch.ones(B, T, dtype=torch.long, device=dev)
+        if self.is_last:
+            self.forward_backward(-1, ids, hidden, tg, mask, 1.0)
+            self.forward_loss(ids, hidden, tg, mask, 1.0)
+        else:
+            y = self.forward(-1, ids, hidden)
+            self.backward(-1, torch.zeros_like(y))
+            self.forward(-1, ids, hidden, keep=False)
+        self.forward_infer(ids, hidden)
+        self.optimizer_step(0.0, 1.0)
+        torch.cuda.synchronize(dev)
+        self.theta.copy_(theta0)
+        K.cast_to_bf16(self.theta, self.w16)
+        for t in (self.grad, self.m, self.v, self.stats):
+            t.zero_()
+        if self.mom_inner is not None:
+            self.mom_inner.zero_()
+        self.opt_step = 0
+        self.status.word.zero_()
+        self.stash.clear()
+        torch.cuda.synchronize(dev)
 
     # ------------------------------------------------------------------ forward pieces
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:

@@ -73,6 +73,28 @@ def cuda_lib():
     return _cuda
 
 
+_loaded = False
+
+
+def load_all_kernels() -> None:
+    """Load every kernel of the library on the current device now.  A kernel's
+    first launch may otherwise wait for the device to go idle, which deadlocks
+    when a pipeline receive is already spinning there (see the package __init__)."""
+    global _loaded
+    if _loaded:
+        return
+    lib = cuda_lib()
+    for name in ("dsw_load_gemm", "dsw_load_elementwise", "dsw_load_optim", "dsw_load_collectives",
+                 "dsw_load_attention"):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.restype = c_int
+            fn.argtypes = []
+            if fn() != 0:
+                raise RuntimeError(f"{name} failed")
+    _loaded = True
+
+
 def stream_ptr(stream: Optional[torch.cuda.Stream] = None) -> int:
     return (stream or torch.cuda.current_stream()).cuda_stream
 

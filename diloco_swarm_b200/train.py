@@ -79,13 +79,15 @@ class Trainer:
         self.routing_seed = config.swarm.routing_seed if config.swarm.routing_seed is not None else tc.seed
         self.comm = PipelineComm(w, (self.mbs, self.seq, config.model.n_embd), self.engine.act_dtype,
                                  self.device, prefetch=2)
+        if hasattr(self.engine, "warmup"):
+            self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
         self.alive: Optional[List[bool]] = None
         self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
         self.num_train_steps = 0
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
         self.ckpt.setup(w)
-        self.last_step_device_ms: Optional[float] = None
+        self.last_enqueue_s: float = 0.0
 
     # ------------------------------------------------------------------
     def _plan(self, step: int, phase: int, forward_only: bool):
@@ -153,6 +155,7 @@ class Trainer:
         self.opt_steps += 1
         if do_sync and eng.has_outer:
             eng.outer_step()
+        self.last_enqueue_s = time.time() - start   # host time to queue the whole step
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
@@ -324,6 +327,11 @@ class Trainer:
 
 
 def main(config: Config) -> Dict[str, float]:
+    dump_s = float(os.environ.get("DSWARM_STACK_DUMP_S", "0"))
+    if dump_s > 0:
+        # hang diagnosis: print every thread's Python stack if the run is still going after dump_s seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(dump_s, repeat=False, file=sys.stderr)
     trainer = Trainer(config)
     w, log = trainer.world, trainer.logger
     log.log_message(f"Starting process {w.local_rank}", master=False, level=Level.INFO)

@@ -61,7 +61,11 @@ class World:
         timeout = datetime.timedelta(seconds=timeout_s)
         if not dist.is_initialized():
             kwargs: Dict[str, Any] = {}
-            if self.backend == "nccl":
+            # Binding the device up front makes NCCL create the communicators eagerly, and
+            # then send/recv of a sub-group run on that group's one stream.  Left lazy,
+            # every rank pair gets its own point-to-point communicator and stream, which
+            # is what the pipeline transport wants.
+            if self.backend == "nccl" and os.environ.get("DSWARM_NCCL_EAGER", "0") == "1":
                 kwargs["device_id"] = torch.device("cuda", self.local_rank)
             dist.init_process_group(
                 backend=self.backend, rank=self.rank, world_size=self.world_size,

@@ -1,0 +1,128 @@
+"""Unit tests of the host-side components (metrics, checkpoint, data, model split, optimiser maths)."""
+import math
+import os
+
+import pytest
+import torch
+
+from helpers import make_config, single_world
+
+
+def test_metrics_keys_and_semantics():
+    from diloco_swarm_b200.utils.metrics import Outputs, aggregate_outputs, train_metrics
+    m = train_metrics("train/global")
+    m.update(Outputs(step=1, time=2.0, loss=1.0, tokens=100, num_micro_batches=4, lr=1e-3, norm=0.5, micro_step_time=0.5))
+    m.update(Outputs(step=2, time=1.0, loss=2.0, tokens=100, num_micro_batches=4, lr=1e-3, norm=0.7, micro_step_time=0.25))
+    out = m.compute()
+    assert out["train/global/step/current"] == 2
+    assert out["train/global/throughput/current"] == 100.0 and out["train/global/throughput/average"] == 75.0
+    assert out["train/global/tokens/total"] == 200 and out["train/global/num_micro_batches/current"] == 8
+    # perplexity average = mean of per-update exp(loss), not exp(mean loss)
+    assert abs(out["train/global/perplexity/average"] - (math.e + math.e ** 2) / 2) < 1e-9
+    a = Outputs(step=3, time=1.0, loss=2.0, tokens=10, num_micro_batches=1, lr=0.1, norm=1.0, micro_step_time=0.1)
+    b = Outputs(step=3, time=3.0, loss=0.0, tokens=0, num_micro_batches=0, lr=0.1, norm=None, micro_step_time=0.3)
+    agg = aggregate_outputs(a, [a, b])
+    assert agg.tokens == 10 and agg.time == 2.0 and agg.loss == 2.0 and agg.norm == 1.0   # zeros and None are ignored
+    v = Outputs.from_vector(b.to_vector())
+    assert v.norm is None and v.tokens == 0 and v.time == 3.0
+
+
+def test_checkpoint_layout_and_roundtrip(tmp_path):
+    from diloco_swarm_b200.utils.ckpt import Checkpoint
+    ck = Checkpoint(str(tmp_path / "checkpoints"))
+    model = torch.nn.Linear(4, 3)
+    p = ck.save(7, model)
+    assert p.endswith(os.path.join("step_7", "model.pt"))
+    ck.save(12, model)
+    assert ck.get_latest_step() == 12
+    sd = ck.load(7)
+    assert torch.equal(sd["weight"], model.weight.detach())
+    with pytest.raises(ValueError):
+        ck.load(99)
+
+    class W:
+        world_size, local_rank = 4, 3
+    ck.setup(W())
+    assert ck.save(1, model).endswith(os.path.join("step_1", "model.3.pt"))
+    ck.save_extra(1, "optim", {"opt_steps": 5})
+    assert ck.load_extra(1, "optim")["opt_steps"] == 5 and ck.load_extra(1, "outer") is None
+    ck.save_meta(1, {"step": 1})
+    assert ck.load_meta(1)["step"] == 1
+
+
+def test_data_pipeline():
+    from diloco_swarm_b200.utils import data as D
+    tok = D.ByteTokenizer()
+    t = D.tokenize("I am", tok, max_length=8)
+    assert t["input_ids"].tolist() == [[73, 32, 97, 109] + [50256] * 4] and t["attention_mask"].sum() == 4
+    cfg = make_config(data={"path": "memorize", "seq_length": 16, "num_examples": 10}).data
+    ds = D.get_dataset(cfg, tok, seed=0)
+    assert len(ds) == 10 and ds.input_ids.shape == (10, 17)
+    tr, va = ds.train_test_split(0.2, seed=1)
+    assert len(tr) == 8 and len(va) == 2
+    b = D.collate(ds, 0, 4)
+    assert torch.equal(b["input_ids"][:, 1:], b["target_ids"][:, :-1]) and b["attention_mask"].shape == (4, 16)
+    z1, z2 = D.zipf_tokens(64, 33, 50257, 1.0, 0), D.zipf_tokens(64, 33, 50257, 1.0, 0)
+    assert torch.equal(z1, z2) and int(z1.max()) < 50257 and (z1 == 0).float().mean() > 0.05
+    loader = D.BatchLoader(ds, 4)
+    assert len(loader) == 2 and len(list(loader)) == 2       # drop_last
+    assert D.get_num_steps(40, 1, 1000, 10) == 40 and D.get_num_steps(-1, 2, 100, 10) == 20
+    assert D.micro_batch_rows(3, 4) == slice(12, 16)
+
+
+def test_layer_split_and_shard_equivalence():
+    from diloco_swarm_b200.models.gpt2 import GPT2Config, TorchStage, num_parameters, split_layers
+    assert split_layers(12, 2) == [list(range(6)), list(range(6, 12))]
+    assert split_layers(7, 3) == [[0, 1, 2], [3, 4], [5, 6]]            # remainder to the first stages
+    assert split_layers(12, 2, "8,4")[1] == [8, 9, 10, 11]
+    assert sum(len(x) for x in split_layers(24, 4, "balanced", 1024)) == 24
+    cfg = GPT2Config(n_layer=4, n_head=4, n_embd=64, vocab_size=256, block_size=32)
+    full = TorchStage(cfg)
+    assert full.num_parameters() == num_parameters(cfg)
+    ids = torch.randint(0, 256, (2, 16))
+    for S_ in (2, 4):
+        x = None
+        for s in range(S_):
+            st = TorchStage(cfg, s, S_)
+            x = st(input_ids=ids if s == 0 else None, hidden_states=x)
+        assert torch.allclose(x, full(input_ids=ids), atol=1e-5)
+    # stage-local block numbering in the state dict (reference checkpoint layout)
+    keys = list(TorchStage(cfg, 1, 2).state_dict().keys())
+    assert keys[0] == "transformer.h.0.ln_1.weight" and keys[-1] == "lm_head.weight"
+
+
+def test_lr_schedule_and_nesterov_reference():
+    from diloco_swarm_b200.optim import lr_factor, nesterov_reference
+    c = make_config(train={"scheduler": {"enable": True, "num_warmup_steps": 10}}).train.scheduler
+    assert lr_factor(0, c, 100) == 0.0 and lr_factor(5, c, 100) == 0.5 and lr_factor(50, c, 100) == 1.0
+    c = make_config(train={"scheduler": {"enable": True, "num_warmup_steps": 10, "type": "cosine"}}).train.scheduler
+    assert abs(lr_factor(10, c, 110) - 1.0) < 1e-9 and abs(lr_factor(110, c, 110) - 0.1) < 1e-9
+    p = torch.nn.Parameter(torch.randn(100))
+    opt = torch.optim.SGD([p], lr=0.7, momentum=0.9, nesterov=True)
+    theta, buf = p.detach().clone(), None
+    for _ in range(3):
+        g = torch.randn(100)
+        p.grad = g.clone()
+        opt.step()
+        theta, buf = nesterov_reference(theta, g, buf, 0.7, 0.9)
+    assert torch.allclose(theta, p.detach(), atol=1e-6)
+
+
+def test_torch_engine_diloco_single_replica():
+    from diloco_swarm_b200.models.engine_torch import TorchEngine
+    from diloco_swarm_b200.models.gpt2 import GPT2Config
+    cfg = make_config(train={"outer_optimizer": {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}})
+    mc = cfg.model
+    eng = TorchEngine(GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer,
+                                 n_head=mc.n_head, n_embd=mc.n_embd), single_world(), cfg, torch.device("cpu"))
+    ids = torch.randint(0, 500, (2, 17))
+    theta0 = [p.detach().clone() for p in eng.model.parameters()]
+    for _ in range(2):
+        eng.forward_backward(0, ids[:, :-1], None, ids[:, 1:], torch.ones(2, 16, dtype=torch.long), 1.0)
+        eng.optimizer_step(1e-3, 1.0)
+        eng.zero_grad()
+    inner = [p.detach().clone() for p in eng.model.parameters()]
+    eng.outer_step()
+    for p, t0, ti in zip(eng.model.parameters(), theta0, inner):
+        d = t0 - ti
+        assert torch.allclose(p.detach(), t0 - 0.7 * (d + 0.9 * d), atol=1e-6)

@@ -1,0 +1,107 @@
+import collections
+
+import numpy as np
+import pytest
+
+from diloco_swarm_b200.parallel import schedule as S
+
+
+def test_route_is_deterministic_and_respects_stages():
+    p1 = S.route(7, 3, 3, 9, 24)
+    p2 = S.route(7, 3, 3, 9, 24)
+    assert np.array_equal(p1, p2)
+    assert not np.array_equal(p1, S.route(7, 4, 3, 9, 24))        # changes with the step
+    assert not np.array_equal(p1, S.route(8, 3, 3, 9, 24))        # and with the seed
+    for s in range(3):
+        assert set(p1[:, s]) <= {r for r in range(9) if r % 3 == s}
+    # first stage: round-robin chunks as in the reference's BatchSampler
+    assert list(p1[:, 0]) == [[0, 3, 6][mb % 3] for mb in range(24)]
+
+
+def test_route_is_roughly_uniform():
+    c = collections.Counter(int(S.route(1, t, 2, 8, 32)[i, 1]) for t in range(200) for i in range(32))
+    assert set(c) == {1, 3, 5, 7}
+    assert max(c.values()) / min(c.values()) < 1.15
+
+
+def test_route_skips_dead_replicas():
+    alive = [True] * 8
+    alive[3] = alive[4] = False
+    p = S.route(1, 1, 2, 8, 64, alive)
+    assert 3 not in p and 4 not in p
+    with pytest.raises(RuntimeError):
+        S.route(1, 1, 2, 2, 4, [True, False])
+
+
+@pytest.mark.parametrize("stages,world,M,cap", [(1, 1, 4, 1), (2, 2, 8, 1), (2, 4, 16, 3), (3, 9, 30, 2), (4, 8, 32, 4)])
+def test_plan_is_complete_and_causal(stages, world, M, cap):
+    path = S.route(5, 2, stages, world, M)
+    plans = {r: S.plan(path, world, r, cap) for r in range(world)}
+    fwd_seen = collections.defaultdict(set)
+    for r, ops in plans.items():
+        st = r % stages
+        inflight = 0
+        for op in ops:
+            assert path[op.mb, st] == r
+            if op.kind == S.FWD:
+                inflight += 1
+                assert inflight <= cap or st == stages - 1
+                fwd_seen[r].add(op.mb)
+            elif op.kind == S.BWD:
+                assert op.mb in fwd_seen[r]          # backward only after its own forward
+                inflight -= 1
+            else:
+                assert st == stages - 1
+        assert inflight == 0
+    # every microbatch runs forward and backward exactly once on every stage
+    for mb in range(M):
+        for st in range(stages):
+            ops = [o for o in plans[int(path[mb, st])] if o.mb == mb]
+            kinds = sorted(o.kind for o in ops)
+            assert kinds == ([S.FWD_BWD] if st == stages - 1 else [S.FWD, S.BWD])
+
+
+def _simulate(plans, world, forward_only=False):
+    """Replay the plans with in-order point-to-point channels; returns True if every rank finishes."""
+    pos = {r: 0 for r in range(world)}
+    sent = collections.defaultdict(list)        # (src, dst, direction) -> queue of mbs
+    progressed = True
+    while progressed:
+        progressed = False
+        for r in range(world):
+            while pos[r] < len(plans[r]):
+                op = plans[r][pos[r]]
+                if op.kind in (S.FWD, S.FWD_BWD) and op.prev >= 0:
+                    q = sent[(op.prev, r, "f")]
+                    if not q or q[0] != op.mb:
+                        break
+                    q.pop(0)
+                if op.kind == S.BWD and op.next >= 0:
+                    q = sent[(op.next, r, "b")]
+                    if not q or q[0] != op.mb:
+                        break
+                    q.pop(0)
+                if op.kind == S.FWD and op.next >= 0:
+                    sent[(r, op.next, "f")].append(op.mb)
+                if op.kind in (S.BWD, S.FWD_BWD) and op.prev >= 0 and not forward_only:
+                    sent[(r, op.prev, "b")].append(op.mb)
+                pos[r] += 1
+                progressed = True
+    return all(pos[r] == len(plans[r]) for r in range(world))
+
+
+@pytest.mark.parametrize("stages,world,M,cap", [(2, 2, 8, 1), (2, 4, 32, 4), (2, 8, 32, 2), (3, 9, 27, 3), (4, 8, 32, 1)])
+def test_plans_do_not_deadlock_on_fifo_channels(stages, world, M, cap):
+    for step in range(1, 6):
+        path = S.route(11, step, stages, world, M)
+        plans = {r: S.plan(path, world, r, cap) for r in range(world)}
+        assert _simulate(plans, world)
+        fplans = {r: S.plan(path, world, r, cap, forward_only=True) for r in range(world)}
+        assert all(o.kind == S.FWD for ops in fplans.values() for o in ops)
+        assert _simulate(fplans, world, forward_only=True)
+
+
+def test_micro_batch_key_matches_reference_naming():
+    assert S.micro_batch_key(0, [0, 2]) == (0, 1)
+    assert S.micro_batch_key(1, [0, 2]) == (2, 1)
+    assert S.micro_batch_key(5, [0, 2]) == (2, 3)
