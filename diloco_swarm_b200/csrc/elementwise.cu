@@ -491,3 +491,44 @@ extern "C" int dsw_load_elementwise() {
 #undef L
   return bad ? -1 : 0;
 }
+
+// ------------------------------------------------------------------ LayerNorm backward without allocations
+// See dswarm_noalloc.h.  Same kernels as dsw_layernorm_bwd; the per-block partial
+// column sums go to a fixed array in device memory instead of a caller-provided one.
+#include "dswarm_noalloc.h"
+#include <cstdio>
+
+static __device__ __align__(256) float g_ln_noalloc_scratch[DSW_NOALLOC_LN_MAX_BLOCKS * 3 * DSW_NOALLOC_LN_MAX_D];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};   // device address of the array, per device
+}
+
+extern "C" int dsw_layernorm_bwd_noalloc(const void* dy, const void* x, const float* gamma, const float* mean,
+                                         const float* rstd, const void* dres, void* dx, float* dgamma,
+                                         float* dbeta, float* dres_sum, int M, int d, cudaStream_t st) {
+  if (M <= 0 || d <= 0 || d % 8) {
+    fprintf(stderr, "dsw_layernorm_bwd_noalloc: M=%d d=%d: d must be a positive multiple of 8\n", M, d);
+    return DSW_NOALLOC_BAD_SHAPE;
+  }
+  const int rb = dsw_layernorm_bwd_blocks(M);
+  if (d > DSW_NOALLOC_LN_MAX_D || rb > DSW_NOALLOC_LN_MAX_BLOCKS) {
+    fprintf(stderr, "dsw_layernorm_bwd_noalloc: d=%d exceeds the built-in scratch (d <= %d); use dsw_layernorm_bwd\n",
+            d, DSW_NOALLOC_LN_MAX_D);
+    return DSW_NOALLOC_TOO_LARGE;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DSW_NOALLOC_NO_DEVICE;
+  if (g_scratch_addr[dev] == nullptr) {
+    // The array's name is only a host-side handle; kernels need its address on the current device.
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_ln_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "dsw_layernorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return DSW_NOALLOC_NO_SYMBOL;
+    }
+    g_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  return dsw_layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, dres_sum, g_scratch_addr[dev], M, d, st);
+}
