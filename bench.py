@@ -52,8 +52,9 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--cap", type=int, default=4, help="max_micro_batches (in-flight microbatches per rank)")
-    ap.add_argument("--layer-split", default="even")
+    ap.add_argument("--layer-split", default="balanced")
     ap.add_argument("--collective", default="fused")
+    ap.add_argument("--routing", default="uniform", choices=["uniform", "balanced"])
     ap.add_argument("--no-outer", action="store_true", help="plain SWARM (per-step gradient all-reduce)")
     return ap.parse_args()
 
@@ -117,7 +118,7 @@ def build_config(args, S: int):
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
         swarm={"num_stages": S, "sync_every_n_steps": 1 if args.no_outer else H, "layer_split": args.layer_split,
-               "collective": args.collective},
+               "collective": args.collective, "routing": args.routing},
         eval={"enable": False}, sample={"enable": False},
         logging={"log_dir": os.path.join(tempfile.gettempdir(), "dswarm_bench"), "run_id": f"bench{os.getpid()}",
                  "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"}},
@@ -195,7 +196,7 @@ def run_ours(args) -> dict:
                    "micro_batch": args.micro_batch, "parallelism": f"{S} stages x {R} replicas",
                    "algorithm": "swarm" if args.no_outer else f"diloco-swarm H={H}",
                    "max_micro_batches": args.cap, "layer_split": args.layer_split, "collective": args.collective,
-                   "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
+                   "routing": args.routing, "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},

@@ -36,6 +36,9 @@ class SwarmConfig(BaseConfig):
     sync_every_n_steps: int = 1
     # (added) seed of the counter-based routing generator; None = train.seed
     routing_seed: Optional[int] = None
+    # (added) "uniform" = independent uniform draw per hop (reference, src/comm.py:91);
+    # "balanced" = seeded random permutation with equal shares per replica.
+    routing: Literal["uniform", "balanced"] = "uniform"
     # (added) "even" = reference split (n_layer // S, remainder to the first
     # stages); "balanced" = weigh embedding / LM head when splitting blocks;
     # or an explicit comma list such as "7,5".

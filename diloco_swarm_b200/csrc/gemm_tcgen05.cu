@@ -9,10 +9,11 @@
 // with the elementwise work fused into the epilogue (bias, exact GELU and its
 // derivative, residual add, fp32 accumulation into the main gradient).
 //
-// Structure: persistent CTAs (one per SM), 192 threads.
+// Structure: persistent CTAs (one per SM), 320 threads.
 //   warp 0      TMA producer: fills a ring of NSTAGE {A,B} k-blocks
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane)
-//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, math, stores
+//   warps 2..9  epilogue: tcgen05.ld of the finished accumulator, math, stores
+//               (two warps per TMEM lane quarter, each takes half of the columns)
 // Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap
 // the main loop of tile i+1.  No thread-block clusters and no multicast loads.
 #include <cuda.h>
@@ -26,7 +27,8 @@ namespace dsw {
 constexpr int BM = 128;
 constexpr int BK = 64;          // one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;          // two per TMEM lane quarter, each takes half of the tile's columns
+constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
 
 enum EpiMode : int {
   EPI_STORE = 0,        // out = acc (+ bias)
@@ -48,6 +50,91 @@ struct GemmArgs {
   __nv_bfloat16* aux_out; const __nv_bfloat16* aux_in; long long ldaux;
   int* status;
 };
+
+// Epilogue for one row and 32 consecutive columns of the accumulator.
+__device__ __forceinline__ void epilogue_store(const GemmArgs& g, int row, int col0, float (&v)[32]) {
+    if (g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32) {
+      float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        if (col0 + i < g.N) {
+          if (g.mode == EPI_ATOMIC_F32) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + i), "f"(v[i]), "f"(v[i + 1]),
+                         "f"(v[i + 2]), "f"(v[i + 3])
+                         : "memory");
+          } else {
+            *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          }
+        }
+      }
+      return;
+    }
+    if (g.bias) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        if (col0 + i < g.N) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
+          v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
+        }
+      }
+    }
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      if (col0 + i >= g.N) break;
+      float* w = v + i;
+      if (g.mode == EPI_GELU) {
+        uint4 pre = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]),
+                               pack_bf16(w[6], w[7]));
+        *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0 + i) = pre;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = gelu_erf(w[j]);
+      } else if (g.mode == EPI_RESID) {
+        const uint4 rr = *reinterpret_cast<const uint4*>(g.resid + (long long)row * g.ldr + col0 + i);
+        const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16(ru[j]);
+          w[2 * j] += f.x; w[2 * j + 1] += f.y;
+        }
+      } else if (g.mode == EPI_DGELU) {
+        const uint4 rr = *reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0 + i);
+        const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16(ru[j]);
+          w[2 * j] *= gelu_erf_grad(f.x); w[2 * j + 1] *= gelu_erf_grad(f.y);
+        }
+      }
+      *reinterpret_cast<uint4*>(o + i) = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]),
+                                                    pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+    }
+}
+
+// Drain NCH chunks of 32 accumulator columns for one row per thread.  The TMEM load of
+// chunk c+1 is in flight while chunk c is converted and stored.  `release` is called once,
+// right after the last load has landed, so the accumulator can be reused while the final
+// chunk is still being written out.
+template <int NCH, class Release>
+__device__ __forceinline__ void drain_accumulator(const GemmArgs& g, uint32_t t_addr, int row, bool row_ok, int col_base,
+                                                  bool has_k, Release release) {
+  uint32_t r[2][32];
+  tmem_ld_32x32(t_addr, r[0]);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    if (c + 1 < NCH) tmem_ld_32x32(t_addr + (c + 1) * 32, r[(c + 1) & 1]);
+    else release();
+    const int col0 = col_base + c * 32;
+    if (row_ok && col0 < g.N && has_k) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[c & 1][i]);
+      epilogue_store(g, row, col0, v);
+    }
+    if (c + 1 < NCH) tmem_ld_wait();
+  }
+}
 
 template <int BN, int NSTAGE>
 struct SmemLayout {
@@ -83,7 +170,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS); }
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -184,6 +271,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;       // which half of the tile's columns
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -193,86 +281,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int n0 = (rem / tiles_m) * BN;
       const int ab = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      const int kb0 = ks * kb_per_split;
-      const bool has_k = kb0 < kb_total;
+      const bool has_k = ks * kb_per_split < kb_total;
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < g.M;
-      const uint32_t t_base = tmem_base + ab * BN + (uint32_t(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_base + c0, r);
+      const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
+      drain_accumulator<BN / 64>(g, t_addr, row, row < g.M, n0 + half * (BN / 2), has_k, [&] {
         tmem_ld_wait();
-        if (c0 + 32 >= BN) {
-          // all TMEM reads of this accumulator are done: hand it back early
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[ab]);
-        }
-        const int col0 = n0 + c0;
-        if (!row_ok || col0 >= g.N || !has_k) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        if (g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32) {
-          float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col0;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (col0 + i < g.N) {
-              if (g.mode == EPI_ATOMIC_F32) {
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + i), "f"(v[i]), "f"(v[i + 1]),
-                             "f"(v[i + 2]), "f"(v[i + 3])
-                             : "memory");
-              } else {
-                *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-              }
-            }
-          }
-          continue;
-        }
-        if (g.bias) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (col0 + i < g.N) {
-              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
-              v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
-            }
-          }
-        }
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col0;
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          if (col0 + i >= g.N) break;
-          float* w = v + i;
-          if (g.mode == EPI_GELU) {
-            uint4 pre = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]),
-                                   pack_bf16(w[6], w[7]));
-            *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0 + i) = pre;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) w[j] = gelu_erf(w[j]);
-          } else if (g.mode == EPI_RESID) {
-            const uint4 rr = *reinterpret_cast<const uint4*>(g.resid + (long long)row * g.ldr + col0 + i);
-            const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16(ru[j]);
-              w[2 * j] += f.x; w[2 * j + 1] += f.y;
-            }
-          } else if (g.mode == EPI_DGELU) {
-            const uint4 rr = *reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0 + i);
-            const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16(ru[j]);
-              w[2 * j] *= gelu_erf_grad(f.x); w[2 * j + 1] *= gelu_erf_grad(f.y);
-            }
-          }
-          *reinterpret_cast<uint4*>(o + i) = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]),
-                                                        pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
-        }
-      }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      });
     }
   }
 
@@ -282,6 +301,190 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ CTA-pair variant
+// 256 x 256 output tile per cluster of two CTAs (tcgen05 cta_group::2).  Each CTA
+// loads only its half of A (128 rows) and its half of B (128 columns) per k-block,
+// 32 KB instead of the 48 KB a lone 128 x 256 CTA needs for the same FLOPs, which is
+// what matters once the main loop is bound by L2-to-shared-memory traffic.  The
+// leader CTA (cluster rank 0) issues the MMAs for both; each CTA drains its own
+// 128 rows of the accumulator from its own TMEM.
+//   full[s]      in the leader, 2 arrivals (one producer per CTA) + both CTAs' bytes
+//   empty[s]     in each CTA, released by the leader's tcgen05.commit (one per CTA)
+//   acc_full[b]  in each CTA, same mechanism
+//   acc_empty[b] in the leader, one arrival per epilogue warp of both CTAs
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGES = 6;
+struct PairSmem {
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
+  using L = PairSmem;
+  constexpr int NSTAGE = PAIR_STAGES;
+  constexpr int BN = PAIR_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + NSTAGE;
+  uint64_t* acc_full = empty_bar + NSTAGE;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (g.M + 255) / 256;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  const int kb_total = (g.K + BK - 1) / BK;
+  const int splits = g.split_k > 1 ? g.split_k : 1;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  const int num_tiles = tiles_m * tiles_n * splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * EPI_WARPS); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, 2 * BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // both CTAs' barriers exist before anyone arrives remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (one per CTA)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int ks = tile / (tiles_m * tiles_n);
+        const int rem = tile - ks * tiles_m * tiles_n;
+        const int m0 = (rem % tiles_m) * 256 + int(rank) * 128;     // this CTA's rows of A
+        const int n0 = (rem / tiles_m) * BN + int(rank) * 128;      // this CTA's columns of B
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, g.status)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[s]), 0);
+          mbar_expect_tx_cluster(full_leader, L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!g.a_mn_major) {
+            tma_load_2d_pair(sa, &tmap_a, full_leader, k0, m0);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, full_leader, m0, k0);
+            tma_load_2d_pair(sa + 8192, &tmap_a, full_leader, m0 + 64, k0);
+          }
+          if (!g.b_mn_major) {
+            tma_load_2d_pair(sb, &tmap_b, full_leader, k0, n0);
+          } else {
+            tma_load_2d_pair(sb, &tmap_b, full_leader, n0, k0);
+            tma_load_2d_pair(sb + 8192, &tmap_b, full_leader, n0 + 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc_bf16(256, BN, g.a_mn_major, g.b_mn_major);
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+        const int ks = tile / (tiles_m * tiles_n);
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(kb_total, kb0 + kb_per_split);
+        const int ab = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&acc_empty[ab], aph ^ 1, abort_flag, g.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        uint32_t accumulate = 0;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = g.a_mn_major ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                             : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = g.b_mn_major ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                             : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16_pair(d_tmem, da, db, idesc, accumulate);
+            accumulate = 1;
+          }
+          const uint32_t e = smem_u32(&empty_bar[s]);
+          umma_commit_pair(map_to_cta(e, 0));
+          umma_commit_pair(map_to_cta(e, 1));
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&acc_full[ab]);
+          umma_commit_pair(map_to_cta(f, 0));
+          umma_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+      const int ks = tile / (tiles_m * tiles_n);
+      const int rem = tile - ks * tiles_m * tiles_n;
+      const int m0 = (rem % tiles_m) * 256 + int(rank) * 128;
+      const int n0 = (rem / tiles_m) * BN;
+      const int ab = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      const bool has_k = ks * kb_per_split < kb_total;
+      if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
+      drain_accumulator<BN / 64>(g, t_addr, row, row < g.M, n0 + half * (BN / 2), has_k, [&] {
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
+      });
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // the peer may still be arriving on this CTA's barriers until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * BN);
   }
 }
 
@@ -337,6 +540,23 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int max_ctas, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) !=
+        cudaSuccess)
+      return -2;
+    attr_set = true;
+  }
+  const int tiles = ((g.M + 255) / 256) * ((g.N + PAIR_BN - 1) / PAIR_BN) * (g.split_k > 1 ? g.split_k : 1);
+  int pairs = g_num_sms / 2;
+  if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (pairs > tiles) pairs = tiles;
+  gemm_pair_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, st>>>(ta, tb, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 }  // namespace dsw
 
 using namespace dsw;
@@ -354,7 +574,7 @@ extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const
   if ((lda | ldb | ldo) % 8 || N % 8 || (a_mn_major ? M % 8 : K % 8) || (b_mn_major ? N % 8 : K % 8)) return -10;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
     return -11;
-  if (bn != 128 && bn != 256) return -12;
+  if (bn != 128 && bn != 256 && bn != 512) return -12;   // 512 = CTA-pair kernel (256 x 256 per cluster)
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -365,7 +585,7 @@ extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const
   if (!a_mn_major) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
   else             rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK);
   if (rc) return rc;
-  if (!b_mn_major) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
+  if (!b_mn_major) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn == 512 ? 128 : bn);
   else             rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
   GemmArgs g;
@@ -377,6 +597,7 @@ extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const
   g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
   g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in); g.ldaux = ldaux;
   g.status = status;
+  if (bn == 512) return launch_pair(ta, tb, g, max_ctas, stream);
   if (bn == 256) return launch<256, 4>(ta, tb, g, max_ctas, stream);
   return launch<128, 6>(ta, tb, g, max_ctas, stream);
 }
@@ -386,5 +607,6 @@ extern "C" int dsw_load_gemm() {
   cudaFuncAttributes a;
   if (cudaFuncGetAttributes(&a, gemm_kernel<256, 4>) != cudaSuccess) return -1;
   if (cudaFuncGetAttributes(&a, gemm_kernel<128, 6>) != cudaSuccess) return -1;
+  if (cudaFuncGetAttributes(&a, gemm_pair_kernel) != cudaSuccess) return -1;
   return 0;
 }

@@ -84,8 +84,12 @@ extern "C" {
 // (round-robin chunks, src/sampler.py:35-38); every later hop is a uniform
 // draw over the live replicas of the next stage.
 // Returns 0, or -1 if some stage has no live replica.
+// mode 0: every hop is an independent uniform draw (the reference's behaviour).
+// mode 1: balanced: per stage, a seeded random permutation of an evenly filled
+//         assignment, so every live replica serves floor or ceil of M/R microbatches
+//         while each microbatch's replica is still uniformly distributed.
 int dsw_route(uint64_t seed, uint64_t step, int S, int world, int M,
-              const uint8_t* alive, int32_t* path) {
+              const uint8_t* alive, int mode, int32_t* path) {
   std::vector<std::vector<int>> live(S);
   for (int r = 0; r < world; ++r)
     if (!alive || alive[r]) live[r % S].push_back(r);
@@ -93,9 +97,25 @@ int dsw_route(uint64_t seed, uint64_t step, int S, int world, int M,
     if (live[s].empty()) return -1;
   for (int mb = 0; mb < M; ++mb) {
     path[mb * S + 0] = live[0][mb % int(live[0].size())];
+    if (mode == 0) {
+      for (int s = 1; s < S; ++s) {
+        const uint32_t u = Philox::draw(seed, step, uint32_t(mb), uint32_t(s - 1));
+        path[mb * S + s] = live[s][u % uint32_t(live[s].size())];
+      }
+    }
+  }
+  if (mode == 1) {
+    std::vector<int> slot(M);
     for (int s = 1; s < S; ++s) {
-      const uint32_t u = Philox::draw(seed, step, uint32_t(mb), uint32_t(s - 1));
-      path[mb * S + s] = live[s][u % uint32_t(live[s].size())];
+      const int L = int(live[s].size());
+      for (int mb = 0; mb < M; ++mb) slot[mb] = mb % L;
+      for (int i = M - 1; i > 0; --i) {        // Fisher-Yates with counter-based draws
+        const uint32_t u = Philox::draw(seed ^ 0x5bd1e995u, step, uint32_t(i), uint32_t(s - 1));
+        std::swap(slot[i], slot[u % uint32_t(i + 1)]);
+      }
+      // a random rotation removes the bias of "mb % L" when L does not divide M
+      const uint32_t rot = Philox::draw(seed ^ 0x5bd1e995u, step, 0xffffffffu, uint32_t(s - 1));
+      for (int mb = 0; mb < M; ++mb) path[mb * S + s] = live[s][(slot[mb] + rot) % uint32_t(L)];
     }
   }
   return 0;

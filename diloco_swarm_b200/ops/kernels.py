@@ -7,6 +7,7 @@ its outputs.  The docstrings name the reference call site each one replaces.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -20,15 +21,31 @@ EPI_STORE, EPI_GELU, EPI_RESID, EPI_DGELU, EPI_ATOMIC_F32, EPI_STORE_F32 = range
 _NUM_SMS = 148
 
 
+_USE_PAIR = os.environ.get("DSWARM_GEMM_PAIR", "1") != "0"
+
+
+def _efficiency(M: int, N: int, splits: int, bm: int, bn: int, units: int) -> float:
+    """Fraction of the machine busy with real tiles when the grid runs in whole waves."""
+    tiles = math.ceil(M / bm) * math.ceil(N / bn) * splits
+    waves = math.ceil(tiles / units)
+    useful = (M * N) / (math.ceil(M / bm) * bm * math.ceil(N / bn) * bn)
+    return useful * tiles / (waves * units)
+
+
 def _pick_bn(M: int, N: int, splits: int = 1) -> int:
-    """Tile width: 256 unless the narrower tile fills the SMs clearly better."""
-    def waves(bn):
-        tiles = math.ceil(M / 128) * math.ceil(N / bn) * splits
-        w = math.ceil(tiles / _NUM_SMS)
-        return tiles / (w * _NUM_SMS)          # fraction of SM-time doing work
+    """Tile choice: 512 = 256x256 on a CTA pair (least operand traffic per FLOP),
+    256 = 128x256 on one CTA, 128 = 128x128.  A wider tile wins unless a
+    narrower one fills the SMs clearly better."""
     if N <= 128:
         return 128
-    return 256 if waves(256) >= waves(128) * 0.93 else 128
+    e128 = _efficiency(M, N, splits, 128, 128, _NUM_SMS)
+    e256 = _efficiency(M, N, splits, 128, 256, _NUM_SMS)
+    best = 256 if e256 >= e128 * 0.93 else 128
+    if _USE_PAIR and M >= 256 and N <= 8192:      # measured: the pair wins up to MLP widths, not on the LM head
+        epair = _efficiency(M, N, splits, 256, 256, _NUM_SMS // 2)
+        if epair >= max(e128 * 0.8, e256 * 0.9):
+            best = 512
+    return best
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = True, mode: int = EPI_STORE,
@@ -85,12 +102,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Tru
 
 
 def wgrad_split(M: int, N: int, K: int) -> int:
-    """Split-K factor for dW[M,N] = dy^T x with K = tokens: enough splits to
-    give every SM a tile."""
-    tiles = math.ceil(M / 128) * math.ceil(N / 256)
-    if tiles >= _NUM_SMS:
+    """Split-K factor for dW[M,N] = dy^T x with K = tokens: the weight gradients
+    of a block have few output tiles, so K is split until the SMs are full."""
+    bm, units = (256, _NUM_SMS // 2) if (_USE_PAIR and M >= 256) else (128, _NUM_SMS)
+    tiles = math.ceil(M / bm) * math.ceil(N / 256)
+    if tiles >= 4 * units:
         return 1
-    return max(1, min(_NUM_SMS // tiles, math.ceil(K / 64) // 4))
+    kb = math.ceil(K / 64)
+    best, best_eff = 1, 0.0
+    for s in range(1, 17):
+        if kb // s < 4:
+            break
+        waves = math.ceil(tiles * s / units)
+        eff = tiles * s / (waves * units) - 0.01 * (s - 1)      # small price per extra split (atomics)
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best
 
 
 def layernorm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float = 1e-5

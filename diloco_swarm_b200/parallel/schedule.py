@@ -25,7 +25,7 @@ def _host():
         lib = ctypes.CDLL(_build.build_host())
         lib.dsw_route.restype = ctypes.c_int
         lib.dsw_route.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
-                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.dsw_plan.restype = ctypes.c_int
         lib.dsw_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
@@ -42,16 +42,24 @@ class Op:
     next: int        # rank that serves it one stage later, or -1
 
 
+ROUTING_MODES = {"uniform": 0, "balanced": 1}
+
+
 def route(seed: int, step: int, num_stages: int, world_size: int, num_micro_batches: int,
-          alive: Optional[Sequence[bool]] = None) -> np.ndarray:
-    """``path[mb, s]`` = rank serving microbatch ``mb`` at stage ``s``."""
+          alive: Optional[Sequence[bool]] = None, mode: str = "uniform") -> np.ndarray:
+    """``path[mb, s]`` = rank serving microbatch ``mb`` at stage ``s``.
+
+    ``uniform``: every hop is an independent uniform draw, as the reference's
+    ``random.choice``.  ``balanced``: a seeded random permutation of an evenly
+    filled assignment per stage; the replica of any one microbatch is still
+    uniform, but replicas serve equal shares, so no replica is the straggler."""
     path = np.empty((num_micro_batches, num_stages), dtype=np.int32)
     a = None
     if alive is not None:
         a = np.ascontiguousarray(np.asarray(alive, dtype=np.uint8))
         assert a.shape == (world_size,)
     rc = _host().dsw_route(seed & (2**64 - 1), step, num_stages, world_size, num_micro_batches,
-                           a.ctypes.data if a is not None else None, path.ctypes.data)
+                           a.ctypes.data if a is not None else None, ROUTING_MODES[mode], path.ctypes.data)
     if rc != 0:
         raise RuntimeError("routing failed: a stage has no live replica")
     return path

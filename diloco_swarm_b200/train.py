@@ -94,7 +94,7 @@ class Trainer:
         w = self.world
         # phase separates the routing streams of train / eval / test steps
         path = schedule.route(self.routing_seed + 7919 * phase, step, w.num_stages, w.world_size,
-                              self.num_micro, self.alive)
+                              self.num_micro, self.alive, mode=self.config.swarm.routing)
         cap = self.config.train.max_micro_batches
         return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
 

@@ -21,7 +21,7 @@ SHAPES = [(128, 256, 64), (256, 512, 768), (200, 264, 200), (1024, 768, 3072), (
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 def test_gemm_nt(M, N, K, bn):
     from diloco_swarm_b200.ops import kernels as Kn
     from diloco_swarm_b200.ops._lib import Status
@@ -40,10 +40,11 @@ def test_gemm_nn_dgrad(M, N, K):
     from diloco_swarm_b200.ops._lib import Status
     st = Status(torch.device("cuda"))
     a, b = _mk((M, K), seed=3), _mk((K, N), seed=4)
-    out = Kn.gemm(a, b, b_t=False, status=st)
-    torch.cuda.synchronize()
-    st.raise_if_set()
-    _close(out, a.float() @ b.float(), f"NN {M}x{N}x{K}")
+    for bn in (256, 512):
+        out = Kn.gemm(a, b, b_t=False, bn=bn, status=st)
+        torch.cuda.synchronize()
+        st.raise_if_set()
+        _close(out, a.float() @ b.float(), f"NN {M}x{N}x{K} bn{bn}")
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES[:-1] + [(136, 136, 72)])
@@ -55,11 +56,12 @@ def test_gemm_tn_wgrad(M, N, K, split):
     st = Status(torch.device("cuda"))
     a, b = _mk((K, M), seed=5), _mk((K, N), seed=6)
     base = torch.randn(M, N, device="cuda")
-    out = base.clone()
-    Kn.gemm(a, b, a_t=True, b_t=False, mode=Kn.EPI_ATOMIC_F32, out=out, split_k=split, status=st)
-    torch.cuda.synchronize()
-    st.raise_if_set()
-    _close(out, base + a.float().t() @ b.float(), f"TN {M}x{N}x{K} split{split}")
+    for bn in (256, 512):
+        out = base.clone()
+        Kn.gemm(a, b, a_t=True, b_t=False, mode=Kn.EPI_ATOMIC_F32, out=out, split_k=split, bn=bn, status=st)
+        torch.cuda.synchronize()
+        st.raise_if_set()
+        _close(out, base + a.float().t() @ b.float(), f"TN {M}x{N}x{K} split{split} bn{bn}")
 
 
 def test_gemm_epilogues():
@@ -91,5 +93,6 @@ def test_gemm_persistent_many_tiles():
     from diloco_swarm_b200.ops import kernels as Kn
     M, N, K = 4096, 2304, 768
     a, b = _mk((M, K), seed=11), _mk((N, K), 0.05, seed=12)
-    _close(Kn.gemm(a, b), a.float() @ b.float().t(), "persistent")
-    _close(Kn.gemm(a, b, max_ctas=7), a.float() @ b.float().t(), "persistent capped grid")
+    for bn in (256, 512):
+        _close(Kn.gemm(a, b, bn=bn), a.float() @ b.float().t(), f"persistent bn{bn}")
+        _close(Kn.gemm(a, b, bn=bn, max_ctas=7), a.float() @ b.float().t(), f"persistent capped grid bn{bn}")

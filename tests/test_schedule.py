@@ -105,3 +105,17 @@ def test_micro_batch_key_matches_reference_naming():
     assert S.micro_batch_key(0, [0, 2]) == (0, 1)
     assert S.micro_batch_key(1, [0, 2]) == (2, 1)
     assert S.micro_batch_key(5, [0, 2]) == (2, 3)
+
+
+def test_balanced_routing_gives_equal_shares_and_uniform_marginals():
+    counts = collections.Counter()
+    for step in range(300):
+        p = S.route(9, step, 2, 8, 32, mode="balanced")
+        per = collections.Counter(p[:, 1].tolist())
+        assert set(per.values()) == {8}                       # 32 microbatches over 4 replicas
+        counts[int(p[5, 1])] += 1
+    assert max(counts.values()) / min(counts.values()) < 1.6   # one microbatch still lands anywhere
+    p = S.route(9, 1, 3, 9, 10, mode="balanced")               # 10 over 3: shares differ by at most one
+    for s in (1, 2):
+        v = collections.Counter(p[:, s].tolist()).values()
+        assert max(v) - min(v) <= 1
