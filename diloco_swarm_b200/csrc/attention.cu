@@ -1,0 +1,597 @@
+// Causal flash attention forward on tcgen05 tensor cores, head size 64.
+//
+// Replaces the reference's F.scaled_dot_product_attention(q, k, v, is_causal=True)
+// (src/model.py:66-67).  Input is the packed [B*T, 3*d] output of the QKV
+// projection (Q | K | V, head h at columns h*64 of each part); output is the
+// [B*T, d] tensor that feeds the output projection, plus the per-row log-sum-exp
+// that the backward pass needs.
+//
+// One CTA per (128 query rows, batch, head).  Warps 0-3 own one query row per
+// thread: they read the score row from tensor memory, do the online softmax and
+// keep the output row (64 fp32) in registers.  Warp 4 issues the MMAs, warp 5
+// the TMA loads.
+//   S = Q K_j^T          A = Q  [128 x 64]  K-major,  B = K_j [128 x 64] K-major   -> TMEM, 128 columns
+//   O_j = P V_j          A = P  [128 x 128] K-major (written by the softmax warps
+//                        in the 128-byte-swizzled layout),  B = V_j [128 x 64] N-major -> TMEM, 64 columns
+// K/V tiles are double buffered; two CTAs fit on an SM (112 KB shared memory,
+// 256 TMEM columns each), so one CTA's MMAs run under the other's softmax.
+// Only kv tiles up to the diagonal are visited; the diagonal tile is masked.
+#include <cuda.h>
+#include "ptx.cuh"
+#include "dswarm.h"
+
+namespace dsw {
+
+int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld,
+                      int box_inner, int box_outer);
+
+constexpr int ATT_BQ = 128;        // query rows per CTA
+constexpr int ATT_BK = 128;        // kv rows per step
+constexpr int ATT_HS = 64;
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_TILE_BYTES = 128 * 64 * 2;     // one [128 x 64] bf16 tile
+
+struct AttSmem {
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = Q_OFF + ATT_TILE_BYTES;            // 2 stages
+  static constexpr int V_OFF = K_OFF + 2 * ATT_TILE_BYTES;        // 2 stages
+  static constexpr int P_OFF = V_OFF + 2 * ATT_TILE_BYTES;        // [2 k-blocks][128 rows][64]
+  static constexpr int BAR_OFF = P_OFF + 2 * ATT_TILE_BYTES;
+  // Two CTAs share an SM only if each stays under (227 KB - 2 KB) / 2 = 115200 bytes, so
+  // there is no room for alignment slack: the dynamic segment is declared 1024-aligned
+  // and the kernel checks that it really is.
+  static constexpr int TOTAL = BAR_OFF + 128;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// byte offset of element (row, col) of a [128 x 128] bf16 operand stored as two
+// 64-column k-blocks in the 128-byte-swizzled K-major layout
+__device__ __forceinline__ uint32_t p_offset(int row, int col) {
+  const int kb = col >> 6, c = col & 63;
+  return kb * ATT_TILE_BYTES + row * 128 + ((((c >> 3) ^ (row & 7)) << 4) | ((c & 7) << 1));
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
+                     float* __restrict__ lse_out, int T, int nh, float scale_log2, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023) {            // swizzled operand tiles need 1024-byte alignment
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARG);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR_OFF);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;        // S ready in TMEM
+  uint64_t* p_full = bars + 6;        // P written to smem, S consumed (4 warps arrive)
+  uint64_t* o_full = bars + 7;        // O_j ready in TMEM
+  uint64_t* o_free = bars + 8;        // O_j consumed (4 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi = gridDim.x - 1 - blockIdx.x;          // heavy (late) query tiles first
+  const int bh = blockIdx.y;
+  const int b = bh / nh, h = bh - b * nh;
+  const int d = nh * ATT_HS;
+  const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
+  const int n_kv = qi + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_free, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_holder, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;            // 128 columns
+  const uint32_t tmem_o = tmem_base + 128;      // 64 columns
+
+  if (warp == 5) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_qkv);
+      mbar_expect_tx(q_full, ATT_TILE_BYTES);
+      tma_load_2d(smem + AttSmem::Q_OFF, &tmap_qkv, q_full, h * ATT_HS, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status)) break;
+        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+        const int kvrow = b * T + j * ATT_BK;
+        tma_load_2d(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], d + h * ATT_HS, kvrow);
+        tma_load_2d(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], 2 * d + h * ATT_HS, kvrow);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
+      const uint32_t sq = smem_u32(smem + AttSmem::Q_OFF);
+      const uint32_t sp = smem_u32(smem + AttSmem::P_OFF);
+      bool ok = mbar_wait(q_full, 0, abort_flag, status);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const uint32_t sk = smem_u32(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES);
+        const uint32_t sv = smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES);
+        if (!mbar_wait(&kv_full[s], ph, abort_flag, status)) { ok = false; break; }
+        // S may be overwritten once the softmax warps have consumed the previous one (p_full of j-1)
+        if (j > 0 && !mbar_wait(p_full, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < ATT_HS / 16; ++k)
+          umma_bf16(tmem_s, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s,
+                    k > 0);
+        umma_commit(s_full);
+        // P_j V_j once the softmax warps have written P_j (and have drained O_{j-1})
+        if (!mbar_wait(p_full, j & 1, abort_flag, status)) { ok = false; break; }
+        if (j > 0 && !mbar_wait(o_free, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < ATT_BK / 16; ++k)
+          umma_bf16(tmem_o, make_smem_desc(sp + (k >> 2) * ATT_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(sv + k * 2048, ATT_TILE_BYTES, 1024), idesc_o, k > 0);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + output (thread = query row)
+    const int r = warp * 32 + lane;                      // row within the tile = TMEM lane
+    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+    float o[ATT_HS];
+#pragma unroll
+    for (int i = 0; i < ATT_HS; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    uint8_t* sp = smem + AttSmem::P_OFF;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!mbar_wait(s_full, j & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = j == qi;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+      {
+        uint32_t v[2][32];
+        tmem_ld_32x32(tmem_s + lane_addr, v[0]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {                 // next chunk's load is in flight during the max
+          if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = __uint_as_float(v[c & 1][i]);
+            if (!diag || c * 32 + i <= r) mx = fmaxf(mx, x);
+          }
+          if (c + 1 < 4) tmem_ld_wait();
+        }
+      }
+      const float m_new = fmaxf(m, mx * scale_log2);
+      const float alpha = fast_exp2(m - m_new);               // 0 on the first tile (m = -inf)
+      // the previous P V product has to be folded in before P is overwritten
+      if (j > 0) {
+        if (!mbar_wait(o_full, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free);
+      }
+#pragma unroll
+      for (int i = 0; i < ATT_HS; ++i) o[i] *= alpha;
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+      float sum = 0.f;
+      {
+        uint32_t v[2][32];
+        tmem_ld_32x32(tmem_s + lane_addr, v[0]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
+          float p[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = __uint_as_float(v[c & 1][i]);
+            p[i] = (!diag || c * 32 + i <= r) ? fast_exp2(x * scale_log2 - m_new) : 0.f;
+            sum += p[i];
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            const uint4 w = make_uint4(pack_bf16(p[i], p[i + 1]), pack_bf16(p[i + 2], p[i + 3]),
+                                       pack_bf16(p[i + 4], p[i + 5]), pack_bf16(p[i + 6], p[i + 7]));
+            *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + i)) = w;
+          }
+          if (c + 1 < 4) tmem_ld_wait();
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, status)) {
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_o + lane_addr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
+      }
+      const float inv = 1.f / l;
+      __nv_bfloat16* dst = out + (long long)(row0 + r) * d + h * ATT_HS;
+#pragma unroll
+      for (int i = 0; i < ATT_HS; i += 8)
+        *reinterpret_cast<uint4*>(dst + i) =
+            make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
+                       pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+      // natural-log LSE of the scaled scores
+      lse_out[(long long)bh * T + qi * ATT_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+
+// ------------------------------------------------------------------ backward
+// One CTA per (128 kv rows, batch, head); it walks the query tiles i >= j (causal).
+// Per query tile, with thread = query row for the softmax algebra:
+//   S  = Q_i K_j^T,  dP = dO_i V_j^T                         -> TMEM (2 x 128 columns)
+//   P  = exp(S*scale - lse),  dS = P * (dP - D) * scale      -> shared memory, bf16, swizzled
+//   dV += P^T dO_i,  dK += dS^T Q_i   (accumulate in TMEM over i),  dQ_i = dS K_j (fresh)
+// The P / dS tiles are written once and read through two descriptors: K-major
+// (rows = queries) for dQ, and M-major (rows of the transposed operand = kv) for dV / dK;
+// the [128 x 64] Q_i, dO_i, K_j tiles likewise serve as K-major A and as N-major B.
+// dQ is accumulated across kv tiles with fp32 reductions into a scratch tensor
+// and converted to bf16 afterwards; dK and dV are written directly.
+struct AttBwdSmem {
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = K_OFF + ATT_TILE_BYTES;
+  static constexpr int Q_OFF = V_OFF + ATT_TILE_BYTES;              // 2 stages
+  static constexpr int DO_OFF = Q_OFF + 2 * ATT_TILE_BYTES;         // 2 stages
+  static constexpr int P_OFF = DO_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
+  static constexpr int DS_OFF = P_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
+  static constexpr int BAR_OFF = DS_OFF + 2 * ATT_TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
+};
+
+// D[bh, t] = sum_c dO[t, h*64 + c] * O[t, h*64 + c]; one warp per (row, head)
+__global__ void __launch_bounds__(256)
+attention_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                          float* __restrict__ D, int B, int T, int nh) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int total = B * T * nh;
+  if (gw >= total) return;
+  const int row = gw / nh, h = gw - row * nh;
+  const long long off = (long long)row * nh * ATT_HS + h * ATT_HS + lane * 2;
+  const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(out + off));
+  const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + off));
+  float v = a.x * g.x + a.y * g.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) {
+    const int b = row / T, t = row - b * T;
+    D[((long long)b * nh + h) * T + t] = v;
+  }
+}
+
+// dqkv[:, 0:d] = bf16(dq_acc)
+__global__ void __launch_bounds__(256)
+attention_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, long long rows, int d) {
+  const int per_row = d / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / per_row;
+    const int col = int(i - row * per_row) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(dq_acc + row * d + col);
+    const float4 b = *reinterpret_cast<const float4*>(dq_acc + row * d + col + 4);
+    *reinterpret_cast<uint4*>(dqkv + row * 3 * d + col) =
+        make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  }
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                     const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
+                     float* __restrict__ dq_acc, int T, int nh, float scale, int* status) {
+  using L = AttBwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;            // 1
+  uint64_t* q_full = bars + 1;         // 2
+  uint64_t* q_empty = bars + 3;        // 2
+  uint64_t* sdp_full = bars + 5;       // S and dP ready
+  uint64_t* pds_full = bars + 6;       // P and dS in shared memory (4 warps arrive)
+  uint64_t* dq_full = bars + 7;        // dV/dK/dQ MMAs of this step done
+  uint64_t* dq_free = bars + 8;        // dQ drained (4 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x;                      // kv tile; tile 0 has the most query tiles and starts first
+  const int bh = blockIdx.y;
+  const int b = bh / nh, h = bh - b * nh;
+  const int d = nh * ATT_HS;
+  const int nq = T / ATT_BQ;
+  const int steps = nq - j;
+  const float scale_log2 = scale * 1.4426950408889634f;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(sdp_full, 1); mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_free, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 320,
+                 tm_dq = tmem_base + 384;
+
+  if (warp == 5) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_qkv);
+      tma_prefetch_desc(&tmap_do);
+      const int kvrow = b * T + j * ATT_BK;
+      mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
+      tma_load_2d(smem + L::K_OFF, &tmap_qkv, kv_full, d + h * ATT_HS, kvrow);
+      tma_load_2d(smem + L::V_OFF, &tmap_qkv, kv_full, 2 * d + h * ATT_HS, kvrow);
+      for (int it = 0; it < steps; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, status)) break;
+        mbar_expect_tx(&q_full[s], 2 * ATT_TILE_BYTES);
+        const int qrow = b * T + (j + it) * ATT_BQ;
+        tma_load_2d(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], h * ATT_HS, qrow);
+        tma_load_2d(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], h * ATT_HS, qrow);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);      // Q K^T and dO V^T
+      const uint32_t id_t = make_idesc_bf16(128, 64, 1, 1);       // P^T dO and dS^T Q : A M-major, B N-major
+      const uint32_t id_q = make_idesc_bf16(128, 64, 0, 1);       // dS K : A K-major, B N-major
+      const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
+      const uint32_t sp = smem_u32(smem + L::P_OFF), sds = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, status);
+      for (int it = 0; it < steps && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
+        const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
+        if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tm_s, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), id_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tm_dp, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), id_s, k > 0);
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, it & 1, abort_flag, status)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
+          umma_bf16(tm_dv, make_smem_desc(sp + k * 2048, ATT_TILE_BYTES, 1024),
+                    make_smem_desc(sdo + k * 2048, ATT_TILE_BYTES, 1024), id_t, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
+          umma_bf16(tm_dk, make_smem_desc(sds + k * 2048, ATT_TILE_BYTES, 1024),
+                    make_smem_desc(sq + k * 2048, ATT_TILE_BYTES, 1024), id_t, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
+          umma_bf16(tm_dq, make_smem_desc(sds + (k >> 2) * ATT_TILE_BYTES + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(sk + k * 2048, ATT_TILE_BYTES, 1024), id_q, k > 0);
+        umma_commit(dq_full);
+        umma_commit(&q_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ row threads
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+    uint8_t* sp = smem + L::P_OFF;
+    uint8_t* sds = smem + L::DS_OFF;
+    bool ok = true;
+    auto drain_dq = [&](int it) -> bool {
+      if (!mbar_wait(dq_full, it & 1, abort_flag, status)) return false;
+      tc_fence_after();
+      float* dst = dq_acc + (long long)(b * T + (j + it) * ATT_BQ + r) * d + h * ATT_HS;
+#pragma unroll
+      for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dq + lane_addr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c0 + i), "f"(__uint_as_float(v[i])),
+                       "f"(__uint_as_float(v[i + 1])), "f"(__uint_as_float(v[i + 2])), "f"(__uint_as_float(v[i + 3]))
+                       : "memory");
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+      return true;
+    };
+    for (int it = 0; it < steps && ok; ++it) {
+      const int i = j + it;
+      const long long stat = (long long)bh * T + i * ATT_BQ + r;
+      const float lse2 = lse[stat] * 1.4426950408889634f;
+      const float Dr = Dvec[stat];
+      // the previous step's MMAs must be done with P / dS before they are overwritten
+      if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = it == 0;
+      uint32_t sv_[2][32], dpv[2][32];
+      tmem_ld_32x32(tm_s + lane_addr, sv_[0]);
+      tmem_ld_32x32(tm_dp + lane_addr, dpv[0]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c0 = cc * 32;
+        if (cc + 1 < 4) {
+          tmem_ld_32x32(tm_s + lane_addr + c0 + 32, sv_[(cc + 1) & 1]);
+          tmem_ld_32x32(tm_dp + lane_addr + c0 + 32, dpv[(cc + 1) & 1]);
+        }
+        float p[32], ds[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const bool keep = !diag || c0 + c <= r;
+          p[c] = keep ? fast_exp2(__uint_as_float(sv_[cc & 1][c]) * scale_log2 - lse2) : 0.f;
+          ds[c] = p[c] * (__uint_as_float(dpv[cc & 1][c]) - Dr) * scale;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          const uint32_t off = p_offset(r, c0 + c);
+          *reinterpret_cast<uint4*>(sp + off) = make_uint4(pack_bf16(p[c], p[c + 1]), pack_bf16(p[c + 2], p[c + 3]),
+                                                            pack_bf16(p[c + 4], p[c + 5]), pack_bf16(p[c + 6], p[c + 7]));
+          *reinterpret_cast<uint4*>(sds + off) = make_uint4(pack_bf16(ds[c], ds[c + 1]), pack_bf16(ds[c + 2], ds[c + 3]),
+                                                             pack_bf16(ds[c + 4], ds[c + 5]), pack_bf16(ds[c + 6], ds[c + 7]));
+        }
+        if (cc + 1 < 4) tmem_ld_wait();
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    if (ok && drain_dq(steps - 1)) {
+      // dV and dK rows of this kv tile (TMEM lane = kv row)
+      __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * ATT_HS;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = which == 0 ? tm_dk : tm_dv;
+        __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d);
+#pragma unroll
+        for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(src + lane_addr + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; c += 8)
+            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(
+                pack_bf16(__uint_as_float(v[c]), __uint_as_float(v[c + 1])),
+                pack_bf16(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])),
+                pack_bf16(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5])),
+                pack_bf16(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7])));
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace dsw
+
+using namespace dsw;
+
+// qkv: bf16 [B*T, 3*nh*64]; out: bf16 [B*T, nh*64]; lse: fp32 [B*nh*T].
+// Requires hs == 64 and T a multiple of 128.
+extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int nh, int hs, float scale,
+                                 int* status, cudaStream_t st) {
+  if (hs != ATT_HS || T % ATT_BQ != 0) return -10;
+  const int d = nh * hs;
+  CUtensorMap tm;
+  int rc = make_tmap_bf16_2d(&tm, qkv, 3LL * d, (long long)B * T, 3LL * d, 64, 128);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL) !=
+        cudaSuccess)
+      return -2;
+    attr_set = true;
+  }
+  dim3 grid(T / ATT_BQ, B * nh);
+  attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh,
+                                                                   scale * 1.4426950408889634f, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// qkv, out, dout as in the forward; lse from the forward.  dqkv: bf16 [B*T, 3*d] (all of it is written).
+// dq_acc: fp32 scratch [B*T, d]; Dvec: fp32 scratch [B*nh*T].  Both are overwritten.
+extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                                 float* dq_acc, float* Dvec, int B, int T, int nh, int hs, float scale, int* status,
+                                 cudaStream_t st) {
+  if (hs != ATT_HS || T % ATT_BQ != 0) return -10;
+  const int d = nh * hs;
+  CUtensorMap tq, tdo;
+  int rc = make_tmap_bf16_2d(&tq, qkv, 3LL * d, (long long)B * T, 3LL * d, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tdo, dout, d, (long long)B * T, d, 64, 128);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttBwdSmem::TOTAL) !=
+        cudaSuccess)
+      return -2;
+    attr_set = true;
+  }
+  if (cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * T * d, st) != cudaSuccess) return -4;
+  const long long warps = (long long)B * T * nh;
+  attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh);
+  dim3 grid(T / ATT_BK, B * nh);
+  attention_bwd_kernel<<<grid, ATT_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
+                                                                     T, nh, scale, status);
+  attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_load_attention() {
+  cudaFuncAttributes a;
+  int bad = 0;
+  bad |= cudaFuncGetAttributes(&a, attention_fwd_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, attention_bwd_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, attention_bwd_prep_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, attention_dq_convert_kernel) != cudaSuccess;
+  return bad ? -1 : 0;
+}

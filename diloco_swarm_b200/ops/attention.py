@@ -25,10 +25,13 @@ from ._lib import check, cuda_lib, stream_ptr
 BF16 = torch.bfloat16
 
 
-def _native_available(hs: int) -> bool:
+def _native_available(hs: int, T: int) -> bool:
+    """The sm_100a kernels cover head size 64 (GPT-2 small to xl) and sequence
+    lengths that are multiples of 128; other shapes use the library kernel."""
     if os.environ.get("DSWARM_ATTENTION", "native") == "sdpa":
         return False
-    return hs in (32, 64) and hasattr(cuda_lib(), "dsw_attention_fwd")
+    lib = cuda_lib()
+    return hs == 64 and T % 128 == 0 and hasattr(lib, "dsw_attention_fwd") and hasattr(lib, "dsw_attention_bwd")
 
 
 class AttnCtx:
@@ -40,7 +43,7 @@ def attention_fwd(qkv: torch.Tensor, B: int, T: int, nh: int, need_ctx: bool = T
     d = d3 // 3
     hs = d // nh
     ctx = AttnCtx() if need_ctx else None
-    if _native_available(hs):
+    if _native_available(hs, T):
         out = torch.empty(M, d, dtype=BF16, device=qkv.device)
         lse = torch.empty(B * nh * T, dtype=torch.float32, device=qkv.device)
         check(cuda_lib().dsw_attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, nh, hs,
@@ -66,9 +69,12 @@ def attention_bwd(dout: torch.Tensor, ctx: AttnCtx) -> torch.Tensor:
         d = ctx.out.shape[1]
         hs = d // nh
         dqkv = torch.empty_like(ctx.qkv)
+        dq_acc = torch.empty(B * T, d, dtype=torch.float32, device=dout.device)     # fp32 accumulator of dQ
+        dvec = torch.empty(B * nh * T, dtype=torch.float32, device=dout.device)     # rowsum(dO * O)
+        dout = dout.contiguous()
         check(cuda_lib().dsw_attention_bwd(ctx.qkv.data_ptr(), ctx.out.data_ptr(), dout.data_ptr(), ctx.lse.data_ptr(),
-                                           dqkv.data_ptr(), None, None, B, T, nh, hs, 1.0 / math.sqrt(hs), None,
-                                           stream_ptr()), "dsw_attention_bwd")
+                                           dqkv.data_ptr(), dq_acc.data_ptr(), dvec.data_ptr(), B, T, nh, hs,
+                                           1.0 / math.sqrt(hs), None, stream_ptr()), "dsw_attention_bwd")
         return dqkv
     q, k, v, o = ctx.q, ctx.k, ctx.v, ctx.o
     B, nh, T, hs = q.shape
