@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--collective", default="fused")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "balanced"])
     ap.add_argument("--no-outer", action="store_true", help="plain SWARM (per-step gradient all-reduce)")
+    ap.add_argument("--stages", type=int, default=0, help="pipeline stages (default: 1 for one GPU, else 2)")
+    ap.add_argument("--H", type=int, default=0, help="DiLoCo sync interval (default: min(50, steps))")
     return ap.parse_args()
 
 
@@ -107,7 +109,7 @@ class ClockSampler:
 def build_config(args, S: int):
     from diloco_swarm_b200.config import Config, load_toml
     model = load_toml(os.path.join(ROOT, "configs", "model", f"gpt2-{args.model}.toml"))
-    H = max(1, min(50, args.steps))
+    H = args.H if args.H > 0 else max(1, min(50, args.steps))
     outer = {"type": "None", "lr": 0.0} if args.no_outer else {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
     return Config(
         model=model,
@@ -134,6 +136,8 @@ def run_ours(args) -> dict:
 
     N = args.gpus
     S, R = TOPOLOGY.get(N, (2 if N % 2 == 0 else 1, N // 2 if N % 2 == 0 else N))
+    if args.stages > 0:
+        S, R = args.stages, N // args.stages
     world_size = int(os.environ.get("WORLD_SIZE", "1"))
     if world_size != N:
         raise SystemExit(f"--gpus {N} needs {N} ranks (launch with torch.distributed.run); WORLD_SIZE={world_size}")

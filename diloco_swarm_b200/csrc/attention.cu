@@ -323,7 +323,10 @@ attention_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __r
   }
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+constexpr int ATT_BWD_ROW_WARPS = 8;     // two per TMEM lane quarter: each thread takes half of its row's columns
+constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 2);
+
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
                      const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
                      float* __restrict__ dq_acc, int T, int nh, float scale, int* status) {
@@ -353,12 +356,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    mbar_init(sdp_full, 1); mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(dq_free, 4);
+    mbar_init(sdp_full, 1); mbar_init(pds_full, ATT_BWD_ROW_WARPS); mbar_init(dq_full, 1);
+    mbar_init(dq_free, ATT_BWD_ROW_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
   }
-  if (warp == 4) {
+  constexpr int MMA_WARP = ATT_BWD_ROW_WARPS, TMA_WARP = ATT_BWD_ROW_WARPS + 1;
+  if (warp == MMA_WARP) {
     tmem_alloc(tmem_holder, 512);
     tmem_relinquish();
   }
@@ -369,7 +374,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 320,
                  tm_dq = tmem_base + 384;
 
-  if (warp == 5) {
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
@@ -387,7 +392,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         tma_load_2d(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], h * ATT_HS, qrow);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);      // Q K^T and dO V^T
@@ -430,23 +435,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     }
   } else {
     // ------------------------------------------------------------ row threads
-    const int r = warp * 32 + lane;
-    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+    const int q4 = warp & 3, half = warp >> 2;     // TMEM lane quarter, column half
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
     uint8_t* sp = smem + L::P_OFF;
     uint8_t* sds = smem + L::DS_OFF;
     bool ok = true;
     auto drain_dq = [&](int it) -> bool {
       if (!mbar_wait(dq_full, it & 1, abort_flag, status)) return false;
       tc_fence_after();
-      float* dst = dq_acc + (long long)(b * T + (j + it) * ATT_BQ + r) * d + h * ATT_HS;
-#pragma unroll
-      for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+      float* dst = dq_acc + (long long)(b * T + (j + it) * ATT_BQ + r) * d + h * ATT_HS + half * 32;
+      {
         uint32_t v[32];
-        tmem_ld_32x32(tm_dq + lane_addr + c0, v);
+        tmem_ld_32x32(tm_dq + lane_addr + half * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c0 + i), "f"(__uint_as_float(v[i])),
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(__uint_as_float(v[i])),
                        "f"(__uint_as_float(v[i + 1])), "f"(__uint_as_float(v[i + 2])), "f"(__uint_as_float(v[i + 3]))
                        : "memory");
       }
@@ -466,13 +471,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       tc_fence_after();
       const bool diag = it == 0;
       uint32_t sv_[2][32], dpv[2][32];
-      tmem_ld_32x32(tm_s + lane_addr, sv_[0]);
-      tmem_ld_32x32(tm_dp + lane_addr, dpv[0]);
+      tmem_ld_32x32(tm_s + lane_addr + half * 64, sv_[0]);
+      tmem_ld_32x32(tm_dp + lane_addr + half * 64, dpv[0]);
       tmem_ld_wait();
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        const int c0 = cc * 32;
-        if (cc + 1 < 4) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c0 = half * 64 + cc * 32;
+        if (cc + 1 < 2) {
           tmem_ld_32x32(tm_s + lane_addr + c0 + 32, sv_[(cc + 1) & 1]);
           tmem_ld_32x32(tm_dp + lane_addr + c0 + 32, dpv[(cc + 1) & 1]);
         }
@@ -491,7 +496,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           *reinterpret_cast<uint4*>(sds + off) = make_uint4(pack_bf16(ds[c], ds[c + 1]), pack_bf16(ds[c + 2], ds[c + 3]),
                                                              pack_bf16(ds[c + 4], ds[c + 5]), pack_bf16(ds[c + 6], ds[c + 7]));
         }
-        if (cc + 1 < 4) tmem_ld_wait();
+        if (cc + 1 < 2) tmem_ld_wait();
       }
       fence_proxy_async();
       tc_fence_before();
@@ -504,15 +509,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tm_dk : tm_dv;
-        __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d);
-#pragma unroll
-        for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+        __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d) + half * 32;
+        {
           uint32_t v[32];
-          tmem_ld_32x32(src + lane_addr + c0, v);
+          tmem_ld_32x32(src + lane_addr + half * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < 32; c += 8)
-            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(
+            *reinterpret_cast<uint4*>(dst + c) = make_uint4(
                 pack_bf16(__uint_as_float(v[c]), __uint_as_float(v[c + 1])),
                 pack_bf16(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])),
                 pack_bf16(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5])),
@@ -524,7 +528,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -580,7 +584,7 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh);
   dim3 grid(T / ATT_BK, B * nh);
-  attention_bwd_kernel<<<grid, ATT_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
+  attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
                                                                      T, nh, scale, status);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

@@ -262,7 +262,7 @@ extern "C" int dsw_outer_sync(void* const* bufs, void* const* flags, float* thet
   a.lr = lr; a.mu = mu; a.nesterov = nesterov; a.seq = seq;
   a.wait_limit = wait_limit > 0 ? wait_limit : WAIT_CYCLES_LIMIT;
   a.use_barrier = use_barrier; a.status = status;
-  if (blocks <= 0) blocks = 128;
+  if (blocks <= 0) blocks = DSW_MAX_COLL_BLOCKS;
   if (blocks > DSW_MAX_COLL_BLOCKS) blocks = DSW_MAX_COLL_BLOCKS;
   outer_sync_kernel<<<blocks, 512, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -279,7 +279,7 @@ extern "C" int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* 
   a.scale = 1.f / R; a.seq = seq;
   a.wait_limit = wait_limit > 0 ? wait_limit : WAIT_CYCLES_LIMIT;
   a.use_barrier = use_barrier; a.phase_mask = phase_mask; a.status = status;
-  if (blocks <= 0) blocks = 128;
+  if (blocks <= 0) blocks = DSW_MAX_COLL_BLOCKS;
   if (blocks > DSW_MAX_COLL_BLOCKS) blocks = DSW_MAX_COLL_BLOCKS;
   if (wire_bf16) grad_allreduce_bf16_kernel<<<blocks, 512, 0, st>>>(a);
   else           grad_allreduce_f32_kernel<<<blocks, 512, 0, st>>>(a);
