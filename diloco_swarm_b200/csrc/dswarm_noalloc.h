@@ -14,7 +14,7 @@
 // in a fixed array that is part of the library image.
 //
 // Cost and limit: the array is DSW_NOALLOC_LN_MAX_BLOCKS * 3 *
-// DSW_NOALLOC_LN_MAX_D floats = 3 MiB, and every GPU that loads the library
+// DSW_NOALLOC_LN_MAX_D floats = 6.9 MiB, and every GPU that loads the library
 // carries it until the process exits, whether or not this entry point is used.
 // Rows of up to DSW_NOALLOC_LN_MAX_D elements are supported (any number of
 // rows); a larger d is refused with DSW_NOALLOC_TOO_LARGE and a message on
@@ -38,7 +38,7 @@
 #include <cuda_runtime.h>
 
 #define DSW_NOALLOC_LN_MAX_D 2048
-#define DSW_NOALLOC_LN_MAX_BLOCKS 128
+#define DSW_NOALLOC_LN_MAX_BLOCKS 296
 
 #define DSW_NOALLOC_BAD_SHAPE (-20)
 #define DSW_NOALLOC_TOO_LARGE (-21)

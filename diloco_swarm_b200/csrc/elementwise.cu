@@ -95,25 +95,29 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
   }
 }
 
-// LayerNorm backward in two kernels.
-// (A) row kernel: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres);
-//     one warp per row, the row stays in registers.
-// (B) column kernel: dgamma = sum_rows dy*xhat, dbeta = sum_rows dy and optionally the
-//     column sum of dres (the bias gradient of the linear layer that fed the residual
-//     branch).  A thread owns 8 columns and walks rows; the operands were just touched
-//     by (A) so most of this pass is served from L2.  Per-block partials go to a
-//     scratch array partial[row_block][3][d]; a finish kernel adds them into the fp32
-//     gradients (no atomics, deterministic order).
+// LayerNorm backward: dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)) (+ dres), and the
+// column sums dgamma = sum_rows dy*xhat, dbeta = sum_rows dy and (optionally) sum_rows dres, which is
+// the bias gradient of the linear layer that fed the residual branch.
+// One warp per row, the row in registers.  The column sums would cost 72 registers per thread if
+// they lived there (d = 768), which caps the kernel at one block per SM; instead every warp adds its
+// row's terms into its own fp32 strip of shared memory (lane-private columns, so no conflicts and no
+// atomics).  At the end the block folds its warps' strips and writes partial[block][3][d]; a small
+// finish kernel adds the per-block partials into the fp32 gradients in a fixed order.
+constexpr int LN_BWD_WARPS = 8;
+
 template <int LN_MAX_CHUNKS>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(32 * LN_BWD_WARPS, 2)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                     __nv_bfloat16* __restrict__ dx, int M, int d) {
-  const int lane = threadIdx.x & 31;
-  const int wpb = blockDim.x >> 5;
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int M, int d) {
+  extern __shared__ float sh[];                 // [LN_BWD_WARPS][3][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nch = (d + 255) / 256;
-  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
+  float* mine = sh + (long long)warp * 3 * d;
+  for (int i = lane; i < 3 * d; i += 32) mine[i] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * LN_BWD_WARPS + warp; row < M; row += gridDim.x * LN_BWD_WARPS) {
     const long long off = (long long)row * d;
     const float mean = mean_in[row], rstd = rstd_in[row];
     float xh[LN_MAX_CHUNKS][8], gy[LN_MAX_CHUNKS][8];
@@ -122,17 +126,24 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
       const int col = c * 256 + lane * 8;
       if (c < nch && col < d) {
-        float g[8];
+        float g[8], dv[8];
         load8(x + off + col, xh[c]);
-        load8(dy + off + col, gy[c]);
+        load8(dy + off + col, dv);
         load8f(gamma + col, g);
+        float4* a0 = reinterpret_cast<float4*>(mine + col);
+        float4* b0 = reinterpret_cast<float4*>(mine + d + col);
+        float4 ag0 = a0[0], ag1 = a0[1], ab0 = b0[0], ab1 = b0[1];
+        float* ag = &ag0.x; float* agh = &ag1.x; float* ab = &ab0.x; float* abh = &ab1.x;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[c][j] = (xh[c][j] - mean) * rstd;
-          gy[c][j] *= g[j];
+          gy[c][j] = dv[j] * g[j];
           s1 += gy[c][j];
           s2 += gy[c][j] * xh[c][j];
+          if (j < 4) { ag[j] += dv[j] * xh[c][j]; ab[j] += dv[j]; }
+          else       { agh[j - 4] += dv[j] * xh[c][j]; abh[j - 4] += dv[j]; }
         }
+        a0[0] = ag0; a0[1] = ag1; b0[0] = ab0; b0[1] = ab1;
       }
     }
     s1 = warp_sum(s1) / d;
@@ -142,57 +153,27 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       const int col = c * 256 + lane * 8;
       if (c < nch && col < d) {
         float o[8], r[8];
-        if (dres) load8(dres + off + col, r);
+        if (dres) {
+          load8(dres + off + col, r);
+          float4* c0 = reinterpret_cast<float4*>(mine + 2 * d + col);
+          float4 r0 = c0[0], r1 = c0[1];
+          r0.x += r[0]; r0.y += r[1]; r0.z += r[2]; r0.w += r[3];
+          r1.x += r[4]; r1.y += r[5]; r1.z += r[6]; r1.w += r[7];
+          c0[0] = r0; c0[1] = r1;
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
         store8(dx + off + col, o);
       }
     }
   }
-}
-
-// Block = 32 column groups of 8 columns x 8 row lanes; grid = (ceil(d/256), row blocks).
-__global__ void __launch_bounds__(256)
-layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                          const __nv_bfloat16* __restrict__ dres, float* __restrict__ partial, int M, int d) {
-  __shared__ float sh[8][256];
-  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
-  const int col = blockIdx.x * 256 + cg * 8;
-  float ag[8], ab[8], ar[8];
+  __syncthreads();
+  float* out = partial + (long long)blockIdx.x * 3 * d;
+  for (int i = threadIdx.x; i < 3 * d; i += blockDim.x) {
+    float s = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { ag[j] = 0.f; ab[j] = 0.f; ar[j] = 0.f; }
-  if (col < d) {
-    for (int row = blockIdx.y * 8 + rl; row < M; row += gridDim.y * 8) {
-      const long long off = (long long)row * d + col;
-      const float mean = mean_in[row], rstd = rstd_in[row];
-      float xv[8], dv[8];
-      load8(x + off, xv);
-      load8(dy + off, dv);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { ag[j] += dv[j] * (xv[j] - mean) * rstd; ab[j] += dv[j]; }
-      if (dres) {
-        float r[8];
-        load8(dres + off, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ar[j] += r[j];
-      }
-    }
-  }
-  float* out = partial + (long long)blockIdx.y * 3 * d;
-  for (int which = 0; which < 3; ++which) {
-    const float* src = which == 0 ? ag : (which == 1 ? ab : ar);
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < 8; ++j) sh[rl][cg * 8 + j] = src[j];
-    __syncthreads();
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c < d) {
-      float s = 0.f;
-#pragma unroll
-      for (int r = 0; r < 8; ++r) s += sh[r][threadIdx.x];
-      out[which * d + c] = s;
-    }
+    for (int w = 0; w < LN_BWD_WARPS; ++w) s += sh[(long long)w * 3 * d + i];
+    out[i] = s;
   }
 }
 
@@ -404,8 +385,11 @@ extern "C" int dsw_layernorm_fwd(const void* x, const float* gamma, const float*
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// Row blocks of the column pass of dsw_layernorm_bwd = rows of scratch it needs.
-extern "C" int dsw_layernorm_bwd_blocks(int M) { return M >= 8192 ? 128 : (M >= 512 ? 32 : 4); }
+// Number of blocks dsw_layernorm_bwd launches for M rows = rows of scratch it needs.
+extern "C" int dsw_layernorm_bwd_blocks(int M) {
+  const int want = (M + LN_BWD_WARPS * 4 - 1) / (LN_BWD_WARPS * 4);      // about 4 rows per warp at least
+  return want < 1 ? 1 : (want > 296 ? 296 : want);     // at most two blocks per SM
+}
 
 // scratch: fp32 [dsw_layernorm_bwd_blocks(M)][3][d], contents irrelevant on entry.
 // dres_sum (optional): fp32 [d] += column sum of dres.
@@ -413,20 +397,26 @@ extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gam
                                  const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
                                  float* dres_sum, float* scratch, int M, int d, cudaStream_t st) {
   if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
-  const int grid = grid_for(M, 8, 148 * 16);
+  const int grid = dsw_layernorm_bwd_blocks(M);
   const int want = dres_sum != nullptr && dres != nullptr;
-#define LN_BWD(NCH) layernorm_bwd_kernel<NCH><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, (const bf16*)dres, (bf16*)dx, M, d)
+  const size_t shmem = sizeof(float) * LN_BWD_WARPS * 3 * d;
+#define LN_BWD(NCH)                                                                                              \
+  do {                                                                                                           \
+    static bool attr = false;                                                                                    \
+    if (!attr) {                                                                                                 \
+      cudaFuncSetAttribute(layernorm_bwd_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 256 * NCH * 4); \
+      attr = true;                                                                                               \
+    }                                                                                                            \
+    layernorm_bwd_kernel<NCH><<<grid, 32 * LN_BWD_WARPS, shmem, st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, \
+                                                                     (const bf16*)dres, (bf16*)dx, scratch, M, d); \
+  } while (0)
   switch ((d + 255) / 256) {
     case 1: LN_BWD(1); break; case 2: LN_BWD(2); break; case 3: LN_BWD(3); break; case 4: LN_BWD(4); break;
     case 5: LN_BWD(5); break; case 6: LN_BWD(6); break; case 7: LN_BWD(7); break; default: LN_BWD(8); break;
   }
 #undef LN_BWD
   if (cudaGetLastError() != cudaSuccess) return -3;
-  const int rb = dsw_layernorm_bwd_blocks(M);
-  layernorm_bwd_cols_kernel<<<dim3((d + 255) / 256, rb), 256, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd,
-                                                                        want ? (const bf16*)dres : nullptr, scratch, M, d);
-  if (cudaGetLastError() != cudaSuccess) return -3;
-  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, rb, d, dgamma, dbeta,
+  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, grid, d, dgamma, dbeta,
                                                                   want ? dres_sum : nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -486,7 +476,7 @@ extern "C" int dsw_load_elementwise() {
   L(layernorm_fwd_kernel<5>); L(layernorm_fwd_kernel<6>); L(layernorm_fwd_kernel<7>); L(layernorm_fwd_kernel<8>);
   L(layernorm_bwd_kernel<1>); L(layernorm_bwd_kernel<2>); L(layernorm_bwd_kernel<3>); L(layernorm_bwd_kernel<4>);
   L(layernorm_bwd_kernel<5>); L(layernorm_bwd_kernel<6>); L(layernorm_bwd_kernel<7>); L(layernorm_bwd_kernel<8>);
-  L(layernorm_bwd_finish_kernel); L(layernorm_bwd_cols_kernel); L(colsum_kernel); L(embedding_fwd_kernel); L(embedding_bwd_kernel);
+  L(layernorm_bwd_finish_kernel); L(colsum_kernel); L(embedding_fwd_kernel); L(embedding_bwd_kernel);
   L(mask_count_kernel); L(cross_entropy_kernel); L(cast_f32_bf16_kernel); L(cast_bf16_f32_kernel);
 #undef L
   return bad ? -1 : 0;
