@@ -189,6 +189,10 @@ def run_ours(args) -> dict:
     ms_e2e, _, last_e2e = timed(host, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     tokens = args.batch * args.seq * args.steps
+    # the loss lives on the last stage; rank 0 may be a first-stage rank
+    loss_t = torch.tensor([last.loss if last else 0.0], dtype=torch.float64, device=dev)
+    if world_size > 1:
+        dist.all_reduce(loss_t, op=dist.ReduceOp.MAX)
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     out = {
@@ -205,7 +209,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
-        "loss": last.loss if last else None,
+        "loss": float(loss_t.item()),
         "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
     }
     tr.world.barrier()

@@ -61,7 +61,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True,
                     choices=["gemm", "layernorm_fwd", "layernorm_bwd", "cross_entropy", "adamw", "outer_sync",
-                             "grad_allreduce"])
+                             "grad_allreduce", "attention"])
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--T", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=768)
@@ -116,6 +119,18 @@ def main():
         ms = timeit(fn, a.warmup, a.iters, flush)
         nbytes = 2 * M * V * 2          # algorithmic: read the logits once, write the gradient once
         out.update(shape=[M, V], ms=ms, gbs=nbytes / ms / 1e6, frac_of_peak=nbytes / ms / 1e6 / pk["hbm_gbs"])
+    elif a.case == "attention":
+        from ..ops.attention import attention_bwd, attention_fwd
+        B, T, nh = a.B, a.T, a.heads
+        qkv = bf(B * T, 3 * nh * 64, scale=1.0)
+        dout = bf(B * T, nh * 64, scale=1.0)
+        _, ctx = attention_fwd(qkv, B, T, nh)
+        ms_f = timeit(lambda: attention_fwd(qkv, B, T, nh), a.warmup, a.iters, flush)
+        ms_b = timeit(lambda: attention_bwd(dout, ctx), a.warmup, a.iters, flush)
+        fl = 4.0 * B * nh * T * T * 64 / 2          # causal: half of the score matrix
+        out.update(shape=[B, T, nh, 64], native=bool(ctx.native), fwd_ms=ms_f, bwd_ms=ms_b,
+                   fwd_tflops=fl / ms_f / 1e9, bwd_tflops=2.5 * fl / ms_b / 1e9,
+                   fwd_frac_of_peak=fl / ms_f / 1e9 / pk["bf16_tflops"])
     elif a.case == "adamw":
         n = a.n // 8 * 8
         p, g, m, v = (torch.randn(n, device="cuda") * 0.01 for _ in range(4))

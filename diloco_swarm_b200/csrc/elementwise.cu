@@ -178,18 +178,26 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 }
 
 // dgamma[c] += sum_b partial[b][0][c], dbeta[c] += sum_b partial[b][1][c],
-// dres_sum[c] += sum_b partial[b][2][c] (when requested).
-__global__ void __launch_bounds__(256)
+// dres_sum[c] += sum_b partial[b][2][c] (when requested).  Block = 32 columns x 32 slices of the
+// partial blocks, so the few hundred partials per column are summed by 32 threads, not one.
+__global__ void __launch_bounds__(1024)
 layernorm_bwd_finish_kernel(const float* __restrict__ partial, int nblocks, int d, float* __restrict__ dgamma,
                             float* __restrict__ dbeta, float* __restrict__ dres_sum) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 3 * d) return;
-  const int which = i / d, c = i - which * d;
-  float* dst = which == 0 ? dgamma : (which == 1 ? dbeta : dres_sum);
-  if (!dst) return;
+  __shared__ float sh[32][33];
+  const int i = blockIdx.x * 32 + threadIdx.x;          // index into [3][d]
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 3 * d + i];
-  dst[c] += s;
+  if (i < 3 * d)
+    for (int b = threadIdx.y; b < nblocks; b += 32) s += partial[(long long)b * 3 * d + i];
+  sh[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < 3 * d) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += sh[y][threadIdx.x];
+    const int which = i / d, c = i - which * d;
+    float* dst = which == 0 ? dgamma : (which == 1 ? dbeta : dres_sum);
+    if (dst) dst[c] += t;
+  }
 }
 
 // ------------------------------------------------------------------ column sum (bias gradients)
@@ -416,8 +424,8 @@ extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gam
   }
 #undef LN_BWD
   if (cudaGetLastError() != cudaSuccess) return -3;
-  layernorm_bwd_finish_kernel<<<(3 * d + 255) / 256, 256, 0, st>>>(scratch, grid, d, dgamma, dbeta,
-                                                                  want ? dres_sum : nullptr);
+  layernorm_bwd_finish_kernel<<<(3 * d + 31) / 32, dim3(32, 32), 0, st>>>(scratch, grid, d, dgamma, dbeta,
+                                                                         want ? dres_sum : nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -19,6 +19,7 @@ optimiser / DiLoCo part of train_step (src/train.py:247-269).
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -98,6 +99,11 @@ class B200Engine:
         self.training = True
         self._build_views()
         load_all_kernels()
+        # Weight-gradient GEMMs and bias column sums are off the backward critical path (nothing in the
+        # backward reads them), so they run on a second stream and fill the SMs that the dgrad chain,
+        # LayerNorm and attention kernels leave idle (last partial waves, memory-bound phases).
+        self.side = torch.cuda.Stream(device) if os.environ.get("DSWARM_WGRAD_STREAM", "1") != "0" else None
+        self._side_dirty = False
 
     # ------------------------------------------------------------------ views
     def _slice(self, buf: torch.Tensor, key: str) -> torch.Tensor:
@@ -190,6 +196,35 @@ class B200Engine:
         self.stash.clear()
         torch.cuda.synchronize(dev)
 
+    def _fork(self, *tensors):
+        """Context for work that may run beside the main stream: waits for what has been queued on
+        the main stream so far and pins the given tensors' memory until the side work is done."""
+        eng = self
+
+        class _Ctx:
+            def __enter__(self_inner):
+                if eng.side is None:
+                    return None
+                eng.side.wait_stream(torch.cuda.current_stream())
+                for t in tensors:
+                    t.record_stream(eng.side)
+                self_inner.cm = torch.cuda.stream(eng.side)
+                self_inner.cm.__enter__()
+                eng._side_dirty = True
+                return eng.side
+
+            def __exit__(self_inner, *exc):
+                if eng.side is not None:
+                    self_inner.cm.__exit__(*exc)
+                return False
+        return _Ctx()
+
+    def _join(self) -> None:
+        """Main stream waits for the side stream (before anything reads the gradients)."""
+        if self.side is not None and self._side_dirty:
+            torch.cuda.current_stream().wait_stream(self.side)
+            self._side_dirty = False
+
     # ------------------------------------------------------------------ forward pieces
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
         return K.embedding_fwd(ids.contiguous(), self.wte, self.wpe, self.status)
@@ -213,22 +248,25 @@ class B200Engine:
         Mtok = x.shape[0]
         d = x.shape[1]
         dh = K.gemm(dx2, b.pr_w, b_t=False, mode=K.EPI_DGELU, aux_in=h, status=st)
-        K.gemm(dx2, g, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dpr_w,
-               split_k=K.wgrad_split(d, 4 * d, Mtok), status=st)
-        K.colsum_accum(dh, b.dfc_b)
+        with self._fork(dx2, g, dh, ln2):
+            K.gemm(dx2, g, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dpr_w,
+                   split_k=K.wgrad_split(d, 4 * d, Mtok), status=st)
+            K.colsum_accum(dh, b.dfc_b)
+            K.gemm(dh, ln2, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dfc_w,
+                   split_k=K.wgrad_split(4 * d, d, Mtok), status=st)
         dln2 = K.gemm(dh, b.fc_w, b_t=False, status=st)
-        K.gemm(dh, ln2, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dfc_w,
-               split_k=K.wgrad_split(4 * d, d, Mtok), status=st)
         # the column sum of dx2 (bias gradient of mlp.c_proj) rides along with the LayerNorm backward
         dx1 = K.layernorm_bwd(dln2, x1, b.ln2_w, mu2, rs2, b.dln2_w, b.dln2_b, dres=dx2, dres_sum=b.dpr_b)
         datt = K.gemm(dx1, b.o_w, b_t=False, status=st)
-        K.gemm(dx1, att, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.do_w,
-               split_k=K.wgrad_split(d, d, Mtok), status=st)
+        with self._fork(dx1, att):
+            K.gemm(dx1, att, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.do_w,
+                   split_k=K.wgrad_split(d, d, Mtok), status=st)
         dqkv = attention_bwd(datt, actx)
-        K.colsum_accum(dqkv, b.dqkv_b)
+        with self._fork(dqkv, ln1):
+            K.colsum_accum(dqkv, b.dqkv_b)
+            K.gemm(dqkv, ln1, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dqkv_w,
+                   split_k=K.wgrad_split(3 * d, d, Mtok), status=st)
         dln1 = K.gemm(dqkv, b.qkv_w, b_t=False, status=st)
-        K.gemm(dqkv, ln1, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dqkv_w,
-               split_k=K.wgrad_split(3 * d, d, Mtok), status=st)
         return K.layernorm_bwd(dln1, x, b.ln1_w, mu1, rs1, b.dln1_w, b.dln1_b, dres=dx1, dres_sum=b.do_b)
 
     def _body_fwd(self, input_ids, hidden, keep: bool):
@@ -284,9 +322,10 @@ class B200Engine:
         loss, (lnf, mu, rs, dlogits) = self._head(x, targets, mask, scale, grad=True)
         d = x.shape[1]
         V = dlogits.shape[1]
+        with self._fork(dlogits, lnf):
+            K.gemm(dlogits, lnf, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=self.dhead_w,
+                   split_k=K.wgrad_split(V, d, x.shape[0]), status=self.status)
         dlnf = K.gemm(dlogits, self.head_w, b_t=False, status=self.status)
-        K.gemm(dlogits, lnf, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=self.dhead_w,
-               split_k=K.wgrad_split(V, d, x.shape[0]), status=self.status)
         dx = K.layernorm_bwd(dlnf, x, self.lnf_w, mu, rs, self.dlnf_w, self.dlnf_b)
         return loss, self._body_bwd(saved, dx, input_ids, B, T)
 
@@ -306,6 +345,7 @@ class B200Engine:
 
     # ------------------------------------------------------------------ sync + optimisers
     def sync_gradients(self) -> None:
+        self._join()
         R = self.world.num_replicas
         if R == 1:
             return
@@ -316,6 +356,7 @@ class B200Engine:
             self.grad.mul_(1.0 / R)
 
     def optimizer_step(self, lr: float, max_norm: float):
+        self._join()
         K.grad_norm_and_clip(self.grad, self.stats, max_norm)
         self.opt_step += 1
         ic = self.inner_cfg
