@@ -51,7 +51,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=1024)
-    ap.add_argument("--cap", type=int, default=4, help="max_micro_batches (in-flight microbatches per rank)")
+    ap.add_argument("--cap", type=int, default=8, help="max_micro_batches (in-flight microbatches per rank)")
     ap.add_argument("--layer-split", default="balanced")
     ap.add_argument("--collective", default="fused")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "balanced"])

@@ -104,6 +104,14 @@ class B200Engine:
         # LayerNorm and attention kernels leave idle (last partial waves, memory-bound phases).
         self.side = torch.cuda.Stream(device) if os.environ.get("DSWARM_WGRAD_STREAM", "1") != "0" else None
         self._side_dirty = False
+        # Gradient buckets in the order the backward pass completes them (head, blocks from last to
+        # first, embeddings).  During the last backward of a step that ends with a gradient sync, each
+        # bucket's fused all-reduce is queued on its own stream as soon as the bucket is final, so the
+        # NVLink traffic runs under the rest of the backward pass.
+        self.comm_stream = torch.cuda.Stream(device)
+        self.buckets = self._make_buckets()
+        self._buckets_sent = 0
+        self._overlap = os.environ.get("DSWARM_GRAD_OVERLAP", "1") != "0"
 
     # ------------------------------------------------------------------ views
     def _slice(self, buf: torch.Tensor, key: str) -> torch.Tensor:
@@ -196,6 +204,36 @@ class B200Engine:
         self.stash.clear()
         torch.cuda.synchronize(dev)
 
+    def _make_buckets(self) -> List[Tuple[int, int]]:
+        groups: List[List[str]] = []
+        if self.is_last:
+            groups.append([k for k, _, _ in self.specs if k.startswith("transformer.ln_f") or k.startswith("lm_head")])
+        for li in reversed(range(len(self.layers))):
+            groups.append([k for k, _, _ in self.specs if k.startswith(f"transformer.h.{li}.")])
+        if self.is_first:
+            groups.append([k for k, _, _ in self.specs if k.startswith("transformer.wte") or k.startswith("transformer.wpe")])
+        ends = sorted(off for off, _ in self.offsets.values()) + [self.n]
+        out = []
+        for g in groups:
+            if not g:
+                continue
+            lo = min(self.offsets[k][0] for k in g)
+            hi = max(self.offsets[k][0] for k in g)
+            hi = min(e for e in ends if e > hi)          # start of the next tensor (offsets are 8-aligned)
+            out.append((lo, hi - lo))
+        covered = sum(c for _, c in out)
+        assert covered == self.n, (covered, self.n)
+        return out
+
+    def _send_bucket(self) -> None:
+        """Queue the next bucket's all-reduce behind everything queued so far on the compute streams."""
+        off, cnt = self.buckets[self._buckets_sent]
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        if self.side is not None:
+            self.comm_stream.wait_stream(self.side)
+        self.grad_sync.bucket(off, cnt, stream=self.comm_stream)
+        self._buckets_sent += 1
+
     def _fork(self, *tensors):
         """Context for work that may run beside the main stream: waits for what has been queued on
         the main stream so far and pins the given tensors' memory until the side work is done."""
@@ -285,11 +323,20 @@ class B200Engine:
             saved.append(s)
         return x, saved, B, T
 
-    def _body_bwd(self, saved, dx: torch.Tensor, input_ids, B: int, T: int) -> Optional[torch.Tensor]:
+    def _body_bwd(self, saved, dx: torch.Tensor, input_ids, B: int, T: int, sync: bool = False
+                  ) -> Optional[torch.Tensor]:
+        """``sync``: this is the step's last backward on this rank and the step ends with a gradient
+        all-reduce, so every finished bucket is sent at once."""
+        if sync and self.is_last:
+            self._send_bucket()                       # final LayerNorm + LM head
         for b, s in zip(reversed(self.blocks), reversed(saved)):
             dx = self._block_bwd(b, s, dx)
+            if sync:
+                self._send_bucket()
         if self.is_first:
             K.embedding_bwd(input_ids.contiguous(), dx, self.dwte, self.dwpe)
+            if sync:
+                self._send_bucket()
             return None
         return dx.view(B, T, -1)
 
@@ -300,13 +347,16 @@ class B200Engine:
             self.stash[key] = {"saved": saved, "ids": input_ids, "B": B, "T": T}
         return x.view(B, T, -1)
 
-    def backward(self, key: int, grad_out: torch.Tensor) -> Optional[torch.Tensor]:
+    def backward(self, key: int, grad_out: torch.Tensor, sync: bool = False) -> Optional[torch.Tensor]:
         s = self.stash.pop(key)
         B, T = s["B"], s["T"]
         dx = grad_out.reshape(B * T, -1)
         if dx.dtype != BF16:
             dx = dx.to(BF16)
-        return self._body_bwd(s["saved"], dx.contiguous(), s["ids"], B, T)
+        return self._body_bwd(s["saved"], dx.contiguous(), s["ids"], B, T, sync=self._want_overlap(sync))
+
+    def _want_overlap(self, sync: bool) -> bool:
+        return bool(sync and self._overlap and self.fused and self.world.num_replicas > 1)
 
     def _head(self, x: torch.Tensor, targets, mask, scale: float, grad: bool):
         """Final LayerNorm, LM head, masked CE.  Returns (loss, pieces for backward)."""
@@ -317,7 +367,7 @@ class B200Engine:
                         scale, loss, self.count_buf, write_grad=grad, status=self.status)
         return loss, (lnf, mu, rs, logits)
 
-    def forward_backward(self, key: int, input_ids, hidden, targets, mask, scale: float):
+    def forward_backward(self, key: int, input_ids, hidden, targets, mask, scale: float, sync: bool = False):
         x, saved, B, T = self._body_fwd(input_ids, hidden, True)
         loss, (lnf, mu, rs, dlogits) = self._head(x, targets, mask, scale, grad=True)
         d = x.shape[1]
@@ -327,7 +377,7 @@ class B200Engine:
                    split_k=K.wgrad_split(V, d, x.shape[0]), status=self.status)
         dlnf = K.gemm(dlogits, self.head_w, b_t=False, status=self.status)
         dx = K.layernorm_bwd(dlnf, x, self.lnf_w, mu, rs, self.dlnf_w, self.dlnf_b)
-        return loss, self._body_bwd(saved, dx, input_ids, B, T)
+        return loss, self._body_bwd(saved, dx, input_ids, B, T, sync=self._want_overlap(sync))
 
     @torch.no_grad()
     def forward_loss(self, input_ids, hidden, targets, mask, scale: float) -> torch.Tensor:
@@ -350,7 +400,12 @@ class B200Engine:
         if R == 1:
             return
         if self.fused:
-            self.grad_sync.all()
+            # buckets not sent during the last backward (none, if this rank had no microbatch) go now,
+            # in the same order on every replica; then the compute stream waits for all of them
+            while self._buckets_sent < len(self.buckets):
+                self._send_bucket()
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            self._buckets_sent = 0
         else:
             dist.all_reduce(self.grad, group=self.world.curr_stage_group)
             self.grad.mul_(1.0 / R)

@@ -81,7 +81,7 @@ class TorchEngine:
             self.stash[key] = (hidden, y)
         return y.detach()
 
-    def backward(self, key: int, grad_out: torch.Tensor) -> Optional[torch.Tensor]:
+    def backward(self, key: int, grad_out: torch.Tensor, sync: bool = False) -> Optional[torch.Tensor]:
         x, y = self.stash.pop(key)
         torch.autograd.backward(y, grad_tensors=grad_out.to(y.dtype))
         return x.grad if x is not None else None
@@ -92,7 +92,7 @@ class TorchEngine:
         tg = targets.reshape(-1)[keep]
         return F.cross_entropy(lg.float() if not self.autocast else lg, tg) * scale
 
-    def forward_backward(self, key: int, input_ids, hidden, targets, mask, scale: float
+    def forward_backward(self, key: int, input_ids, hidden, targets, mask, scale: float, sync: bool = False
                          ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Last stage: forward, masked mean CE times ``scale``, backward."""
         if hidden is not None:

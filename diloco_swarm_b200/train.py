@@ -119,13 +119,19 @@ class Trainer:
         tokens_per_mb = self.mbs * self.seq
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
         n_local = 0
+        H = cfg.swarm.sync_every_n_steps
+        do_sync = (H > 0 and step % H == 0) or step == self.num_train_steps
+        # the static plan tells which backward is this rank's last one: when the step ends with a
+        # gradient all-reduce, that backward sends each bucket as soon as it is complete
+        last_bwd = max((i for i, op in enumerate(ops) if op.kind in (BWD, FWD_BWD)), default=-1)
+        sync_here = do_sync and not eng.has_outer
         comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
         try:
             for i, op in enumerate(ops):
                 rows = D.micro_batch_rows(op.mb, self.mbs)
                 if op.kind == BWD:
                     dy = comm.recv(i)
-                    dx = eng.backward(op.mb, dy)
+                    dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
                     if op.prev >= 0:
                         comm.send_backward(dx, op.prev)
                     continue
@@ -137,7 +143,8 @@ class Trainer:
                     comm.send_forward(y, op.next)
                 else:
                     loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
-                                                    dev["attention_mask"][rows], self.loss_scale)
+                                                    dev["attention_mask"][rows], self.loss_scale,
+                                                    sync=sync_here and i == last_bwd)
                     loss_acc += loss
                     if op.prev >= 0:
                         comm.send_backward(dx, op.prev)
@@ -146,8 +153,6 @@ class Trainer:
             self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
             comm.abandon_step()
 
-        H = cfg.swarm.sync_every_n_steps
-        do_sync = (H > 0 and step % H == 0) or step == self.num_train_steps
         if do_sync and not eng.has_outer:
             eng.sync_gradients()
         lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
