@@ -211,6 +211,7 @@ def run_ours(args) -> dict:
         "gpu_launches": launches,
         "loss": float(loss_t.item()),
         "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
+        "device_phases_ms_last_step_rank0": tr.last_phase_ms,
     }
     tr.world.barrier()
     tr.logger.close()

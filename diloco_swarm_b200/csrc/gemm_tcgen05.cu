@@ -249,7 +249,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
-          tc_fence_after();
+          // no tcgen05 fence here: the operands were written by TMA (async proxy) and the mbarrier
+          // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
 #pragma unroll
@@ -428,7 +429,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
-          tc_fence_after();
+          // no tcgen05 fence here: the operands were written by TMA (async proxy) and the mbarrier
+          // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
 #pragma unroll

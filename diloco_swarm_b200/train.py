@@ -32,6 +32,7 @@ from .utils import data as D
 from .utils.ckpt import Checkpoint
 from .utils.logger import Level, Logger
 from .utils.metrics import Outputs, eval_metrics, train_metrics
+from .utils.timers import PhaseTimer
 from .utils.misc import format_float, format_int, get_device, seed_everything
 from .world import World
 
@@ -88,6 +89,8 @@ class Trainer:
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
         self.ckpt.setup(w)
         self.last_enqueue_s: float = 0.0
+        self.timer = PhaseTimer(self.device, nvtx=os.environ.get("DSWARM_NVTX", "0") == "1")
+        self.last_phase_ms: Dict[str, float] = {}
 
     # ------------------------------------------------------------------
     def _plan(self, step: int, phase: int, forward_only: bool):
@@ -126,6 +129,8 @@ class Trainer:
         last_bwd = max((i for i, op in enumerate(ops) if op.kind in (BWD, FWD_BWD)), default=-1)
         sync_here = do_sync and not eng.has_outer
         comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
+        pipeline_phase = self.timer.phase("pipeline")
+        pipeline_phase.__enter__()
         try:
             for i, op in enumerate(ops):
                 rows = D.micro_batch_rows(op.mb, self.mbs)
@@ -152,19 +157,26 @@ class Trainer:
         except StepTimeout:
             self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
             comm.abandon_step()
+        finally:
+            pipeline_phase.__exit__(None, None, None)
 
         if do_sync and not eng.has_outer:
-            eng.sync_gradients()
+            with self.timer.phase("grad_sync"):
+                eng.sync_gradients()
         lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
-        norm = eng.optimizer_step(lr, cfg.train.max_norm)
+        with self.timer.phase("optimizer"):
+            norm = eng.optimizer_step(lr, cfg.train.max_norm)
         self.opt_steps += 1
         if do_sync and eng.has_outer:
-            eng.outer_step()
+            with self.timer.phase("outer_sync"):
+                eng.outer_step()
         self.last_enqueue_s = time.time() - start   # host time to queue the whole step
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         eng.check_status()
+        self.last_phase_ms = self.timer.collect()
+        self.logger.log_message(f"Step {step} device phases (ms): {self.last_phase_ms}", master=False, level=Level.DEBUG)
         step_time = time.time() - start
         local = Outputs(step=step, lr=lr, loss=loss_val, tokens=n_local * tokens_per_mb, norm=float(norm),
                         time=step_time, micro_step_time=step_time / self.micro_per_device,

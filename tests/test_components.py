@@ -126,3 +126,26 @@ def test_torch_engine_diloco_single_replica():
     for p, t0, ti in zip(eng.model.parameters(), theta0, inner):
         d = t0 - ti
         assert torch.allclose(p.detach(), t0 - 0.7 * (d + 0.9 * d), atol=1e-6)
+
+
+def test_comm_model_reproduces_the_notebook_figures():
+    from diloco_swarm_b200.utils.comm_model import cumulative, run_cost, summary
+    s = summary("small")
+    assert abs(s["pp_gb_per_step"] - 12.88) < 0.01 and abs(s["dp_gb_per_sync"] - 1.08) < 1e-6
+    c = run_cost(100, 2, 4, 2048, 1024, 768, 180e6, sync_every_n_steps=50)
+    assert c.syncs == 2 and abs(cumulative(c, 50)[-1] - c.total) < 1e-3
+    ours = run_cost(100, 2, 4, 2048, 1024, 768, 180e6, 50, pp_bytes_per_value=2)
+    ref = run_cost(100, 2, 4, 2048, 1024, 768, 180e6, 50, pp_bytes_per_value=4, metadata_plane=True)
+    assert abs(ref.pp_per_step / ours.pp_per_step - 4.0) < 1e-9     # bf16 payload, no metadata plane
+
+
+def test_phase_timer_on_cpu():
+    import time
+    from diloco_swarm_b200.utils.timers import PhaseTimer
+    t = PhaseTimer(torch.device("cpu"))
+    with t.phase("a"):
+        time.sleep(0.01)
+    with t.phase("a"):
+        time.sleep(0.01)
+    out = t.collect()
+    assert out["a"] >= 15 and t.collect() == {}

@@ -1,0 +1,73 @@
+"""Multi-GPU runs of the b200 engine (skipped on boxes with fewer GPUs).
+
+Plain SWARM with a gradient sync every step yields the same weights whatever the
+routing, so a 1 x 2 data-parallel run must reproduce the one-GPU loss curve, and a
+2 x 2 swarm must reproduce the 2 x 1 pipeline (per-stage gradient clipping makes
+pipelines differ slightly from the one-stage run).  Fused and library collectives
+must agree for DiLoCo.
+"""
+import os
+import re
+import shutil
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LOG = "/tmp/dsw_tests/gpu_multi"
+_port = [29700]
+
+
+def _run(run_id, nproc, stages, extra=()):
+    shutil.rmtree(f"{LOG}/{run_id}", ignore_errors=True)
+    _port[0] += 3
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_port[0]), "-m", "diloco_swarm_b200.train",
+           "--swarm.num_stages", str(stages), "--engine", "b200", "--model", "@configs/model/gpt2-tiny.toml",
+           "--model.n_head", "2",                      # head size 64: the tcgen05 attention kernels
+           "--data", "@configs/data/synthetic-zipf.toml", "--data.num_examples", "256", "--data.seq_length", "128",
+           "--train.inner_optimizer", "@configs/optimizer/adamw.toml", "--train.inner_optimizer.lr", "0.003",
+           "--train.outer_optimizer", "@configs/optimizer/none.toml", "--train.max_steps", "5",
+           "--train.batch_size", "16", "--train.micro_batch_size", "2", "--train.max_micro_batches", "3",
+           "--train.step_timeout", "30", "--eval.enable", "false", "--sample.enable", "false",
+           "--logging.log_dir", LOG, "--logging.run_id", run_id, "--logging.console.log_level", "ERROR"] + list(extra)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run(cmd, cwd=ROOT, env=env, timeout=300, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    text = open(f"{LOG}/{run_id}/master.log").read()
+    return [float(x) for x in re.findall(r"\[TRAIN\] Step: \d+ - Time: [\d.]+s - Loss: ([\d.]+)", text)]
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def test_data_parallel_fused_grad_sync_matches_single_gpu():
+    _need(2)
+    one = _run("one", 1, 1)
+    two = _run("dp2", 2, 1)
+    assert len(one) == len(two) == 5
+    assert max(abs(a - b) for a, b in zip(one, two)) < 5e-3, (one, two)
+    wire = _run("dp2_bf16", 2, 1, ["--swarm.grad_wire_dtype", "bfloat16"])
+    assert max(abs(a - b) for a, b in zip(one, wire)) < 2e-2, (one, wire)
+
+
+def test_diloco_fused_outer_sync_matches_library_twin():
+    _need(2)
+    extra = ["--train.outer_optimizer.type", "SGD", "--train.outer_optimizer.lr", "0.7",
+             "--train.outer_optimizer.nesterov", "true", "--swarm.sync_every_n_steps", "2", "--train.max_steps", "6"]
+    fused = _run("diloco_fused", 2, 1, extra)
+    nccl = _run("diloco_nccl", 2, 1, extra + ["--swarm.collective", "nccl"])
+    assert len(fused) == len(nccl) == 3
+    assert max(abs(a - b) for a, b in zip(fused, nccl)) < 5e-3, (fused, nccl)
+
+
+def test_swarm_2x2_matches_pipeline_2x1():
+    _need(4)
+    pipe = _run("pp2", 2, 2)
+    swarm = _run("sw4", 4, 2)
+    assert max(abs(a - b) for a, b in zip(pipe, swarm)) < 5e-3, (pipe, swarm)
