@@ -162,6 +162,16 @@ class LoggingConfig(BaseConfig):
     wandb: WandbLoggingConfig = WandbLoggingConfig()
 
 
+class ElasticConfig(BaseConfig):
+    """(added) host-side membership tracking and re-routing around ranks that leave.
+    The reference's world is static (src/world.py) and has no counterpart."""
+    enable: bool = False
+    timeout: float = 30.0            # seconds the coordinator waits for a rank's end-of-step report
+    # host-side fault injection for tests: this rank announces a leave and exits after that step
+    leave_rank: int = -1
+    leave_after_step: int = -1
+
+
 class CkptConfig(BaseConfig):
     """(added) the reference defines a checkpoint layout (src/ckpt.py) but
     never writes one from the training loop."""
@@ -183,6 +193,7 @@ class Config(BaseConfig):
     sample: SampleConfig = SampleConfig()
     logging: LoggingConfig = LoggingConfig()
     ckpt: CkptConfig = CkptConfig()
+    elastic: ElasticConfig = ElasticConfig()
     # (added) "torch" = autograd stage on library ops (CPU oracle and
     # debugging); "b200" = flat-buffer stage on the sm_100a kernels;
     # "auto" = b200 on CUDA devices, torch elsewhere.

@@ -84,6 +84,13 @@ class Trainer:
             self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
         self.alive: Optional[List[bool]] = None
+        self.membership = None
+        if config.elastic.enable and w.world_size > 1:
+            if self.engine.name != "torch":
+                raise NotImplementedError("elastic membership is implemented for the autograd engine (CPU/gloo): "
+                                          "the fused collectives would have to re-map their peer buffers")
+            from .parallel.liveness import Membership
+            self.membership = Membership(w.rank, w.world_size, w.master_addr, w.master_port + 1, config.elastic.timeout)
         self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
         self.num_train_steps = 0
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
@@ -112,9 +119,23 @@ class Trainer:
         return out
 
     # ------------------------------------------------------------------
+    def _update_membership(self, step: int) -> None:
+        mask = self.membership.begin_step(step)
+        if self.alive is None or mask != self.alive:
+            if self.alive is not None or not all(mask):
+                gone = [r for r, a in enumerate(mask) if not a]
+                self.logger.log_message(f"Step {step}: ranks {gone} are gone, re-routing around them",
+                                        master=False, level=Level.WARNING)
+                self.world.regroup(mask)
+                self.micro_per_device = max(1, self.num_micro // len(self.world.last_stage_ranks))
+                self.loss_scale = 1.0 / self.micro_per_device
+            self.alive = mask
+
     def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Optional[Outputs]]:
         cfg, w, eng, comm = self.config, self.world, self.engine, self.comm
         start = time.time()
+        if self.membership is not None:
+            self._update_membership(step)
         eng.train()
         eng.zero_grad()
         _, ops = self._plan(step, 0, forward_only=False)
@@ -182,6 +203,8 @@ class Trainer:
                         time=step_time, micro_step_time=step_time / self.micro_per_device,
                         num_micro_batches=n_local)
         stage = sync_outputs(w, local, self.device) if do_sync else None
+        if self.membership is not None:
+            self.membership.end_step(step)
         return local, stage
 
     # ------------------------------------------------------------------
@@ -311,6 +334,9 @@ class Trainer:
         step = start_step
         for step in range(start_step + 1, num_train_steps + 1):
             batch = next(it)
+            el = cfg.elastic
+            if self.membership is not None and el.leave_rank == w.rank and el.leave_after_step == step:
+                self.membership.announce_leave(step)
             local, stage = self.train_step(step, batch)
             local_m.update(local)
             log.log_metrics(local_m.compute(), step=step, master=False)
@@ -330,6 +356,10 @@ class Trainer:
                 log.log_metrics(self.eval_loop("eval", eval_loader, eval_m), step=step, master=True)
             if cfg.ckpt.enable and cfg.ckpt.every_n_steps > 0 and step % cfg.ckpt.every_n_steps == 0:
                 self.save_checkpoint(step)
+            if self.membership is not None and el.leave_rank == w.rank and el.leave_after_step == step:
+                log.log_message(f"Rank {w.rank} leaves after step {step}", master=False, level=Level.WARNING)
+                self.left = True
+                return last
         if cfg.eval.enable:
             out = self.eval_loop("test", eval_loader, eval_m)
             log.log_metrics(out, step=step, master=True)
@@ -372,6 +402,14 @@ def main(config: Config) -> Dict[str, float]:
         f"{k.replace('_', ' ').title()}: {format_int(v, 1) if isinstance(v, int) else format_float(v)}"
         for k, v in setup.items()), master=True, level=Level.INFO)
     out = trainer.train_loop(train_loader, eval_loader, tokenizer, num_steps)
+    if trainer.membership is not None:
+        # ranks that left are not waited for, and the process group is not torn down collectively
+        if not getattr(trainer, "left", False):
+            trainer.membership.barrier("end")
+            if w.rank == 0:
+                time.sleep(1.0)          # the store lives here: let the others read the barrier first
+        log.close()
+        os._exit(0)
     w.barrier()
     log.close()
     w.destroy()

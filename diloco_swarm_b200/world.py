@@ -85,6 +85,23 @@ class World:
         self.first_last_stage_group = dist.new_group(fl, timeout=timeout)
         self.barrier()
 
+    def regroup(self, alive: List[bool]) -> None:
+        """Shrink this rank's view of the world to the live ranks: stage membership, leaders and the
+        stage group used by the collectives (created among the live members only).  Point-to-point
+        groups are left alone: transfers only ever involve two live ranks."""
+        S = self.num_stages
+        self.stage2ranks = {s: [r for r in range(self.world_size) if r % S == s and alive[r]] for s in range(S)}
+        for s in range(S):
+            if not self.stage2ranks[s]:
+                raise RuntimeError(f"stage {s} has no live replica left")
+        self.stage2leader = {s: self.stage2ranks[s][0] for s in range(S)}
+        self.is_leader = self.rank == self.stage2leader[self.stage]
+        self.is_master = self.is_leader and self.is_last_stage
+        mine = self.stage2ranks[self.stage]
+        self.num_replicas = len(mine)
+        self.replica_index = mine.index(self.rank)
+        self.curr_stage_group = (dist.new_group(mine, use_local_synchronization=True) if len(mine) > 1 else None)
+
     def barrier(self) -> None:
         if dist.is_initialized():
             if self.backend == "nccl":

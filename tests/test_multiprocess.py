@@ -147,3 +147,17 @@ def launch_keep(run_id, nproc, stages, extra):
         return launch(run_id, nproc, stages, extra)
     finally:
         shutil.rmtree = real_rmtree
+
+
+@pytest.mark.parametrize("leaver", [3, 2])
+def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
+    """Host-side failure: one replica announces a leave, finishes its step and exits; the others learn
+    of it from the store before their next step, route around it and keep training."""
+    name = f"leave{leaver}"
+    launch(name, 4, 2, ["--elastic.enable", "true", "--elastic.timeout", "20", "--elastic.leave_rank", str(leaver),
+                        "--elastic.leave_after_step", "2", "--train.max_steps", "5"])
+    losses = global_losses(name)
+    assert len(losses) == 5 and losses[-1] < losses[0]
+    text = open(f"{LOG}/{name}/master.log").read() + open(f"{LOG}/{name}/0.log").read()
+    assert f"ranks [{leaver}] are gone" in text
+    assert f"Rank {leaver} leaves after step 2" in open(f"{LOG}/{name}/{leaver}.log").read()
