@@ -193,6 +193,10 @@ def run_ours(args) -> dict:
     loss_t = torch.tensor([last.loss if last else 0.0], dtype=torch.float64, device=dev)
     if world_size > 1:
         dist.all_reduce(loss_t, op=dist.ReduceOp.MAX)
+    # device time of the last outer sync (fused all-reduce + Nesterov + write-back + bf16 refresh), max over ranks
+    osync = torch.tensor([tr.last_phase_ms.get("outer_sync", 0.0)], dtype=torch.float64, device=dev)
+    if world_size > 1:
+        dist.all_reduce(osync, op=dist.ReduceOp.MAX)
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     out = {
@@ -209,6 +213,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
+        "outer_sync_ms": float(osync.item()),
         "loss": float(loss_t.item()),
         "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
         "device_phases_ms_last_step_rank0": tr.last_phase_ms,
