@@ -189,11 +189,14 @@ def run_ours(args) -> dict:
     ms_e2e, _, last_e2e = timed(host, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     tokens = args.batch * args.seq * args.steps
-    # the loss lives on the last stage; rank 0 may be a first-stage rank
-    loss_t = torch.tensor([last.loss if last else 0.0], dtype=torch.float64, device=dev)
+    # the loss lives on the last stage (rank 0 may be a first-stage rank); every last-stage replica reports the
+    # sum over its own microbatches divided by M/R, so the mean over those replicas is the batch loss
+    loss_t = torch.tensor([last.loss if (last and tr.engine.is_last) else 0.0], dtype=torch.float64, device=dev)
     if world_size > 1:
-        dist.all_reduce(loss_t, op=dist.ReduceOp.MAX)
-    # device time of the last outer sync (fused all-reduce + Nesterov + write-back + bf16 refresh), max over ranks
+        dist.all_reduce(loss_t, op=dist.ReduceOp.SUM)
+        loss_t /= len(tr.world.last_stage_ranks)
+    # device time of the last outer sync (fused all-reduce + Nesterov + write-back + bf16 refresh), max over
+    # ranks; the kernel's entry barrier waits for the slowest replica, so replica skew is part of it
     osync = torch.tensor([tr.last_phase_ms.get("outer_sync", 0.0)], dtype=torch.float64, device=dev)
     if world_size > 1:
         dist.all_reduce(osync, op=dist.ReduceOp.MAX)
@@ -213,7 +216,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
-        "outer_sync_ms": float(osync.item()),
+        "outer_sync_ms_incl_peer_wait": float(osync.item()),
         "loss": float(loss_t.item()),
         "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
         "device_phases_ms_last_step_rank0": tr.last_phase_ms,
