@@ -95,35 +95,48 @@ outer_sync_kernel(OuterArgs a) {
   const long long lo = (long long)a.rank * a.shard;
   const long long hi = min(a.n, lo + a.shard);
   const float invR = 1.f / a.R;
-  for (long long i = lo + 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i < hi;
-       i += 4LL * gridDim.x * blockDim.x) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long stride = 4LL * gridDim.x * blockDim.x;
+  // two independent float4 columns per thread and iteration: all 2R peer loads are issued before
+  // the first one is consumed, which doubles the bytes each thread keeps in flight on the links
+  for (long long i0 = lo + 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i0 < hi; i0 += 2 * stride) {
+    const long long idx[2] = {i0, i0 + stride};
+    float4 s[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
 #pragma unroll
-    for (int j = 0; j < MAX_PEERS; ++j) {
-      if (j < a.R) {
-        const float4 v = ld_f4(reinterpret_cast<const float*>(a.pt.buf[j]) + i);
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] < hi) {
+#pragma unroll
+        for (int j = 0; j < MAX_PEERS; ++j) {
+          if (j < a.R) {
+            const float4 v = ld_f4(reinterpret_cast<const float*>(a.pt.buf[j]) + idx[u]);
+            s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+          }
+        }
       }
     }
-    const long long k = i - lo;
-    float4 tg = ld_f4(a.theta_g + k);
-    float4 mb = ld_f4(a.mom + k);
-    float* S = &s.x; float* T = &tg.x; float* B = &mb.x;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float delta = T[c] - S[c] * invR;              // averaged pseudo-gradient
-      float upd = delta;
-      if (a.mu != 0.f) {
-        B[c] = a.mu * B[c] + delta;                        // first step: buffer starts at 0, so it becomes delta
-        upd = a.nesterov ? delta + a.mu * B[c] : B[c];
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] >= hi) continue;
+      const long long i = idx[u];
+      const long long k = i - lo;
+      float4 tg = ld_f4(a.theta_g + k);
+      float4 mb = ld_f4(a.mom + k);
+      float* S = &s[u].x; float* T = &tg.x; float* B = &mb.x;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float delta = T[c] - S[c] * invR;              // averaged pseudo-gradient
+        float upd = delta;
+        if (a.mu != 0.f) {
+          B[c] = a.mu * B[c] + delta;                        // first step: buffer starts at 0, so it becomes delta
+          upd = a.nesterov ? delta + a.mu * B[c] : B[c];
+        }
+        T[c] = T[c] - a.lr * upd;
       }
-      T[c] = T[c] - a.lr * upd;
-    }
-    st_f4(a.theta_g + k, tg);
-    st_f4(a.mom + k, mb);
+      st_f4(a.theta_g + k, tg);
+      st_f4(a.mom + k, mb);
 #pragma unroll
-    for (int j = 0; j < MAX_PEERS; ++j)
-      if (j < a.R) st_f4(reinterpret_cast<float*>(a.pt.buf[j]) + i, tg);
+      for (int j = 0; j < MAX_PEERS; ++j)
+        if (j < a.R) st_f4(reinterpret_cast<float*>(a.pt.buf[j]) + i, tg);
+    }
   }
   if (a.use_barrier) peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok);
 }
@@ -149,20 +162,30 @@ grad_allreduce_f32_kernel(GradArgs a) {
   if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq, a.wait_limit, a.status, &sh_ok)) return;
   const long long lo = a.offset + (long long)a.rank * a.shard;
   const long long hi = min(a.offset + a.count, lo + a.shard);
-  for (long long i = lo + 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i < hi;
-       i += 4LL * gridDim.x * blockDim.x) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long stride = 4LL * gridDim.x * blockDim.x;
+  for (long long i0 = lo + 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i0 < hi; i0 += 2 * stride) {
+    const long long idx[2] = {i0, i0 + stride};          // two columns per thread: 2R peer loads in flight
+    float4 s[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
 #pragma unroll
-    for (int j = 0; j < MAX_PEERS; ++j) {
-      if (j < a.R) {
-        const float4 v = ld_f4(reinterpret_cast<const float*>(a.pt.buf[j]) + i);
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] < hi) {
+#pragma unroll
+        for (int j = 0; j < MAX_PEERS; ++j) {
+          if (j < a.R) {
+            const float4 v = ld_f4(reinterpret_cast<const float*>(a.pt.buf[j]) + idx[u]);
+            s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+          }
+        }
       }
     }
-    s.x *= a.scale; s.y *= a.scale; s.z *= a.scale; s.w *= a.scale;
 #pragma unroll
-    for (int j = 0; j < MAX_PEERS; ++j)
-      if (j < a.R) st_f4(reinterpret_cast<float*>(a.pt.buf[j]) + i, s);
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] >= hi) continue;
+      s[u].x *= a.scale; s[u].y *= a.scale; s[u].z *= a.scale; s[u].w *= a.scale;
+#pragma unroll
+      for (int j = 0; j < MAX_PEERS; ++j)
+        if (j < a.R) st_f4(reinterpret_cast<float*>(a.pt.buf[j]) + idx[u], s[u]);
+    }
   }
   if (a.use_barrier) peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok);
 }
