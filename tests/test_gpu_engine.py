@@ -111,3 +111,56 @@ def test_diloco_outer_step_single_replica():
     want = theta0 - 0.7 * (delta + 0.9 * delta)     # first Nesterov step: buf = delta
     assert torch.allclose(eb.theta, want, atol=1e-6)
     assert torch.allclose(eb.w16.float(), eb.theta, atol=1e-2, rtol=1e-2)
+
+
+def test_checkpoint_roundtrip_restores_the_training_state(tmp_path):
+    """state_dict / optimiser / outer state of the flat-buffer engine: a fresh engine loaded from them
+    continues exactly like the original."""
+    from diloco_swarm_b200.models.engine_b200 import B200Engine
+    from diloco_swarm_b200.models.gpt2 import GPT2Config
+    cfg = make_config(train={"outer_optimizer": {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}})
+    mc = cfg.model
+    g = GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer, n_head=mc.n_head,
+                   n_embd=mc.n_embd)
+    dev = torch.device("cuda", 0)
+    a = B200Engine(g, single_world(), cfg, dev)
+    ids, tg, mask = _batch(cfg)
+    for _ in range(3):
+        a.forward_backward(0, ids, None, tg, mask, 1.0)
+        a.optimizer_step(1e-3, 1.0)
+    a.outer_step()
+    sd, opt, outer = a.state_dict(), a.optim_state(), a.outer_state()
+    assert set(sd) == {k for k, _, _ in a.specs} and sd["lm_head.weight"].shape == (mc.vocab_size, mc.n_embd)
+    torch.save(sd, tmp_path / "model.pt")
+    b = B200Engine(g, single_world(), cfg, dev)
+    b.load_state_dict(torch.load(tmp_path / "model.pt", weights_only=True))
+    b.load_optim_state(opt)
+    b.load_outer_state(outer)
+    for eng in (a, b):
+        eng.forward_backward(0, ids, None, tg, mask, 1.0)
+        eng.optimizer_step(1e-3, 1.0)
+        eng.outer_step()
+    torch.cuda.synchronize()
+    assert torch.allclose(a.theta, b.theta, atol=1e-6)
+    la, _ = a.forward_backward(1, ids, None, tg, mask, 1.0)
+    lb, _ = b.forward_backward(1, ids, None, tg, mask, 1.0)
+    assert abs(la.item() - lb.item()) < 1e-4
+
+
+def test_sgd_inner_optimizer_and_explicit_layer_split():
+    from diloco_swarm_b200.models.engine_b200 import B200Engine
+    from diloco_swarm_b200.models.gpt2 import GPT2Config
+    cfg = make_config(train={"inner_optimizer": {"type": "SGD", "lr": 0.05, "momentum": 0.9, "nesterov": True}},
+                      swarm={"layer_split": "2"})
+    mc = cfg.model
+    g = GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer, n_head=mc.n_head,
+                   n_embd=mc.n_embd)
+    eng = B200Engine(g, single_world(), cfg, torch.device("cuda", 0))
+    ids, tg, mask = _batch(cfg)
+    first = None
+    for _ in range(6):
+        loss, _ = eng.forward_backward(0, ids, None, tg, mask, 1.0)
+        eng.optimizer_step(0.05, 1.0)
+        first = first if first is not None else loss.item()
+    eng.check_status()
+    assert loss.item() < first
