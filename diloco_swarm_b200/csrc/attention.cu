@@ -24,6 +24,17 @@ namespace dsw {
 
 int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld,
                       int box_inner, int box_outer);
+int make_tmap_f32_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
+                     int box_outer);
+
+// Optional in-kernel timeline for tuning: when a trace buffer is registered (dsw_attention_set_trace),
+// CTA (0,0) stores %globaltimer values at its phase boundaries: [0,256) row-warp 0, [256,512) MMA thread.
+__device__ __forceinline__ long long gtimer() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define ATT_TRACE(buf, base, slot) do { if ((buf) != nullptr && (slot) < 256) (buf)[(base) + (slot)++] = gtimer(); } while (0)
 
 constexpr int ATT_BQ = 128;        // query rows per CTA
 constexpr int ATT_BK = 128;        // kv rows per step
@@ -58,7 +69,7 @@ __device__ __forceinline__ uint32_t p_offset(int row, int col) {
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
-                     float* __restrict__ lse_out, int T, int nh, float scale_log2, int* status) {
+                     float* __restrict__ lse_out, int T, int nh, float scale_log2, int* status, long long* trace) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023) {            // swizzled operand tiles need 1024-byte alignment
@@ -83,6 +94,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   const int d = nh * ATT_HS;
   const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
   const int n_kv = qi + 1;
+  long long* tr = (blockIdx.x == 0 && blockIdx.y == 0) ? trace : nullptr;
+  int tslot = 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -126,22 +139,29 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       const uint32_t sq = smem_u32(smem + AttSmem::Q_OFF);
       const uint32_t sp = smem_u32(smem + AttSmem::P_OFF);
       bool ok = mbar_wait(q_full, 0, abort_flag, status);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const uint32_t sk = smem_u32(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES);
-        const uint32_t sv = smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES);
-        if (!mbar_wait(&kv_full[s], ph, abort_flag, status)) { ok = false; break; }
-        // S may be overwritten once the softmax warps have consumed the previous one (p_full of j-1)
-        if (j > 0 && !mbar_wait(p_full, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
+      auto issue_s = [&](int jj) -> bool {          // S_jj = Q K_jj^T into the (single) score buffer
+        const int st = jj & 1;
+        if (!mbar_wait(&kv_full[st], (jj >> 1) & 1, abort_flag, status)) return false;
+        const uint32_t sk = smem_u32(smem + AttSmem::K_OFF + st * ATT_TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < ATT_HS / 16; ++k)
           umma_bf16(tmem_s, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s,
                     k > 0);
         umma_commit(s_full);
-        // P_j V_j once the softmax warps have written P_j (and have drained O_{j-1})
+        ATT_TRACE(tr, 256, tslot);          // S issued
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t sv = smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES);
+        // P_j is in shared memory and S_j has been consumed
         if (!mbar_wait(p_full, j & 1, abort_flag, status)) { ok = false; break; }
+        ATT_TRACE(tr, 256, tslot);          // P ready
+        tc_fence_after();
+        // the next score tile goes first: the softmax warps need it next, while the P V product
+        // is only folded in after their first pass over it
+        if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
         if (j > 0 && !mbar_wait(o_free, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -150,6 +170,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
                     make_smem_desc(sv + k * 2048, ATT_TILE_BYTES, 1024), idesc_o, k > 0);
         umma_commit(o_full);
         umma_commit(&kv_empty[s]);
+        ATT_TRACE(tr, 256, tslot);          // PV issued
       }
     }
   } else {
@@ -162,9 +183,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     float m = -INFINITY, l = 0.f;
     uint8_t* sp = smem + AttSmem::P_OFF;
     bool ok = true;
+    if (threadIdx.x != 0) tr = nullptr;
     for (int j = 0; j < n_kv && ok; ++j) {
+      ATT_TRACE(tr, 0, tslot);              // waiting for S
       if (!mbar_wait(s_full, j & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
+      ATT_TRACE(tr, 0, tslot);              // S arrived
       const bool diag = j == qi;
       // pass 1: row maximum
       float mx = -INFINITY;
@@ -185,6 +209,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
       const float m_new = fmaxf(m, mx * scale_log2);
       const float alpha = fast_exp2(m - m_new);               // 0 on the first tile (m = -inf)
+      ATT_TRACE(tr, 0, tslot);              // pass 1 done
       // the previous P V product has to be folded in before P is overwritten
       if (j > 0) {
         if (!mbar_wait(o_full, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
@@ -203,6 +228,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
 #pragma unroll
       for (int i = 0; i < ATT_HS; ++i) o[i] *= alpha;
+      ATT_TRACE(tr, 0, tslot);              // previous O folded in
       // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
       float sum = 0.f;
       {
@@ -230,6 +256,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
       l = l * alpha + sum;
       m = m_new;
+      ATT_TRACE(tr, 0, tslot);              // pass 2 done
       fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
       tc_fence_before();
       __syncwarp();
@@ -284,7 +311,8 @@ struct AttBwdSmem {
   static constexpr int DO_OFF = Q_OFF + 2 * ATT_TILE_BYTES;         // 2 stages
   static constexpr int P_OFF = DO_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
   static constexpr int DS_OFF = P_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
-  static constexpr int BAR_OFF = DS_OFF + 2 * ATT_TILE_BYTES;
+  static constexpr int DQ_OFF = DS_OFF + 2 * ATT_TILE_BYTES;        // fp32 [2 halves][128 rows][32], 128-byte swizzled
+  static constexpr int BAR_OFF = DQ_OFF + 2 * ATT_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
 };
 
@@ -328,8 +356,8 @@ constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 2);
 
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
-                     const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
-                     float* __restrict__ dq_acc, int T, int nh, float scale, int* status) {
+                     const __grid_constant__ CUtensorMap tmap_dq, const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
+                     float* __restrict__ dq_acc, int T, int nh, float scale, int* status, long long* trace) {
   using L = AttBwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -352,6 +380,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   const int nq = T / ATT_BQ;
   const int steps = nq - j;
   const float scale_log2 = scale * 1.4426950408889634f;
+  long long* tr = (blockIdx.x == 0 && blockIdx.y == 0) ? trace : nullptr;
+  int tslot = 0;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -414,7 +444,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         for (int k = 0; k < 4; ++k)
           umma_bf16(tm_dp, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), id_s, k > 0);
         umma_commit(sdp_full);
+        ATT_TRACE(tr, 256, tslot);          // S, dP issued
         if (!mbar_wait(pds_full, it & 1, abort_flag, status)) { ok = false; break; }
+        ATT_TRACE(tr, 256, tslot);          // P, dS ready
         if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -431,6 +463,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
                     make_smem_desc(sk + k * 2048, ATT_TILE_BYTES, 1024), id_q, k > 0);
         umma_commit(dq_full);
         umma_commit(&q_empty[s]);
+        ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
       }
     }
   } else {
@@ -441,23 +474,38 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     uint8_t* sp = smem + L::P_OFF;
     uint8_t* sds = smem + L::DS_OFF;
     bool ok = true;
+    if (threadIdx.x != 0) tr = nullptr;
+    uint8_t* sdq = smem + L::DQ_OFF + half * ATT_TILE_BYTES;     // this thread's half: [128 rows][32 fp32]
+    const bool elected = threadIdx.x == 0;
+    // dQ of step `it`: TMEM -> registers -> swizzled shared tile -> one TMA reduce-add per half into the
+    // fp32 dQ scratch.  The bulk reduction runs asynchronously, so no thread waits on global atomics.
     auto drain_dq = [&](int it) -> bool {
       if (!mbar_wait(dq_full, it & 1, abort_flag, status)) return false;
       tc_fence_after();
-      float* dst = dq_acc + (long long)(b * T + (j + it) * ATT_BQ + r) * d + h * ATT_HS + half * 32;
-      {
-        uint32_t v[32];
-        tmem_ld_32x32(tm_dq + lane_addr + half * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(__uint_as_float(v[i])),
-                       "f"(__uint_as_float(v[i + 1])), "f"(__uint_as_float(v[i + 2])), "f"(__uint_as_float(v[i + 3]))
-                       : "memory");
-      }
+      uint32_t v[32];
+      tmem_ld_32x32(tm_dq + lane_addr + half * 32, v);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
+      // the previous reduction must have finished reading the staging tile
+      if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(sdq + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (elected) {
+        const int row_g = b * T + (j + it) * ATT_BQ;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                       ::"l"(&tmap_dq), "r"(h * ATT_HS + hh * 32), "r"(row_g),
+                         "r"(smem_u32(smem + L::DQ_OFF + hh * ATT_TILE_BYTES))
+                       : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
       return true;
     };
     for (int it = 0; it < steps && ok; ++it) {
@@ -465,10 +513,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       const long long stat = (long long)bh * T + i * ATT_BQ + r;
       const float lse2 = lse[stat] * 1.4426950408889634f;
       const float Dr = Dvec[stat];
+      ATT_TRACE(tr, 0, tslot);              // step start
       // the previous step's MMAs must be done with P / dS before they are overwritten
       if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }
+      ATT_TRACE(tr, 0, tslot);              // dQ drained
       if (!mbar_wait(sdp_full, it & 1, abort_flag, status)) { ok = false; break; }
       tc_fence_after();
+      ATT_TRACE(tr, 0, tslot);              // S, dP arrived
       const bool diag = it == 0;
       uint32_t sv_[2][32], dpv[2][32];
       tmem_ld_32x32(tm_s + lane_addr + half * 64, sv_[0]);
@@ -498,12 +549,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         }
         if (cc + 1 < 2) tmem_ld_wait();
       }
+      ATT_TRACE(tr, 0, tslot);              // P, dS written
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
     }
     if (ok && drain_dq(steps - 1)) {
+      if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
       // dV and dK rows of this kv tile (TMEM lane = kv row)
       __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * ATT_HS;
 #pragma unroll
@@ -538,6 +591,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 
 using namespace dsw;
 
+static long long* g_att_trace = nullptr;
+// Register (or clear, with nullptr) a device buffer of 512 int64 for the in-kernel timeline.
+extern "C" int dsw_attention_set_trace(long long* buf) { g_att_trace = buf; return 0; }
+
 // qkv: bf16 [B*T, 3*nh*64]; out: bf16 [B*T, nh*64]; lse: fp32 [B*nh*T].
 // Requires hs == 64 and T a multiple of 128.
 extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int nh, int hs, float scale,
@@ -556,7 +613,7 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
   }
   dim3 grid(T / ATT_BQ, B * nh);
   attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh,
-                                                                   scale * 1.4426950408889634f, status);
+                                                                   scale * 1.4426950408889634f, status, g_att_trace);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -572,6 +629,9 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tdo, dout, d, (long long)B * T, d, 64, 128);
   if (rc) return rc;
+  CUtensorMap tdq;
+  rc = make_tmap_f32_2d(&tdq, dq_acc, d, (long long)B * T, d, 32, 128);
+  if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttBwdSmem::TOTAL) !=
@@ -584,8 +644,8 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh);
   dim3 grid(T / ATT_BK, B * nh);
-  attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
-                                                                     T, nh, scale, status);
+  attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
+                                                                     T, nh, scale, status, g_att_trace);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

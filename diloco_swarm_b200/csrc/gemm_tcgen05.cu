@@ -523,6 +523,21 @@ int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, long long inner, long lo
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
 }
 
+// 2-D fp32 tensor map, 128-byte swizzle (box_inner * 4 bytes must be 128).
+int make_tmap_f32_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
+                     int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
 static int g_num_sms = 0;
 
 template <int BN, int NSTAGE>
