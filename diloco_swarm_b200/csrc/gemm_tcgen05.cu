@@ -24,6 +24,13 @@
 
 namespace dsw {
 
+__device__ __forceinline__ long long gemm_gtimer() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GEMM_TRACE(buf, slot) do { if ((buf) != nullptr && (slot) < 512) (buf)[(slot)++] = gemm_gtimer(); } while (0)
+
 constexpr int BM = 128;
 constexpr int BK = 64;          // one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
@@ -49,6 +56,7 @@ struct GemmArgs {
   const __nv_bfloat16* resid; long long ldr;
   __nv_bfloat16* aux_out; const __nv_bfloat16* aux_in; long long ldaux;
   int* status;
+  long long* trace;     // optional: CTA 0's MMA thread stores %globaltimer stamps per k-block (tuning aid)
 };
 
 // Epilogue for one row and 32 consecutive columns of the accumulator.
@@ -117,12 +125,14 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& g, int row, int c
 // chunk is still being written out.
 template <int NCH, class Release>
 __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, uint32_t t_addr, int row, bool row_ok, int col_base,
-                                                  bool has_k, Release release) {
+                                                  bool has_k, Release release, long long* etr = nullptr,
+                                                  int* eslot = nullptr) {
   uint32_t r[2][32];
   tmem_ld_32x32(t_addr, r[0]);
   tmem_ld_wait();
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
+    if (etr) GEMM_TRACE(etr, *eslot);
     if (c + 1 < NCH) tmem_ld_32x32(t_addr + (c + 1) * 32, r[(c + 1) & 1]);
     else release();
     const int col0 = col_base + c * 32;
@@ -136,12 +146,138 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, uint32_t t_
   }
 }
 
+// Staged epilogue.  A thread owns one accumulator row (that is how tcgen05.ld hands the data out),
+// but a store in which every lane writes 16 bytes of a different row touches 32 cache lines per
+// instruction.  So each warp passes its 32 x 128-byte slab through a private 4 KB tile of shared
+// memory (16-byte chunks XOR-swizzled by row, conflict-free both ways) and writes it out with
+// lane = (row within a group of 4, 16-byte chunk): every store, residual/aux load or fp32
+// reduction instruction then covers 4 rows x 128 contiguous bytes.
+constexpr int EPI_STAGE_BYTES = 32 * 128;
+
+__device__ __forceinline__ void stage_row(uint8_t* stage, int lane, const uint32_t (&w)[32]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+        make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+
+// Write one staged slab: rows row_base..+31, `elems` columns of `esize` bytes starting at col0.
+template <class F>
+__device__ __forceinline__ void unstage_rows(const uint8_t* stage, int lane, F&& emit) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = i * 4 + (lane >> 3), ch = lane & 7;
+    const uint4 d = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((ch ^ (rl & 7)) << 4));
+    emit(rl, ch, d);
+  }
+}
+
+template <int NCOLS, class Release>
+__device__ __forceinline__ void drain_accumulator_staged(const GemmArgs& g, uint32_t t_addr, int row_base, int lane,
+                                                         int col_base, bool has_k, uint8_t* stage, Release release) {
+  const bool f32 = g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32;
+  constexpr int NCH = NCOLS / 32;
+  uint32_t r[2][32];
+  tmem_ld_32x32(t_addr, r[0]);
+  if (NCH > 1) tmem_ld_32x32(t_addr + 32, r[1]);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < NCH; c += 2) {
+    // r[0], r[1] hold columns [c*32, c*32+64) of this thread's row
+    float v[64];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { v[i] = __uint_as_float(r[0][i]); v[32 + i] = __uint_as_float(r[1][i]); }
+    if (c + 2 < NCH) {                       // next 64 columns: in flight while this slab is written out
+      tmem_ld_32x32(t_addr + (c + 2) * 32, r[0]);
+      tmem_ld_32x32(t_addr + (c + 3) * 32, r[1]);
+    } else {
+      release();
+    }
+    const int col0 = col_base + c * 32;
+    if (has_k && col0 < g.N) {
+      if (f32) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {      // fp32: 32 columns fill a 128-byte row
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(v[hh * 32 + i]);
+          __syncwarp();
+          stage_row(stage, lane, w);
+          __syncwarp();
+          const int cb = col0 + hh * 32;
+          unstage_rows(stage, lane, [&](int rl, int ch, const uint4& d) {
+            const int row = row_base + rl, col = cb + ch * 4;
+            if (row < g.M && col < g.N) {
+              float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col;
+              if (g.mode == EPI_ATOMIC_F32)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(__uint_as_float(d.x)),
+                             "f"(__uint_as_float(d.y)), "f"(__uint_as_float(d.z)), "f"(__uint_as_float(d.w))
+                             : "memory");
+              else
+                *reinterpret_cast<uint4*>(o) = d;
+            }
+          });
+        }
+      } else {
+        if (g.bias) {
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            if (col0 + i < g.N) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
+              v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
+            }
+          }
+        }
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        __syncwarp();
+        stage_row(stage, lane, w);
+        __syncwarp();
+        if (g.mode == EPI_GELU) {
+          // pre-activation goes out first, then the slab is re-staged with the activation
+          unstage_rows(stage, lane, [&](int rl, int ch, const uint4& d) {
+            const int row = row_base + rl, col = col0 + ch * 8;
+            if (row < g.M && col < g.N) *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col) = d;
+          });
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = pack_bf16(gelu_erf(v[2 * i]), gelu_erf(v[2 * i + 1]));
+          __syncwarp();
+          stage_row(stage, lane, w);
+          __syncwarp();
+        }
+        unstage_rows(stage, lane, [&](int rl, int ch, uint4 d) {
+          const int row = row_base + rl, col = col0 + ch * 8;
+          if (row >= g.M || col >= g.N) return;
+          if (g.mode == EPI_RESID || g.mode == EPI_DGELU) {
+            const __nv_bfloat16* src = g.mode == EPI_RESID ? g.resid + (long long)row * g.ldr + col
+                                                           : g.aux_in + (long long)row * g.ldaux + col;
+            const uint4 x = *reinterpret_cast<const uint4*>(src);
+            uint32_t du[4] = {d.x, d.y, d.z, d.w};
+            const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 a = unpack_bf16(du[q]), b = unpack_bf16(xu[q]);
+              du[q] = g.mode == EPI_RESID ? pack_bf16(a.x + b.x, a.y + b.y)
+                                          : pack_bf16(a.x * gelu_erf_grad(b.x), a.y * gelu_erf_grad(b.y));
+            }
+            d = make_uint4(du[0], du[1], du[2], du[3]);
+          }
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col) = d;
+        });
+      }
+    }
+    if (c + 2 < NCH) tmem_ld_wait();
+  }
+}
+
 template <int BN, int NSTAGE>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = NSTAGE * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = NSTAGE * STAGE_BYTES;              // per-warp epilogue staging tiles
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_WARPS * EPI_STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + alignment slack
 };
 
@@ -235,6 +371,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
+      long long* tr = blockIdx.x == 0 ? g.trace : nullptr;
+      int tslot = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
         const int ks = tile / (tiles_m * tiles_n);
         const int kb0 = ks * kb_per_split;
@@ -248,7 +386,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
+          GEMM_TRACE(tr, tslot);
           if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
+          GEMM_TRACE(tr, tslot);
           // no tcgen05 fence here: the operands were written by TMA (async proxy) and the mbarrier
           // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -264,7 +404,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             umma_bf16(d_tmem, da, db, idesc, accumulate);
             accumulate = 1;
           }
+          GEMM_TRACE(tr, tslot);
           umma_commit(&empty_bar[s]);      // frees the smem stage when these MMAs retire
+          GEMM_TRACE(tr, tslot);
         }
         if (ok) umma_commit(&acc_full[ab]);  // accumulator complete
       }
@@ -285,9 +427,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool has_k = ks * kb_per_split < kb_total;
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
-      drain_accumulator<BN / 64>(g, t_addr, row, row < g.M, n0 + half * (BN / 2), has_k, [&] {
+      drain_accumulator_staged<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
+                                       smem + L::EPI_OFFSET + (warp - 2) * EPI_STAGE_BYTES, [&] {
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -322,7 +464,8 @@ struct PairSmem {
   static constexpr int A_BYTES = 128 * BK * 2;
   static constexpr int B_BYTES = 128 * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = PAIR_STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_WARPS * EPI_STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
 };
 
@@ -469,9 +612,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool has_k = ks * kb_per_split < kb_total;
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
-      drain_accumulator<BN / 64>(g, t_addr, row, row < g.M, n0 + half * (BN / 2), has_k, [&] {
+      drain_accumulator_staged<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
+                                       smem + L::EPI_OFFSET + (warp - 2) * EPI_STAGE_BYTES, [&] {
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -578,6 +721,10 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
 
 using namespace dsw;
 
+static long long* g_gemm_trace = nullptr;
+// Register (or clear) a device buffer of 512 int64 for the one-CTA kernel's MMA-thread timeline.
+extern "C" int dsw_gemm_set_trace(long long* buf) { g_gemm_trace = buf; return 0; }
+
 // A: [M,K] row-major (a_mn_major = 0) or [K,M] row-major (1); lda = row pitch in
 // elements.  B: [N,K] (b_mn_major = 0) or [K,N] (1).  All pitches and the
 // contiguous extents must be multiples of 8 elements; pointers 16-byte aligned.
@@ -614,6 +761,7 @@ extern "C" int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const
   g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
   g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in); g.ldaux = ldaux;
   g.status = status;
+  g.trace = g_gemm_trace;
   if (bn == 512) return launch_pair(ta, tb, g, max_ctas, stream);
   if (bn == 256) return launch<256, 4>(ta, tb, g, max_ctas, stream);
   return launch<128, 6>(ta, tb, g, max_ctas, stream);

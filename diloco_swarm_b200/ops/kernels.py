@@ -41,7 +41,7 @@ def _pick_bn(M: int, N: int, splits: int = 1) -> int:
     e128 = _efficiency(M, N, splits, 128, 128, _NUM_SMS)
     e256 = _efficiency(M, N, splits, 128, 256, _NUM_SMS)
     best = 256 if e256 >= e128 * 0.93 else 128
-    if _USE_PAIR and M >= 256 and N <= 8192:      # measured: the pair wins up to MLP widths, not on the LM head
+    if _USE_PAIR and M >= 256:
         epair = _efficiency(M, N, splits, 256, 256, _NUM_SMS // 2)
         if epair >= max(e128 * 0.8, e256 * 0.9):
             best = 512
