@@ -1,0 +1,109 @@
+"""In-kernel timelines of the GEMM and attention kernels.
+
+    python -m diloco_swarm_b200.benchmarks.timelines --kernel gemm --M 16384 --N 2304 --K 768
+    python -m diloco_swarm_b200.benchmarks.timelines --kernel attention --B 16 --T 1024 --heads 12
+
+The kernels can stamp ``%globaltimer`` at their phase boundaries into a small
+device buffer (``dsw_gemm_set_trace`` / ``dsw_attention_set_trace``; CTA 0 only,
+32 ns resolution, off unless a buffer is registered).  This prints the
+per-phase durations: for the GEMM the MMA-issuing thread's wait / issue / commit
+per k-block, for attention the softmax (or row) warp 0 and the MMA thread per
+tile.  It is a tuning aid; the stamps perturb the kernel slightly, so these are
+not benchmark numbers.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import statistics
+
+import torch
+
+from ..ops import kernels as K
+from ..ops._lib import cuda_lib
+from ..ops.attention import attention_bwd, attention_fwd
+
+
+def _bf(*shape, scale=0.1):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _setter(name):
+    fn = getattr(cuda_lib(), name)
+    fn.argtypes = [ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    return fn
+
+
+def gemm_timeline(M, N, Kd, bn=256):
+    set_trace = _setter("dsw_gemm_set_trace")
+    a, b = _bf(M, Kd), _bf(N, Kd)
+    for _ in range(3):
+        K.gemm(a, b, bn=bn)
+    torch.cuda.synchronize()
+    tr = torch.zeros(512, dtype=torch.int64, device="cuda")
+    set_trace(tr.data_ptr())
+    K.gemm(a, b, bn=bn)
+    torch.cuda.synchronize()
+    set_trace(None)
+    t = [x for x in tr.cpu().tolist() if x]
+    waits = [t[i + 1] - t[i] for i in range(0, len(t) - 3, 4)]
+    mmas = [t[i + 2] - t[i + 1] for i in range(0, len(t) - 3, 4)]
+    commits = [t[i + 3] - t[i + 2] for i in range(0, len(t) - 3, 4)]
+    period = [t[i + 4] - t[i] for i in range(0, len(t) - 4, 4)]
+    print(f"gemm {M}x{N}x{Kd} (one-CTA kernel, bn={bn}): {len(waits)} k-blocks of CTA 0")
+    for name, v in (("full-barrier wait", waits), ("4 x tcgen05.mma", mmas), ("tcgen05.commit", commits),
+                    ("k-block period", period)):
+        print(f"  {name:18s} median {statistics.median(v):6.0f} ns   mean {statistics.mean(v):7.1f} ns   max {max(v)} ns")
+    print("  first periods:", period[:28])
+
+
+def attention_timeline(B, T, nh):
+    set_trace = _setter("dsw_attention_set_trace")
+    qkv, dout = _bf(B * T, 3 * nh * 64, scale=1.0), _bf(B * T, nh * 64, scale=1.0)
+    for _ in range(3):
+        _, ctx = attention_fwd(qkv, B, T, nh)
+        attention_bwd(dout, ctx)
+    torch.cuda.synchronize()
+    tr = torch.zeros(512, dtype=torch.int64, device="cuda")
+
+    def show(title, row_labels, mma_labels):
+        t = tr.cpu().tolist()
+        row, mma = [x for x in t[:256] if x], [x for x in t[256:] if x]
+        t0 = min(row + mma)
+        print(title)
+        print("  row warp 0 :", " ".join(f"{row_labels[i % len(row_labels)]}={x - t0}" for i, x in enumerate(row[:len(row_labels) * 4])))
+        print("  MMA thread :", " ".join(f"{mma_labels[i % len(mma_labels)]}={x - t0}" for i, x in enumerate(mma[:len(mma_labels) * 4])))
+        print(f"  CTA span {max(row + mma) - t0} ns")
+
+    set_trace(tr.data_ptr())
+    _, ctx = attention_fwd(qkv, B, T, nh)
+    torch.cuda.synchronize()
+    show("attention forward, CTA (0,0) (last query tile: all kv tiles), ns since first stamp",
+         ["waitS", "gotS", "pass1", "fold", "pass2"], ["S_issued", "P_ready", "PV_issued"])
+    tr.zero_()
+    attention_bwd(dout, ctx)
+    torch.cuda.synchronize()
+    show("attention backward, CTA (0,0) (kv tile 0: all query tiles), ns since first stamp",
+         ["start", "dQ_drained", "S_dP_ready", "P_dS_written"], ["S_dP_issued", "P_dS_ready", "dV_dK_dQ_issued"])
+    set_trace(None)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=["gemm", "attention"])
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--N", type=int, default=2304)
+    ap.add_argument("--K", type=int, default=768)
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--T", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=12)
+    a = ap.parse_args()
+    if a.kernel == "gemm":
+        gemm_timeline(a.M, a.N, a.K)
+    else:
+        attention_timeline(a.B, a.T, a.heads)
+
+
+if __name__ == "__main__":
+    main()
