@@ -191,6 +191,18 @@ def micro_batch_rows(mb: int, micro_batch_size: int) -> slice:
     return slice(mb * micro_batch_size, (mb + 1) * micro_batch_size)
 
 
+def get_micro_batches(batch: Dict[str, torch.Tensor], micro_batch_size: int, first_stage_ranks: Sequence[int]
+                      ) -> Iterator[Tuple[int, int, Dict[str, torch.Tensor]]]:
+    """(root_rank, local_micro_step, micro_batch) for every microbatch of the global batch, in the
+    reference's naming (src/utils.py:120-126, src/sampler.py:35-38): first-stage rank i owns the chunks
+    k*R0 + i and counts them from 1.  Every rank can evaluate this; only the key would have to travel."""
+    n = next(iter(batch.values())).size(0)
+    r0 = len(first_stage_ranks)
+    for mb in range(n // micro_batch_size):
+        rows = micro_batch_rows(mb, micro_batch_size)
+        yield first_stage_ranks[mb % r0], mb // r0 + 1, {k: v[rows] for k, v in batch.items()}
+
+
 def get_num_steps(max_steps: int, max_epochs: int, num_examples: int, batch_size: int) -> int:
     """Whichever of max_steps / max_epochs is reached first (src/utils.py:145-152)."""
     if num_examples < batch_size:

@@ -149,3 +149,18 @@ def test_phase_timer_on_cpu():
         time.sleep(0.01)
     out = t.collect()
     assert out["a"] >= 15 and t.collect() == {}
+
+
+def test_serializer_and_micro_batch_naming():
+    from diloco_swarm_b200.parallel.serializer import HEADER_BYTES, Serializer
+    from diloco_swarm_b200.utils.data import get_micro_batches
+    s = Serializer((2, 3, 4))
+    x = torch.randn(2, 3, 4)
+    msg = s.serialize(x, (5, 7))
+    assert msg.numel() == HEADER_BYTES + x.numel() * 4          # a header, not a second plane
+    y, meta = s.deserialize(msg)
+    assert torch.equal(x, y) and meta == (5, 7)
+    batch = {"input_ids": torch.arange(32).view(8, 4)}
+    got = [(r, l, mb["input_ids"][0, 0].item()) for r, l, mb in get_micro_batches(batch, 2, [0, 2])]
+    # rank 0 owns chunks 0 and 2 (rows 0-1, 4-5), rank 2 owns chunks 1 and 3: [k*R*mbs + i*mbs, +mbs)
+    assert got == [(0, 1, 0), (2, 1, 8), (0, 2, 16), (2, 2, 24)]
