@@ -455,7 +455,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // leader CTA (cluster rank 0) issues the MMAs for both; each CTA drains its own
 // 128 rows of the accumulator from its own TMEM.
 //   full[s]      in the leader, 2 arrivals (one producer per CTA) + both CTAs' bytes
-//   empty[s]     in each CTA, released by the leader's tcgen05.commit (one per CTA)
+//   empty[s]     in each CTA, released by one multicast tcgen05.commit of the leader
 //   acc_full[b]  in each CTA, same mechanism
 //   acc_empty[b] in the leader, one arrival per epilogue warp of both CTAs
 constexpr int PAIR_BN = 256;
@@ -585,14 +585,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             umma_bf16_pair(d_tmem, da, db, idesc, accumulate);
             accumulate = 1;
           }
-          const uint32_t e = smem_u32(&empty_bar[s]);
-          umma_commit_pair(map_to_cta(e, 0));
-          umma_commit_pair(map_to_cta(e, 1));
+          umma_commit_pair_all(smem_u32(&empty_bar[s]), 0x3);     // frees the stage in both CTAs
         }
         if (ok) {
-          const uint32_t f = smem_u32(&acc_full[ab]);
-          umma_commit_pair(map_to_cta(f, 0));
-          umma_commit_pair(map_to_cta(f, 1));
+          umma_commit_pair_all(smem_u32(&acc_full[ab]), 0x3);
         }
       }
     }

@@ -240,6 +240,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
                : "memory");
 }
 
+// Same, arriving on the barrier at this shared-memory offset in every CTA of `cta_mask` with one
+// instruction (a multicast arrive, not a multicast load).
+__device__ __forceinline__ void umma_commit_pair_all(uint32_t bar_local_addr, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar_local_addr), "h"(cta_mask)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
