@@ -368,6 +368,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(BM, BN, g.a_mn_major, g.b_mn_major);
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t a_lbo = g.a_mn_major ? 8192 : 16, b_lbo = g.b_mn_major ? 8192 : 16;
+      const uint32_t a_step = g.a_mn_major ? (2048 >> 4) : (32 >> 4), b_step = g.b_mn_major ? (2048 >> 4) : (32 >> 4);
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
@@ -393,15 +396,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
+          // K-major: 16 elements = 32 bytes further along the swizzled row per MMA.
+          // MN-major: 16 k-rows of 128 bytes further down.  Only the low descriptor word moves.
+          uint32_t a_lo = smem_desc_lo(sa, a_lbo), b_lo = smem_desc_lo(sb, b_lbo);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 elements = 32 bytes further along the swizzled row.
-            // MN-major: 16 k-rows of 128 bytes further down.
-            const uint64_t da = g.a_mn_major ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                             : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = g.b_mn_major ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                             : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(d_tmem, da, db, idesc, accumulate);
+            umma_bf16_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+            a_lo += a_step; b_lo += b_step;
             accumulate = 1;
           }
           GEMM_TRACE(tr, tslot);
@@ -555,6 +556,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = make_idesc_bf16(256, BN, g.a_mn_major, g.b_mn_major);
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t a_lbo = g.a_mn_major ? 8192 : 16, b_lbo = g.b_mn_major ? 8192 : 16;
+      const uint32_t a_step = g.a_mn_major ? (2048 >> 4) : (32 >> 4), b_step = g.b_mn_major ? (2048 >> 4) : (32 >> 4);
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
@@ -576,13 +580,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
+          uint32_t a_lo = smem_desc_lo(sa, a_lbo), b_lo = smem_desc_lo(sb, b_lbo);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = g.a_mn_major ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                             : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = g.b_mn_major ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                             : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16_pair(d_tmem, da, db, idesc, accumulate);
+            umma_bf16_pair_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+            a_lo += a_step; b_lo += b_step;
             accumulate = 1;
           }
           umma_commit_pair_all(smem_u32(&empty_bar[s]), 0x3);     // frees the stage in both CTAs
