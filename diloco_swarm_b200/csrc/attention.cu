@@ -1,4 +1,4 @@
-// Causal flash attention forward on tcgen05 tensor cores, head size 64.
+// Causal flash attention forward on tcgen05 tensor cores, head size 64 or 32.
 //
 // Replaces the reference's F.scaled_dot_product_attention(q, k, v, is_causal=True)
 // (src/model.py:66-67).  Input is the packed [B*T, 3*d] output of the QKV
@@ -16,6 +16,11 @@
 // K/V tiles are double buffered; two CTAs fit on an SM (112 KB shared memory,
 // 256 TMEM columns each), so one CTA's MMAs run under the other's softmax.
 // Only kv tiles up to the diagonal are visited; the diagonal tile is masked.
+//
+// Head size 32 (the 4-head, 128-wide test model) runs the same tiles: its tensor maps describe the matrix as
+// (32 columns, head, row) and the 64-column box reaches past the head, so TMA fills the right half of each
+// operand tile with zeros.  Q K^T and dO V^T are unchanged by the zero columns, the output tiles get zero
+// right halves, and the epilogues write the first 32 columns only.
 #include <cuda.h>
 #include "ptx.cuh"
 #include "dswarm.h"
@@ -26,6 +31,14 @@ int make_tmap_bf16_2d(CUtensorMap* tm, const void* ptr, long long inner, long lo
                       int box_inner, int box_outer);
 int make_tmap_f32_2d(CUtensorMap* tm, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
                      int box_outer);
+int make_tmap_3d(CUtensorMap* tm, int is_f32, const void* ptr, long long inner, long long ncol, long long rows,
+                 long long ld, int box_inner, int box_rows);
+
+// [128 x 64] operand tile of column block `cb` (= part * heads + head) at `row`.
+__device__ __forceinline__ void att_load_tile(void* dst, const CUtensorMap* tm, uint64_t* bar, int hs, int cb, int row) {
+  if (hs == 64) tma_load_2d(dst, tm, bar, cb * 64, row);
+  else          tma_load_3d(dst, tm, bar, 0, cb, row);
+}
 
 // Optional in-kernel timeline for tuning: when a trace buffer is registered (dsw_attention_set_trace),
 // CTA (0,0) stores %globaltimer values at its phase boundaries: [0,256) row-warp 0, [256,512) MMA thread.
@@ -69,7 +82,8 @@ __device__ __forceinline__ uint32_t p_offset(int row, int col) {
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
-                     float* __restrict__ lse_out, int T, int nh, float scale_log2, int* status, long long* trace) {
+                     float* __restrict__ lse_out, int T, int nh, int hs, float scale_log2, int* status,
+                     long long* trace) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023) {            // swizzled operand tiles need 1024-byte alignment
@@ -91,7 +105,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   const int qi = gridDim.x - 1 - blockIdx.x;          // heavy (late) query tiles first
   const int bh = blockIdx.y;
   const int b = bh / nh, h = bh - b * nh;
-  const int d = nh * ATT_HS;
+  const int d = nh * hs;
   const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
   const int n_kv = qi + 1;
   long long* tr = (blockIdx.x == 0 && blockIdx.y == 0) ? trace : nullptr;
@@ -121,14 +135,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
       mbar_expect_tx(q_full, ATT_TILE_BYTES);
-      tma_load_2d(smem + AttSmem::Q_OFF, &tmap_qkv, q_full, h * ATT_HS, row0);
+      att_load_tile(smem + AttSmem::Q_OFF, &tmap_qkv, q_full, hs, h, row0);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status)) break;
         mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
         const int kvrow = b * T + j * ATT_BK;
-        tma_load_2d(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], d + h * ATT_HS, kvrow);
-        tma_load_2d(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], 2 * d + h * ATT_HS, kvrow);
+        att_load_tile(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, nh + h, kvrow);
+        att_load_tile(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, 2 * nh + h, kvrow);
       }
     }
   } else if (warp == 4) {
@@ -273,12 +287,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
         for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
       }
       const float inv = 1.f / l;
-      __nv_bfloat16* dst = out + (long long)(row0 + r) * d + h * ATT_HS;
+      __nv_bfloat16* dst = out + (long long)(row0 + r) * d + h * hs;
 #pragma unroll
       for (int i = 0; i < ATT_HS; i += 8)
-        *reinterpret_cast<uint4*>(dst + i) =
-            make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                       pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+        if (i < hs)
+          *reinterpret_cast<uint4*>(dst + i) =
+              make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
+                         pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
       // natural-log LSE of the scaled scores
       lse_out[(long long)bh * T + qi * ATT_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
     }
@@ -316,18 +331,21 @@ struct AttBwdSmem {
   static constexpr int TOTAL = BAR_OFF + 128 + 1024;
 };
 
-// D[bh, t] = sum_c dO[t, h*64 + c] * O[t, h*64 + c]; one warp per (row, head)
+// D[bh, t] = sum_c dO[t, h*hs + c] * O[t, h*hs + c]; one warp per (row, head)
 __global__ void __launch_bounds__(256)
 attention_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                          float* __restrict__ D, int B, int T, int nh) {
+                          float* __restrict__ D, int B, int T, int nh, int hs) {
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int total = B * T * nh;
   if (gw >= total) return;
   const int row = gw / nh, h = gw - row * nh;
-  const long long off = (long long)row * nh * ATT_HS + h * ATT_HS + lane * 2;
-  const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(out + off));
-  const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + off));
-  float v = a.x * g.x + a.y * g.y;
+  const long long off = (long long)row * nh * hs + h * hs + lane * 2;
+  float v = 0.f;
+  if (lane * 2 < hs) {
+    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(out + off));
+    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + off));
+    v = a.x * g.x + a.y * g.y;
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   if (lane == 0) {
@@ -357,7 +375,7 @@ constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 2);
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
                      const __grid_constant__ CUtensorMap tmap_dq, const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
-                     float* __restrict__ dq_acc, int T, int nh, float scale, int* status, long long* trace) {
+                     float* __restrict__ dq_acc, int T, int nh, int hs, float scale, int* status, long long* trace) {
   using L = AttBwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -376,7 +394,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   const int j = blockIdx.x;                      // kv tile; tile 0 has the most query tiles and starts first
   const int bh = blockIdx.y;
   const int b = bh / nh, h = bh - b * nh;
-  const int d = nh * ATT_HS;
+  const int d = nh * hs;
   const int nq = T / ATT_BQ;
   const int steps = nq - j;
   const float scale_log2 = scale * 1.4426950408889634f;
@@ -411,15 +429,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       tma_prefetch_desc(&tmap_do);
       const int kvrow = b * T + j * ATT_BK;
       mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
-      tma_load_2d(smem + L::K_OFF, &tmap_qkv, kv_full, d + h * ATT_HS, kvrow);
-      tma_load_2d(smem + L::V_OFF, &tmap_qkv, kv_full, 2 * d + h * ATT_HS, kvrow);
+      att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
+      att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
       for (int it = 0; it < steps; ++it) {
         const int s = it & 1;
         if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, status)) break;
         mbar_expect_tx(&q_full[s], 2 * ATT_TILE_BYTES);
         const int qrow = b * T + (j + it) * ATT_BQ;
-        tma_load_2d(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], h * ATT_HS, qrow);
-        tma_load_2d(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], h * ATT_HS, qrow);
+        att_load_tile(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], hs, h, qrow);
+        att_load_tile(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], hs, h, qrow);
       }
     }
   } else if (warp == MMA_WARP) {
@@ -498,12 +516,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (elected) {
         const int row_g = b * T + (j + it) * ATT_BQ;
+        if (hs == 64) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                       ::"l"(&tmap_dq), "r"(h * ATT_HS + hh * 32), "r"(row_g),
-                         "r"(smem_u32(smem + L::DQ_OFF + hh * ATT_TILE_BYTES))
+          for (int hh = 0; hh < 2; ++hh)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(&tmap_dq), "r"(h * ATT_HS + hh * 32), "r"(row_g),
+                           "r"(smem_u32(smem + L::DQ_OFF + hh * ATT_TILE_BYTES))
+                         : "memory");
+        } else {          // 32 columns per head: the first staging half is the whole dQ tile
+          asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                       ::"l"(&tmap_dq), "r"(0), "r"(h), "r"(row_g), "r"(smem_u32(smem + L::DQ_OFF))
                        : "memory");
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
       return true;
@@ -558,12 +582,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     if (ok && drain_dq(steps - 1)) {
       if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
       // dV and dK rows of this kv tile (TMEM lane = kv row)
-      __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * ATT_HS;
+      __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * hs;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tm_dk : tm_dv;
         __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d) + half * 32;
-        {
+        if (half * 32 < hs) {
           uint32_t v[32];
           tmem_ld_32x32(src + lane_addr + half * 32, v);
           tmem_ld_wait();
@@ -595,14 +619,15 @@ static long long* g_att_trace = nullptr;
 // Register (or clear, with nullptr) a device buffer of 512 int64 for the in-kernel timeline.
 extern "C" int dsw_attention_set_trace(long long* buf) { g_att_trace = buf; return 0; }
 
-// qkv: bf16 [B*T, 3*nh*64]; out: bf16 [B*T, nh*64]; lse: fp32 [B*nh*T].
-// Requires hs == 64 and T a multiple of 128.
+// qkv: bf16 [B*T, 3*nh*hs]; out: bf16 [B*T, nh*hs]; lse: fp32 [B*nh*T].
+// Requires hs == 64 or 32 and T a multiple of 128.
 extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int nh, int hs, float scale,
                                  int* status, cudaStream_t st) {
-  if (hs != ATT_HS || T % ATT_BQ != 0) return -10;
+  if ((hs != 64 && hs != 32) || T % ATT_BQ != 0) return -10;
   const int d = nh * hs;
   CUtensorMap tm;
-  int rc = make_tmap_bf16_2d(&tm, qkv, 3LL * d, (long long)B * T, 3LL * d, 64, 128);
+  int rc = hs == 64 ? make_tmap_bf16_2d(&tm, qkv, 3LL * d, (long long)B * T, 3LL * d, 64, 128)
+                    : make_tmap_3d(&tm, 0, qkv, hs, 3LL * nh, (long long)B * T, 3LL * d, 64, 128);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -612,7 +637,7 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
     attr_set = true;
   }
   dim3 grid(T / ATT_BQ, B * nh);
-  attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh,
+  attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh, hs,
                                                                    scale * 1.4426950408889634f, status, g_att_trace);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -622,15 +647,20 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
 extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
                                  float* dq_acc, float* Dvec, int B, int T, int nh, int hs, float scale, int* status,
                                  cudaStream_t st) {
-  if (hs != ATT_HS || T % ATT_BQ != 0) return -10;
+  if ((hs != 64 && hs != 32) || T % ATT_BQ != 0) return -10;
   const int d = nh * hs;
-  CUtensorMap tq, tdo;
-  int rc = make_tmap_bf16_2d(&tq, qkv, 3LL * d, (long long)B * T, 3LL * d, 64, 128);
-  if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tdo, dout, d, (long long)B * T, d, 64, 128);
-  if (rc) return rc;
-  CUtensorMap tdq;
-  rc = make_tmap_f32_2d(&tdq, dq_acc, d, (long long)B * T, d, 32, 128);
+  const long long rows = (long long)B * T;
+  CUtensorMap tq, tdo, tdq;
+  int rc;
+  if (hs == 64) {
+    rc = make_tmap_bf16_2d(&tq, qkv, 3LL * d, rows, 3LL * d, 64, 128);
+    if (!rc) rc = make_tmap_bf16_2d(&tdo, dout, d, rows, d, 64, 128);
+    if (!rc) rc = make_tmap_f32_2d(&tdq, dq_acc, d, rows, d, 32, 128);
+  } else {
+    rc = make_tmap_3d(&tq, 0, qkv, hs, 3LL * nh, rows, 3LL * d, 64, 128);
+    if (!rc) rc = make_tmap_3d(&tdo, 0, dout, hs, nh, rows, d, 64, 128);
+    if (!rc) rc = make_tmap_3d(&tdq, 1, dq_acc, hs, nh, rows, d, 32, 128);
+  }
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -642,10 +672,10 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   if (cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * T * d, st) != cudaSuccess) return -4;
   const long long warps = (long long)B * T * nh;
   attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh);
+      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh, hs);
   dim3 grid(T / ATT_BK, B * nh);
   attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
-                                                                     T, nh, scale, status, g_att_trace);
+                                                                     T, nh, hs, scale, status, g_att_trace);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

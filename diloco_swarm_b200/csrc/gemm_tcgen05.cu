@@ -679,6 +679,23 @@ int make_tmap_f32_2d(CUtensorMap* tm, const void* ptr, long long inner, long lon
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
 }
 
+// 3-D map over a [rows, ncol * inner] matrix seen as (inner, ncol, rows), 128-byte swizzle.  The box may be wider
+// than `inner`: the columns past it are out of bounds, so loads fill them with zeros and stores skip them.
+int make_tmap_3d(CUtensorMap* tm, int is_f32, const void* ptr, long long inner, long long ncol, long long rows,
+                 long long ld, int box_inner, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  const cuuint64_t es = is_f32 ? 4 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)ncol, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)inner * es, (cuuint64_t)ld * es};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, 1, (cuuint32_t)box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
 static int g_num_sms = 0;
 
 template <int BN, int NSTAGE>

@@ -26,12 +26,13 @@ BF16 = torch.bfloat16
 
 
 def _native_available(hs: int, T: int) -> bool:
-    """The sm_100a kernels cover head size 64 (GPT-2 small to xl) and sequence
-    lengths that are multiples of 128; other shapes use the library kernel."""
+    """The sm_100a kernels cover head size 64 (GPT-2 small to xl) and 32 (the
+    4-head, 128-wide test model) at sequence lengths that are multiples of 128;
+    other shapes use the library kernel."""
     if os.environ.get("DSWARM_ATTENTION", "native") == "sdpa":
         return False
     lib = cuda_lib()
-    return hs == 64 and T % 128 == 0 and hasattr(lib, "dsw_attention_fwd") and hasattr(lib, "dsw_attention_bwd")
+    return hs in (32, 64) and T % 128 == 0 and hasattr(lib, "dsw_attention_fwd") and hasattr(lib, "dsw_attention_bwd")
 
 
 class AttnCtx:

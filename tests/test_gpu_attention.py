@@ -19,12 +19,15 @@ def _ref(qkv, B, T, nh):
     return o.transpose(1, 2).reshape(B * T, d), lse
 
 
-@pytest.mark.parametrize("B,T,nh", [(1, 128, 1), (2, 256, 3), (1, 1024, 2)])
-def test_attention_forward(B, T, nh, monkeypatch):
+SHAPES = [(1, 128, 1, 64), (2, 256, 3, 64), (1, 1024, 2, 64), (1, 128, 1, 32), (2, 384, 4, 32), (1, 1024, 3, 32)]
+
+
+@pytest.mark.parametrize("B,T,nh,hs", SHAPES)
+def test_attention_forward(B, T, nh, hs, monkeypatch):
     monkeypatch.setenv("DSWARM_ATTENTION", "native")
     from diloco_swarm_b200.ops.attention import attention_fwd
     torch.manual_seed(0)
-    qkv = (torch.randn(B * T, 3 * nh * 64, device="cuda")).to(torch.bfloat16)
+    qkv = (torch.randn(B * T, 3 * nh * hs, device="cuda")).to(torch.bfloat16)
     out, ctx = attention_fwd(qkv, B, T, nh)
     torch.cuda.synchronize()
     assert ctx.native
@@ -33,20 +36,20 @@ def test_attention_forward(B, T, nh, monkeypatch):
     assert (ctx.lse.view(B, nh, T) - lse).abs().max() < 2e-2
 
 
-@pytest.mark.parametrize("B,T,nh", [(1, 128, 1), (2, 256, 3), (1, 1024, 2)])
-def test_attention_backward(B, T, nh, monkeypatch):
+@pytest.mark.parametrize("B,T,nh,hs", SHAPES)
+def test_attention_backward(B, T, nh, hs, monkeypatch):
     monkeypatch.setenv("DSWARM_ATTENTION", "native")
     from diloco_swarm_b200.ops.attention import attention_bwd, attention_fwd
     torch.manual_seed(1)
-    qkv = (torch.randn(B * T, 3 * nh * 64, device="cuda")).to(torch.bfloat16)
-    dout = (torch.randn(B * T, nh * 64, device="cuda")).to(torch.bfloat16)
+    qkv = (torch.randn(B * T, 3 * nh * hs, device="cuda")).to(torch.bfloat16)
+    dout = (torch.randn(B * T, nh * hs, device="cuda")).to(torch.bfloat16)
     out, ctx = attention_fwd(qkv, B, T, nh)
     dqkv = attention_bwd(dout, ctx)
     torch.cuda.synchronize()
     x = qkv.float().requires_grad_(True)
     ref, _ = _ref(x, B, T, nh)
     ref.backward(dout.float())
-    d = nh * 64
+    d = nh * hs
     for name, sl in (("dq", slice(0, d)), ("dk", slice(d, 2 * d)), ("dv", slice(2 * d, 3 * d))):
         got, want = dqkv[:, sl].float(), x.grad[:, sl]
         err = (got - want).abs().max().item()
