@@ -35,8 +35,12 @@ def _setter(name):
     return fn
 
 
-def gemm_timeline(M, N, Kd, bn=256):
+def gemm_timeline(M, N, Kd, bn=256, ksub=2):
     set_trace = _setter("dsw_gemm_set_trace")
+    if bn == 512:
+        set_ksub = cuda_lib().dsw_gemm_set_pair_ksub
+        set_ksub.argtypes, set_ksub.restype = [ctypes.c_int], ctypes.c_int
+        set_ksub(ksub)
     a, b = _bf(M, Kd), _bf(N, Kd)
     for _ in range(3):
         K.gemm(a, b, bn=bn)
@@ -51,9 +55,11 @@ def gemm_timeline(M, N, Kd, bn=256):
     mmas = [t[i + 2] - t[i + 1] for i in range(0, len(t) - 3, 4)]
     commits = [t[i + 3] - t[i + 2] for i in range(0, len(t) - 3, 4)]
     period = [t[i + 4] - t[i] for i in range(0, len(t) - 4, 4)]
-    print(f"gemm {M}x{N}x{Kd} (one-CTA kernel, bn={bn}): {len(waits)} k-blocks of CTA 0")
-    for name, v in (("full-barrier wait", waits), ("4 x tcgen05.mma", mmas), ("tcgen05.commit", commits),
-                    ("k-block period", period)):
+    kind = f"CTA-pair kernel, {ksub} k-block(s) per barrier" if bn == 512 else f"one-CTA kernel, bn={bn}"
+    n_mma = 4 * ksub if bn == 512 else 4
+    print(f"gemm {M}x{N}x{Kd} ({kind}): {len(waits)} barrier periods of CTA 0")
+    for name, v in (("full-barrier wait", waits), (f"{n_mma} x tcgen05.mma", mmas), ("tcgen05.commit", commits),
+                    ("period", period)):
         print(f"  {name:18s} median {statistics.median(v):6.0f} ns   mean {statistics.mean(v):7.1f} ns   max {max(v)} ns")
     print("  first periods:", period[:28])
 
@@ -95,12 +101,14 @@ def main():
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=768)
+    ap.add_argument("--bn", type=int, default=256, choices=[128, 256, 512], help="512 = the CTA-pair kernel")
+    ap.add_argument("--ksub", type=int, default=2, choices=[1, 2], help="CTA-pair kernel: k-blocks per barrier pair")
     ap.add_argument("--B", type=int, default=16)
     ap.add_argument("--T", type=int, default=1024)
     ap.add_argument("--heads", type=int, default=12)
     a = ap.parse_args()
     if a.kernel == "gemm":
-        gemm_timeline(a.M, a.N, a.K)
+        gemm_timeline(a.M, a.N, a.K, a.bn, a.ksub)
     else:
         attention_timeline(a.B, a.T, a.heads)
 

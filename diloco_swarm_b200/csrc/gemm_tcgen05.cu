@@ -459,8 +459,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 //   empty[s]     in each CTA, released by one multicast tcgen05.commit of the leader
 //   acc_full[b]  in each CTA, same mechanism
 //   acc_empty[b] in the leader, one arrival per epilogue warp of both CTAs
+// KSUB k-blocks share one full/empty barrier pair (KSUB = 2: a stage is two 64-wide k-blocks, so the issuing
+// thread pays one barrier wait and one commit per eight MMAs instead of per four).
 constexpr int PAIR_BN = 256;
-constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGES = 6;          // k-blocks resident in shared memory
 struct PairSmem {
   static constexpr int A_BYTES = 128 * BK * 2;
   static constexpr int B_BYTES = 128 * BK * 2;
@@ -470,10 +472,12 @@ struct PairSmem {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
 };
 
+template <int KSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
   using L = PairSmem;
-  constexpr int NSTAGE = PAIR_STAGES;
+  constexpr int NSTAGE = PAIR_STAGES / KSUB;          // barrier pairs; each covers KSUB k-blocks
+  static_assert(PAIR_STAGES % KSUB == 0, "stages must divide into groups");
   constexpr int BN = PAIR_BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -528,26 +532,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int n0 = (rem / tiles_m) * BN + int(rank) * 128;      // this CTA's columns of B
         const int kb0 = ks * kb_per_split;
         const int kb1 = min(kb_total, kb0 + kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; kb += KSUB, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
+          const int nsub = min(KSUB, kb1 - kb);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, g.status)) { ok = false; break; }
-          uint8_t* sa = smem + s * L::STAGE_BYTES;
-          uint8_t* sb = sa + L::A_BYTES;
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[s]), 0);
-          mbar_expect_tx_cluster(full_leader, L::STAGE_BYTES);
-          const int k0 = kb * BK;
-          if (!g.a_mn_major) {
-            tma_load_2d_pair(sa, &tmap_a, full_leader, k0, m0);
-          } else {
-            tma_load_2d_pair(sa, &tmap_a, full_leader, m0, k0);
-            tma_load_2d_pair(sa + 8192, &tmap_a, full_leader, m0 + 64, k0);
-          }
-          if (!g.b_mn_major) {
-            tma_load_2d_pair(sb, &tmap_b, full_leader, k0, n0);
-          } else {
-            tma_load_2d_pair(sb, &tmap_b, full_leader, n0, k0);
-            tma_load_2d_pair(sb + 8192, &tmap_b, full_leader, n0 + 64, k0);
+          mbar_expect_tx_cluster(full_leader, nsub * L::STAGE_BYTES);
+          for (int sub = 0; sub < nsub; ++sub) {
+            uint8_t* sa = smem + (s * KSUB + sub) * L::STAGE_BYTES;
+            uint8_t* sb = sa + L::A_BYTES;
+            const int k0 = (kb + sub) * BK;
+            if (!g.a_mn_major) {
+              tma_load_2d_pair(sa, &tmap_a, full_leader, k0, m0);
+            } else {
+              tma_load_2d_pair(sa, &tmap_a, full_leader, m0, k0);
+              tma_load_2d_pair(sa + 8192, &tmap_a, full_leader, m0 + 64, k0);
+            }
+            if (!g.b_mn_major) {
+              tma_load_2d_pair(sb, &tmap_b, full_leader, k0, n0);
+            } else {
+              tma_load_2d_pair(sb, &tmap_b, full_leader, n0, k0);
+              tma_load_2d_pair(sb + 8192, &tmap_b, full_leader, n0 + 64, k0);
+            }
           }
         }
       }
@@ -562,6 +569,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
+      long long* tr = blockIdx.x == 0 ? g.trace : nullptr;
+      int tslot = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
         const int ks = tile / (tiles_m * tiles_n);
         const int kb0 = ks * kb_per_split;
@@ -572,22 +581,32 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * BN;
         uint32_t accumulate = 0;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; kb += KSUB, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
+          const int nsub = min(KSUB, kb1 - kb);
+          GEMM_TRACE(tr, tslot);
           if (!mbar_wait(&full_bar[s], ph, abort_flag, g.status)) { ok = false; break; }
+          GEMM_TRACE(tr, tslot);
           // no tcgen05 fence here: the operands were written by TMA (async proxy) and the mbarrier
           // wait orders them; a fence per k-block only delays the next MMAs behind the previous ones
-          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint32_t sb = sa + L::A_BYTES;
-          uint32_t a_lo = smem_desc_lo(sa, a_lbo), b_lo = smem_desc_lo(sb, b_lbo);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16_pair_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
-            a_lo += a_step; b_lo += b_step;
-            accumulate = 1;
+          for (int sub = 0; sub < KSUB; ++sub) {
+            if (sub < nsub) {
+              const uint32_t sa = smem_u32(smem + (s * KSUB + sub) * L::STAGE_BYTES);
+              const uint32_t sb = sa + L::A_BYTES;
+              uint32_t a_lo = smem_desc_lo(sa, a_lbo), b_lo = smem_desc_lo(sb, b_lbo);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                umma_bf16_pair_lohi(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate);
+                a_lo += a_step; b_lo += b_step;
+                accumulate = 1;
+              }
+            }
           }
+          GEMM_TRACE(tr, tslot);
           umma_commit_pair_all(smem_u32(&empty_bar[s]), 0x3);     // frees the stage in both CTAs
+          GEMM_TRACE(tr, tslot);
         }
         if (ok) {
           umma_commit_pair_all(smem_u32(&acc_full[ab]), 0x3);
@@ -716,11 +735,15 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
 }
 
 
+static int g_pair_ksub = 2;
+
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int max_ctas, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL) !=
+            cudaSuccess)
       return -2;
     attr_set = true;
   }
@@ -728,13 +751,21 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   int pairs = g_num_sms / 2;
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (pairs > tiles) pairs = tiles;
-  gemm_pair_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, st>>>(ta, tb, g);
+  if (g_pair_ksub == 2) gemm_pair_kernel<2><<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, st>>>(ta, tb, g);
+  else                  gemm_pair_kernel<1><<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, st>>>(ta, tb, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 }  // namespace dsw
 
 using namespace dsw;
+
+// Tuning knob of the CTA-pair kernel: k-blocks per barrier pair (1 or 2).
+extern "C" int dsw_gemm_set_pair_ksub(int ksub) {
+  if (ksub != 1 && ksub != 2) return -10;
+  dsw::g_pair_ksub = ksub;
+  return 0;
+}
 
 static long long* g_gemm_trace = nullptr;
 // Register (or clear) a device buffer of 512 int64 for the one-CTA kernel's MMA-thread timeline.
@@ -787,6 +818,7 @@ extern "C" int dsw_load_gemm() {
   cudaFuncAttributes a;
   if (cudaFuncGetAttributes(&a, gemm_kernel<256, 4>) != cudaSuccess) return -1;
   if (cudaFuncGetAttributes(&a, gemm_kernel<128, 6>) != cudaSuccess) return -1;
-  if (cudaFuncGetAttributes(&a, gemm_pair_kernel) != cudaSuccess) return -1;
+  if (cudaFuncGetAttributes(&a, gemm_pair_kernel<1>) != cudaSuccess) return -1;
+  if (cudaFuncGetAttributes(&a, gemm_pair_kernel<2>) != cudaSuccess) return -1;
   return 0;
 }
