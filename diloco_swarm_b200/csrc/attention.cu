@@ -98,23 +98,28 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   uint64_t* p_full = bars + 6;        // P written to smem, S consumed (4 warps arrive)
   uint64_t* o_full = bars + 7;        // O_j ready in TMEM
   uint64_t* o_free = bars + 8;        // O_j consumed (4 warps arrive)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* s_free = bars + 9;        // S_j read out of TMEM for the last time (4 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qi = gridDim.x - 1 - blockIdx.x;          // heavy (late) query tiles first
-  const int bh = blockIdx.y;
+  // 1-D grid ordered by work: all (batch, head) pairs of the last query tile (the most kv tiles) first, the
+  // first query tile last, so the tail of the launch is made of the short CTAs
+  const int n_bh = gridDim.x / (T / ATT_BQ);
+  const int qi = T / ATT_BQ - 1 - blockIdx.x / n_bh;
+  const int bh = blockIdx.x % n_bh;
   const int b = bh / nh, h = bh - b * nh;
   const int d = nh * hs;
   const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
   const int n_kv = qi + 1;
-  long long* tr = (blockIdx.x == 0 && blockIdx.y == 0) ? trace : nullptr;
+  long long* tr = blockIdx.x == 0 ? trace : nullptr;
   int tslot = 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_free, 4);
+    mbar_init(s_free, 4);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -150,17 +155,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);
-      const uint32_t sq = smem_u32(smem + AttSmem::Q_OFF);
-      const uint32_t sp = smem_u32(smem + AttSmem::P_OFF);
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(smem_u32(smem + AttSmem::Q_OFF), 16);
+      const uint32_t p_lo = smem_desc_lo(smem_u32(smem + AttSmem::P_OFF), 16);
       bool ok = mbar_wait(q_full, 0, abort_flag, status);
       auto issue_s = [&](int jj) -> bool {          // S_jj = Q K_jj^T into the (single) score buffer
         const int st = jj & 1;
         if (!mbar_wait(&kv_full[st], (jj >> 1) & 1, abort_flag, status)) return false;
-        const uint32_t sk = smem_u32(smem + AttSmem::K_OFF + st * ATT_TILE_BYTES);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(smem + AttSmem::K_OFF + st * ATT_TILE_BYTES), 16);
 #pragma unroll
         for (int k = 0; k < ATT_HS / 16; ++k)
-          umma_bf16(tmem_s, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), idesc_s,
-                    k > 0);
+          umma_bf16_lohi(tmem_s, q_lo + k * 2, k_lo + k * 2, desc_hi, idesc_s, k > 0);
         umma_commit(s_full);
         ATT_TRACE(tr, 256, tslot);          // S issued
         return true;
@@ -168,20 +173,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
-        const uint32_t sv = smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES);
-        // P_j is in shared memory and S_j has been consumed
+        const uint32_t v_lo = smem_desc_lo(smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES), ATT_TILE_BYTES);
+        // The next score tile goes first, as soon as the softmax warps have read S_j for the last time
+        // (they are still turning its last columns into P_j): they need S_{j+1} next, while the P V
+        // product is only folded in after their first pass over it.
+        if (j + 1 < n_kv) {
+          if (!mbar_wait(s_free, j & 1, abort_flag, status)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_s(j + 1)) { ok = false; break; }
+        }
+        // P_j is in shared memory
         if (!mbar_wait(p_full, j & 1, abort_flag, status)) { ok = false; break; }
         ATT_TRACE(tr, 256, tslot);          // P ready
-        tc_fence_after();
-        // the next score tile goes first: the softmax warps need it next, while the P V product
-        // is only folded in after their first pass over it
-        if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
         if (j > 0 && !mbar_wait(o_free, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < ATT_BK / 16; ++k)
-          umma_bf16(tmem_o, make_smem_desc(sp + (k >> 2) * ATT_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(sv + k * 2048, ATT_TILE_BYTES, 1024), idesc_o, k > 0);
+        for (int k = 0; k < ATT_BK / 16; ++k)          // P: 32 bytes along the row per step, second k-block after 4
+          umma_bf16_lohi(tmem_o, p_lo + (k >> 2) * (ATT_TILE_BYTES >> 4) + (k & 3) * 2, v_lo + k * (2048 >> 4), desc_hi,
+                         idesc_o, k > 0);
         umma_commit(o_full);
         umma_commit(&kv_empty[s]);
         ATT_TRACE(tr, 256, tslot);          // PV issued
@@ -252,6 +261,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
+          if (c == 3) {            // the whole score row is in registers: the score buffer may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
+          }
           float p[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -391,14 +405,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x;                      // kv tile; tile 0 has the most query tiles and starts first
-  const int bh = blockIdx.y;
+  // 1-D grid ordered by work: kv tile 0 (the most query tiles) of every (batch, head) first
+  const int n_bh = gridDim.x / (T / ATT_BK);
+  const int j = blockIdx.x / n_bh;
+  const int bh = blockIdx.x % n_bh;
   const int b = bh / nh, h = bh - b * nh;
   const int d = nh * hs;
   const int nq = T / ATT_BQ;
   const int steps = nq - j;
   const float scale_log2 = scale * 1.4426950408889634f;
-  long long* tr = (blockIdx.x == 0 && blockIdx.y == 0) ? trace : nullptr;
+  long long* tr = blockIdx.x == 0 ? trace : nullptr;
   int tslot = 0;
 
   if (threadIdx.x == 0) {
@@ -446,21 +462,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);      // Q K^T and dO V^T
       const uint32_t id_t = make_idesc_bf16(128, 64, 1, 1);       // P^T dO and dS^T Q : A M-major, B N-major
       const uint32_t id_q = make_idesc_bf16(128, 64, 0, 1);       // dS K : A K-major, B N-major
-      const uint32_t sk = smem_u32(smem + L::K_OFF), sv = smem_u32(smem + L::V_OFF);
-      const uint32_t sp = smem_u32(smem + L::P_OFF), sds = smem_u32(smem + L::DS_OFF);
+      // Descriptor low words: K-major operands (leading offset 16) step 32 bytes per MMA, M/N-major ones
+      // (leading offset = one tile) step 16 rows of 128 bytes; the high word is the same for all.
+      constexpr uint32_t KSTEP = 32 >> 4, MNSTEP = 2048 >> 4, TILE16 = ATT_TILE_BYTES >> 4;
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t k_km = smem_desc_lo(smem_u32(smem + L::K_OFF), 16), v_km = smem_desc_lo(smem_u32(smem + L::V_OFF), 16);
+      const uint32_t k_mn = smem_desc_lo(smem_u32(smem + L::K_OFF), ATT_TILE_BYTES);
+      const uint32_t p_mn = smem_desc_lo(smem_u32(smem + L::P_OFF), ATT_TILE_BYTES);
+      const uint32_t ds_mn = smem_desc_lo(smem_u32(smem + L::DS_OFF), ATT_TILE_BYTES);
+      const uint32_t ds_km = smem_desc_lo(smem_u32(smem + L::DS_OFF), 16);
       bool ok = mbar_wait(kv_full, 0, abort_flag, status);
       for (int it = 0; it < steps && ok; ++it) {
         const int s = it & 1;
         const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
         const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
+        const uint32_t q_km = smem_desc_lo(sq, 16), do_km = smem_desc_lo(sdo, 16);
+        const uint32_t q_mn = smem_desc_lo(sq, ATT_TILE_BYTES), do_mn = smem_desc_lo(sdo, ATT_TILE_BYTES);
         if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16(tm_s, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), id_s, k > 0);
+        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_s, q_km + k * KSTEP, k_km + k * KSTEP, desc_hi, id_s, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16(tm_dp, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), id_s, k > 0);
+        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_dp, do_km + k * KSTEP, v_km + k * KSTEP, desc_hi, id_s, k > 0);
         umma_commit(sdp_full);
         ATT_TRACE(tr, 256, tslot);          // S, dP issued
         if (!mbar_wait(pds_full, it & 1, abort_flag, status)) { ok = false; break; }
@@ -469,16 +492,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
-          umma_bf16(tm_dv, make_smem_desc(sp + k * 2048, ATT_TILE_BYTES, 1024),
-                    make_smem_desc(sdo + k * 2048, ATT_TILE_BYTES, 1024), id_t, (it > 0 || k > 0));
+          umma_bf16_lohi(tm_dv, p_mn + k * MNSTEP, do_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
 #pragma unroll
         for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
-          umma_bf16(tm_dk, make_smem_desc(sds + k * 2048, ATT_TILE_BYTES, 1024),
-                    make_smem_desc(sq + k * 2048, ATT_TILE_BYTES, 1024), id_t, (it > 0 || k > 0));
+          umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
 #pragma unroll
         for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
-          umma_bf16(tm_dq, make_smem_desc(sds + (k >> 2) * ATT_TILE_BYTES + (k & 3) * 32, 16, 1024),
-                    make_smem_desc(sk + k * 2048, ATT_TILE_BYTES, 1024), id_q, k > 0);
+          umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
         umma_commit(dq_full);
         umma_commit(&q_empty[s]);
         ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
@@ -636,7 +656,7 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
       return -2;
     attr_set = true;
   }
-  dim3 grid(T / ATT_BQ, B * nh);
+  dim3 grid((T / ATT_BQ) * B * nh);
   attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh, hs,
                                                                    scale * 1.4426950408889634f, status, g_att_trace);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -673,7 +693,7 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   const long long warps = (long long)B * T * nh;
   attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh, hs);
-  dim3 grid(T / ATT_BK, B * nh);
+  dim3 grid((T / ATT_BK) * B * nh);
   attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
                                                                      T, nh, hs, scale, status, g_att_trace);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
