@@ -73,13 +73,14 @@ def attention_timeline(B, T, nh):
     torch.cuda.synchronize()
     tr = torch.zeros(512, dtype=torch.int64, device="cuda")
 
-    def show(title, row_labels, mma_labels):
+    def show(title, row_labels, mma_labels, mma_prefix=()):
         t = tr.cpu().tolist()
         row, mma = [x for x in t[:256] if x], [x for x in t[256:] if x]
         t0 = min(row + mma)
+        names = list(mma_prefix) + [mma_labels[i % len(mma_labels)] for i in range(len(mma_labels) * 4)]
         print(title)
         print("  row warp 0 :", " ".join(f"{row_labels[i % len(row_labels)]}={x - t0}" for i, x in enumerate(row[:len(row_labels) * 4])))
-        print("  MMA thread :", " ".join(f"{mma_labels[i % len(mma_labels)]}={x - t0}" for i, x in enumerate(mma[:len(mma_labels) * 4])))
+        print("  MMA thread :", " ".join(f"{n}={x - t0}" for n, x in zip(names, mma)))
         print(f"  CTA span {max(row + mma) - t0} ns")
 
     set_trace(tr.data_ptr())
@@ -91,7 +92,8 @@ def attention_timeline(B, T, nh):
     attention_bwd(dout, ctx)
     torch.cuda.synchronize()
     show("attention backward, CTA (0,0) (kv tile 0: all query tiles), ns since first stamp",
-         ["start", "dQ_drained", "S_dP_ready", "P_dS_written"], ["S_dP_issued", "P_dS_ready", "dV_dK_dQ_issued"])
+         ["start", "S_dP_ready", "P_dS_in_regs", "dQ_drained_P_dS_written"],
+         ["P_dS_ready", "next_S_dP_issued", "dV_dK_dQ_issued"], mma_prefix=["S_dP_issued"])
     set_trace(None)
 
 

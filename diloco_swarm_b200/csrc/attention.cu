@@ -80,9 +80,17 @@ __device__ __forceinline__ uint32_t p_offset(int row, int col) {
   return kb * ATT_TILE_BYTES + row * 128 + ((((c >> 3) ^ (row & 7)) << 4) | ((c & 7) << 1));
 }
 
+// Work items of a persistent launch: item = (query or kv tile, batch*head), listed heaviest first; CTA c of G
+// takes items c, 2G-1-c, 2G+c, ... (a snake over the rounds), which evens out the tile counts per CTA.
+// Returns false when round r holds no item for this CTA.
+__device__ __forceinline__ bool att_item(int r, int c, int G, int total, int& idx) {
+  idx = r * G + ((r & 1) ? G - 1 - c : c);
+  return idx < total;
+}
+
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
-                     float* __restrict__ lse_out, int T, int nh, int hs, float scale_log2, int* status,
+                     float* __restrict__ lse_out, int T, int nh, int n_bh, int hs, float scale_log2, int* status,
                      long long* trace) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -90,33 +98,32 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_BAD_ARG);
     return;
   }
+  // Every barrier below completes one phase per kv tile (q_full / q_empty: per work item), counted over the
+  // whole life of the CTA: g is the number of tiles, w the number of items this CTA has finished.
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR_OFF);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* q_full = bars;            // Q of the item loaded
+  uint64_t* kv_full = bars + 1;       // 2 stages
+  uint64_t* kv_empty = bars + 3;      // 2 stages
   uint64_t* s_full = bars + 5;        // S ready in TMEM
-  uint64_t* p_full = bars + 6;        // P written to smem, S consumed (4 warps arrive)
-  uint64_t* o_full = bars + 7;        // O_j ready in TMEM
-  uint64_t* o_free = bars + 8;        // O_j consumed (4 warps arrive)
-  uint64_t* s_free = bars + 9;        // S_j read out of TMEM for the last time (4 warps arrive)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* p_full = bars + 6;        // P written to smem (4 warps arrive)
+  uint64_t* o_full = bars + 7;        // P V ready in TMEM
+  uint64_t* o_free = bars + 8;        // P V folded into the output registers (4 warps arrive)
+  uint64_t* s_free = bars + 9;        // S read out of TMEM for the last time (4 warps arrive)
+  uint64_t* q_empty = bars + 10;      // all S products of the item done: Q may be overwritten
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid ordered by work: all (batch, head) pairs of the last query tile (the most kv tiles) first, the
-  // first query tile last, so the tail of the launch is made of the short CTAs
-  const int n_bh = gridDim.x / (T / ATT_BQ);
-  const int qi = T / ATT_BQ - 1 - blockIdx.x / n_bh;
-  const int bh = blockIdx.x % n_bh;
-  const int b = bh / nh, h = bh - b * nh;
+  const int nq = T / ATT_BQ;
+  const int total = nq * n_bh;
+  const int G = gridDim.x, cta = blockIdx.x;
+  const int rounds = (total + G - 1) / G;
   const int d = nh * hs;
-  const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
-  const int n_kv = qi + 1;
   long long* tr = blockIdx.x == 0 ? trace : nullptr;
   int tslot = 0;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 1); mbar_init(q_empty, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1); mbar_init(o_free, 4);
     mbar_init(s_free, 4);
@@ -139,15 +146,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
-      mbar_expect_tx(q_full, ATT_TILE_BYTES);
-      att_load_tile(smem + AttSmem::Q_OFF, &tmap_qkv, q_full, hs, h, row0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status)) break;
-        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
-        const int kvrow = b * T + j * ATT_BK;
-        att_load_tile(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, nh + h, kvrow);
-        att_load_tile(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, 2 * nh + h, kvrow);
+      uint32_t g = 0, w = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        int idx;
+        if (!att_item(r, cta, G, total, idx)) continue;
+        const int qi = nq - 1 - idx / n_bh, bh = idx % n_bh;
+        const int b = bh / nh, h = bh - b * nh;
+        if (w > 0 && !mbar_wait(q_empty, (w - 1) & 1, abort_flag, status)) break;
+        mbar_expect_tx(q_full, ATT_TILE_BYTES);
+        att_load_tile(smem + AttSmem::Q_OFF, &tmap_qkv, q_full, hs, h, b * T + qi * ATT_BQ);
+        for (int j = 0; j <= qi; ++j, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait(&kv_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+          mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+          const int kvrow = b * T + j * ATT_BK;
+          att_load_tile(smem + AttSmem::K_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, nh + h, kvrow);
+          att_load_tile(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &kv_full[s], hs, 2 * nh + h, kvrow);
+        }
+        ++w;
       }
     }
   } else if (warp == 4) {
@@ -158,139 +175,71 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(smem_u32(smem + AttSmem::Q_OFF), 16);
       const uint32_t p_lo = smem_desc_lo(smem_u32(smem + AttSmem::P_OFF), 16);
-      bool ok = mbar_wait(q_full, 0, abort_flag, status);
-      auto issue_s = [&](int jj) -> bool {          // S_jj = Q K_jj^T into the (single) score buffer
-        const int st = jj & 1;
-        if (!mbar_wait(&kv_full[st], (jj >> 1) & 1, abort_flag, status)) return false;
+      // S of global tile gt = Q K^T into the (single) score buffer; `first` / `last`: position in its item wi
+      auto issue_s = [&](uint32_t gt, uint32_t wi, bool first, bool last) -> bool {
+        if (first && !mbar_wait(q_full, wi & 1, abort_flag, status)) return false;
+        const int st = gt & 1;
+        if (!mbar_wait(&kv_full[st], (gt >> 1) & 1, abort_flag, status)) return false;
         const uint32_t k_lo = smem_desc_lo(smem_u32(smem + AttSmem::K_OFF + st * ATT_TILE_BYTES), 16);
 #pragma unroll
         for (int k = 0; k < ATT_HS / 16; ++k)
           umma_bf16_lohi(tmem_s, q_lo + k * 2, k_lo + k * 2, desc_hi, idesc_s, k > 0);
         umma_commit(s_full);
+        if (last) umma_commit(q_empty);
         ATT_TRACE(tr, 256, tslot);          // S issued
         return true;
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t v_lo = smem_desc_lo(smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES), ATT_TILE_BYTES);
-        // The next score tile goes first, as soon as the softmax warps have read S_j for the last time
-        // (they are still turning its last columns into P_j): they need S_{j+1} next, while the P V
-        // product is only folded in after their first pass over it.
-        if (j + 1 < n_kv) {
-          if (!mbar_wait(s_free, j & 1, abort_flag, status)) { ok = false; break; }
+      uint32_t g = 0, w = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        int idx;
+        if (!att_item(r, cta, G, total, idx)) continue;
+        const int n_kv = nq - idx / n_bh;
+        // the item after this one (its first score tile is issued during this item's last tile)
+        int next_n_kv = 0;
+        for (int r2 = r + 1, idx2; r2 < rounds; ++r2)
+          if (att_item(r2, cta, G, total, idx2)) { next_n_kv = nq - idx2 / n_bh; break; }
+        if (g == 0) ok = issue_s(0, 0, true, n_kv == 1);
+        for (int j = 0; j < n_kv && ok; ++j, ++g) {
+          const int s = g & 1;
+          const uint32_t v_lo = smem_desc_lo(smem_u32(smem + AttSmem::V_OFF + s * ATT_TILE_BYTES), ATT_TILE_BYTES);
+          // The next score tile goes first, as soon as the softmax warps have read this one for the last
+          // time (they are still turning its last columns into P): they need the next S next, while the
+          // P V product is only folded in after their first pass over it.
+          const bool more = j + 1 < n_kv;
+          if (more || next_n_kv > 0) {
+            if (!mbar_wait(s_free, g & 1, abort_flag, status)) { ok = false; break; }
+            tc_fence_after();
+            const bool okk = more ? issue_s(g + 1, w, false, j + 2 == n_kv) : issue_s(g + 1, w + 1, true, next_n_kv == 1);
+            if (!okk) { ok = false; break; }
+          }
+          // P of this tile is in shared memory
+          if (!mbar_wait(p_full, g & 1, abort_flag, status)) { ok = false; break; }
+          ATT_TRACE(tr, 256, tslot);          // P ready
+          if (g > 0 && !mbar_wait(o_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
-          if (!issue_s(j + 1)) { ok = false; break; }
-        }
-        // P_j is in shared memory
-        if (!mbar_wait(p_full, j & 1, abort_flag, status)) { ok = false; break; }
-        ATT_TRACE(tr, 256, tslot);          // P ready
-        if (j > 0 && !mbar_wait(o_free, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < ATT_BK / 16; ++k)          // P: 32 bytes along the row per step, second k-block after 4
-          umma_bf16_lohi(tmem_o, p_lo + (k >> 2) * (ATT_TILE_BYTES >> 4) + (k & 3) * 2, v_lo + k * (2048 >> 4), desc_hi,
-                         idesc_o, k > 0);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
-        ATT_TRACE(tr, 256, tslot);          // PV issued
+          for (int k = 0; k < ATT_BK / 16; ++k)          // P: 32 bytes along the row per step, second k-block after 4
+            umma_bf16_lohi(tmem_o, p_lo + (k >> 2) * (ATT_TILE_BYTES >> 4) + (k & 3) * 2, v_lo + k * (2048 >> 4), desc_hi,
+                           idesc_o, k > 0);
+          umma_commit(o_full);
+          umma_commit(&kv_empty[s]);
+          ATT_TRACE(tr, 256, tslot);          // PV issued
+        }
+        ++w;
       }
     }
   } else {
     // ------------------------------------------------------------ softmax + output (thread = query row)
     const int r = warp * 32 + lane;                      // row within the tile = TMEM lane
     const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-    float o[ATT_HS];
-#pragma unroll
-    for (int i = 0; i < ATT_HS; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
     uint8_t* sp = smem + AttSmem::P_OFF;
-    bool ok = true;
     if (threadIdx.x != 0) tr = nullptr;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      ATT_TRACE(tr, 0, tslot);              // waiting for S
-      if (!mbar_wait(s_full, j & 1, abort_flag, status)) { ok = false; break; }
-      tc_fence_after();
-      ATT_TRACE(tr, 0, tslot);              // S arrived
-      const bool diag = j == qi;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-      {
-        uint32_t v[2][32];
-        tmem_ld_32x32(tmem_s + lane_addr, v[0]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {                 // next chunk's load is in flight during the max
-          if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float x = __uint_as_float(v[c & 1][i]);
-            if (!diag || c * 32 + i <= r) mx = fmaxf(mx, x);
-          }
-          if (c + 1 < 4) tmem_ld_wait();
-        }
-      }
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const float alpha = fast_exp2(m - m_new);               // 0 on the first tile (m = -inf)
-      ATT_TRACE(tr, 0, tslot);              // pass 1 done
-      // the previous P V product has to be folded in before P is overwritten
-      if (j > 0) {
-        if (!mbar_wait(o_full, (j - 1) & 1, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_o + lane_addr + c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_free);
-      }
-#pragma unroll
-      for (int i = 0; i < ATT_HS; ++i) o[i] *= alpha;
-      ATT_TRACE(tr, 0, tslot);              // previous O folded in
-      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
-      float sum = 0.f;
-      {
-        uint32_t v[2][32];
-        tmem_ld_32x32(tmem_s + lane_addr, v[0]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
-          if (c == 3) {            // the whole score row is in registers: the score buffer may be overwritten
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free);
-          }
-          float p[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float x = __uint_as_float(v[c & 1][i]);
-            p[i] = (!diag || c * 32 + i <= r) ? fast_exp2(x * scale_log2 - m_new) : 0.f;
-            sum += p[i];
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            const uint4 w = make_uint4(pack_bf16(p[i], p[i + 1]), pack_bf16(p[i + 2], p[i + 3]),
-                                       pack_bf16(p[i + 4], p[i + 5]), pack_bf16(p[i + 6], p[i + 7]));
-            *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + i)) = w;
-          }
-          if (c + 1 < 4) tmem_ld_wait();
-        }
-      }
-      l = l * alpha + sum;
-      m = m_new;
-      ATT_TRACE(tr, 0, tslot);              // pass 2 done
-      fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-    }
-    if (ok && mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, status)) {
+    uint32_t g = 0;
+    bool ok = true;
+    // fold the P V product of global tile gt into o and hand the accumulator back
+    auto fold = [&](float (&o)[ATT_HS], uint32_t gt) -> bool {
+      if (!mbar_wait(o_full, gt & 1, abort_flag, status)) return false;
       tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
@@ -300,7 +249,94 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
+      return true;
+    };
+    for (int rr = 0; rr < rounds && ok; ++rr) {
+      int idx;
+      if (!att_item(rr, cta, G, total, idx)) continue;
+      const int qi = nq - 1 - idx / n_bh, bh = idx % n_bh;
+      const int b = bh / nh, h = bh - b * nh;
+      const int n_kv = qi + 1;
+      float o[ATT_HS];
+#pragma unroll
+      for (int i = 0; i < ATT_HS; ++i) o[i] = 0.f;
+      float m = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv && ok; ++j, ++g) {
+        ATT_TRACE(tr, 0, tslot);              // waiting for S
+        if (!mbar_wait(s_full, g & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        ATT_TRACE(tr, 0, tslot);              // S arrived
+        const bool diag = j == qi;
+        // pass 1: row maximum (four independent chains)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        {
+          uint32_t v[2][32];
+          tmem_ld_32x32(tmem_s + lane_addr, v[0]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {                 // next chunk's load is in flight during the max
+            if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float x = __uint_as_float(v[c & 1][i]);
+              if (!diag || c * 32 + i <= r) mx4[i & 3] = fmaxf(mx4[i & 3], x);
+            }
+            if (c + 1 < 4) tmem_ld_wait();
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m, mx * scale_log2);
+        const float alpha = fast_exp2(m - m_new);               // 0 on the first tile (m = -inf)
+        ATT_TRACE(tr, 0, tslot);              // pass 1 done
+        // the previous P V product has to be folded in before P is overwritten
+        if (j > 0 && !fold(o, g - 1)) { ok = false; break; }
+#pragma unroll
+        for (int i = 0; i < ATT_HS; ++i) o[i] *= alpha;
+        ATT_TRACE(tr, 0, tslot);              // previous O folded in
+        // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          uint32_t v[2][32];
+          tmem_ld_32x32(tmem_s + lane_addr, v[0]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
+            if (c == 3) {            // the whole score row is in registers: the score buffer may be overwritten
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(s_free);
+            }
+            float p[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float x = __uint_as_float(v[c & 1][i]);
+              p[i] = (!diag || c * 32 + i <= r) ? fast_exp2(x * scale_log2 - m_new) : 0.f;
+              sum4[i & 3] += p[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              const uint4 wv = make_uint4(pack_bf16(p[i], p[i + 1]), pack_bf16(p[i + 2], p[i + 3]),
+                                          pack_bf16(p[i + 4], p[i + 5]), pack_bf16(p[i + 6], p[i + 7]));
+              *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + i)) = wv;
+            }
+            if (c + 1 < 4) tmem_ld_wait();
+          }
+        }
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m = m_new;
+        ATT_TRACE(tr, 0, tslot);              // pass 2 done
+        fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+      }
+      if (!ok || !fold(o, g - 1)) { ok = false; break; }
       const float inv = 1.f / l;
+      const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
       __nv_bfloat16* dst = out + (long long)(row0 + r) * d + h * hs;
 #pragma unroll
       for (int i = 0; i < ATT_HS; i += 8)
@@ -383,45 +419,69 @@ attention_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __r
   }
 }
 
+// 32 columns of one query row: P = exp2(S * scale_log2 - lse2), dS = P * (dP - D) * scale, both packed to bf16
+// pairs.  MASKED: columns past `r` (above the diagonal) give zero.
+template <bool MASKED>
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], uint32_t (&pk_p)[16],
+                                              uint32_t (&pk_ds)[16], int c0, int r, float scale_log2, float lse2,
+                                              float Dr, float scale) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    float p0 = fast_exp2(__uint_as_float(sv[c]) * scale_log2 - lse2);
+    float p1 = fast_exp2(__uint_as_float(sv[c + 1]) * scale_log2 - lse2);
+    if (MASKED) {
+      p0 = c0 + c <= r ? p0 : 0.f;
+      p1 = c0 + c + 1 <= r ? p1 : 0.f;
+    }
+    const float d0 = p0 * (__uint_as_float(dpv[c]) - Dr) * scale;
+    const float d1 = p1 * (__uint_as_float(dpv[c + 1]) - Dr) * scale;
+    pk_p[c >> 1] = pack_bf16(p0, p1);
+    pk_ds[c >> 1] = pack_bf16(d0, d1);
+  }
+}
+
 constexpr int ATT_BWD_ROW_WARPS = 8;     // two per TMEM lane quarter: each thread takes half of its row's columns
 constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 2);
 
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
-                     const __grid_constant__ CUtensorMap tmap_dq, const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
-                     float* __restrict__ dq_acc, int T, int nh, int hs, float scale, int* status, long long* trace) {
+                     const __grid_constant__ CUtensorMap tmap_dq, const float* __restrict__ lse,
+                     const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv, int T, int nh, int n_bh, int hs,
+                     float scale, int* status, long long* trace) {
   using L = AttBwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // Persistent: one CTA per SM walks work items (kv tile, batch*head).  The per-step barriers complete one
+  // phase per step, kv_full / kv_empty / dkv_free one per item, counted over the life of the CTA
+  // (g = steps done, w = items done).
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* kv_full = bars;            // 1
-  uint64_t* q_full = bars + 1;         // 2
+  uint64_t* kv_full = bars;            // K, V of the item loaded
+  uint64_t* q_full = bars + 1;         // 2 stages of (Q_i, dO_i)
   uint64_t* q_empty = bars + 3;        // 2
   uint64_t* sdp_full = bars + 5;       // S and dP ready
-  uint64_t* pds_full = bars + 6;       // P and dS in shared memory (4 warps arrive)
+  uint64_t* pds_full = bars + 6;       // P and dS in shared memory (8 warps arrive)
   uint64_t* dq_full = bars + 7;        // dV/dK/dQ MMAs of this step done
-  uint64_t* dq_free = bars + 8;        // dQ drained (4 warps arrive)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* dq_free = bars + 8;        // dQ read out of TMEM (8 warps arrive)
+  uint64_t* kv_empty = bars + 9;       // every MMA of the item done: K, V may be overwritten
+  uint64_t* dkv_free = bars + 10;      // dK, dV of the item read out of TMEM (8 warps arrive)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid ordered by work: kv tile 0 (the most query tiles) of every (batch, head) first
-  const int n_bh = gridDim.x / (T / ATT_BK);
-  const int j = blockIdx.x / n_bh;
-  const int bh = blockIdx.x % n_bh;
-  const int b = bh / nh, h = bh - b * nh;
-  const int d = nh * hs;
   const int nq = T / ATT_BQ;
-  const int steps = nq - j;
+  const int total = nq * n_bh;                   // items, heaviest first: kv tile 0 meets every query tile
+  const int G = gridDim.x, cta = blockIdx.x;
+  const int rounds = (total + G - 1) / G;
+  const int d = nh * hs;
   const float scale_log2 = scale * 1.4426950408889634f;
   long long* tr = blockIdx.x == 0 ? trace : nullptr;
   int tslot = 0;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
+    mbar_init(kv_full, 1); mbar_init(kv_empty, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
     mbar_init(sdp_full, 1); mbar_init(pds_full, ATT_BWD_ROW_WARPS); mbar_init(dq_full, 1);
-    mbar_init(dq_free, ATT_BWD_ROW_WARPS);
+    mbar_init(dq_free, ATT_BWD_ROW_WARPS); mbar_init(dkv_free, ATT_BWD_ROW_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -443,17 +503,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
       tma_prefetch_desc(&tmap_do);
-      const int kvrow = b * T + j * ATT_BK;
-      mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
-      att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
-      att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
-      for (int it = 0; it < steps; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, status)) break;
-        mbar_expect_tx(&q_full[s], 2 * ATT_TILE_BYTES);
-        const int qrow = b * T + (j + it) * ATT_BQ;
-        att_load_tile(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], hs, h, qrow);
-        att_load_tile(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], hs, h, qrow);
+      uint32_t g = 0, w = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        int idx;
+        if (!att_item(r, cta, G, total, idx)) continue;
+        const int j = idx / n_bh, bh = idx % n_bh;
+        const int b = bh / nh, h = bh - b * nh;
+        const int steps = nq - j;
+        if (w > 0 && !mbar_wait(kv_empty, (w - 1) & 1, abort_flag, status)) break;
+        const int kvrow = b * T + j * ATT_BK;
+        mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
+        att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
+        att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
+        for (int it = 0; it < steps; ++it, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait(&q_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+          mbar_expect_tx(&q_full[s], 2 * ATT_TILE_BYTES);
+          const int qrow = b * T + (j + it) * ATT_BQ;
+          att_load_tile(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], hs, h, qrow);
+          att_load_tile(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], hs, h, qrow);
+        }
+        ++w;
       }
     }
   } else if (warp == MMA_WARP) {
@@ -471,37 +542,59 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       const uint32_t p_mn = smem_desc_lo(smem_u32(smem + L::P_OFF), ATT_TILE_BYTES);
       const uint32_t ds_mn = smem_desc_lo(smem_u32(smem + L::DS_OFF), ATT_TILE_BYTES);
       const uint32_t ds_km = smem_desc_lo(smem_u32(smem + L::DS_OFF), 16);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, status);
-      for (int it = 0; it < steps && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
-        const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
-        const uint32_t q_km = smem_desc_lo(sq, 16), do_km = smem_desc_lo(sdo, 16);
-        const uint32_t q_mn = smem_desc_lo(sq, ATT_TILE_BYTES), do_mn = smem_desc_lo(sdo, ATT_TILE_BYTES);
-        if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
+      uint32_t g = 0, w = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        int idx;
+        if (!att_item(r, cta, G, total, idx)) continue;
+        const int steps = nq - idx / n_bh;
+        if (!mbar_wait(kv_full, w & 1, abort_flag, status)) break;
+        // S = Q K^T and dP = dO V^T of global step gs (operands in stage gs & 1)
+        auto issue_sdp = [&](uint32_t gs) -> bool {
+          const int st = gs & 1;
+          if (!mbar_wait(&q_full[st], (gs >> 1) & 1, abort_flag, status)) return false;
+          tc_fence_after();
+          const uint32_t q_km = smem_desc_lo(smem_u32(smem + L::Q_OFF + st * ATT_TILE_BYTES), 16);
+          const uint32_t do_km = smem_desc_lo(smem_u32(smem + L::DO_OFF + st * ATT_TILE_BYTES), 16);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_s, q_km + k * KSTEP, k_km + k * KSTEP, desc_hi, id_s, k > 0);
+          for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_s, q_km + k * KSTEP, k_km + k * KSTEP, desc_hi, id_s, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_dp, do_km + k * KSTEP, v_km + k * KSTEP, desc_hi, id_s, k > 0);
-        umma_commit(sdp_full);
-        ATT_TRACE(tr, 256, tslot);          // S, dP issued
-        if (!mbar_wait(pds_full, it & 1, abort_flag, status)) { ok = false; break; }
-        ATT_TRACE(tr, 256, tslot);          // P, dS ready
-        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, abort_flag, status)) { ok = false; break; }
-        tc_fence_after();
+          for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_dp, do_km + k * KSTEP, v_km + k * KSTEP, desc_hi, id_s, k > 0);
+          umma_commit(sdp_full);
+          ATT_TRACE(tr, 256, tslot);          // S, dP issued
+          return true;
+        };
+        ok = issue_sdp(g);
+        for (int it = 0; it < steps && ok; ++it, ++g) {
+          const int s = g & 1;
+          const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
+          const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
+          const uint32_t q_mn = smem_desc_lo(sq, ATT_TILE_BYTES), do_mn = smem_desc_lo(sdo, ATT_TILE_BYTES);
+          if (!mbar_wait(pds_full, g & 1, abort_flag, status)) { ok = false; break; }
+          ATT_TRACE(tr, 256, tslot);          // P, dS ready
+          // The row threads have read S and dP of this step (they did before writing P / dS), so the next
+          // step's pair goes first: they turn it into P / dS in registers while the products below run.
+          // (Not across items: the next item's K and V replace the ones the dQ product below still reads.)
+          if (it + 1 < steps && !issue_sdp(g + 1)) { ok = false; break; }
+          if (g > 0 && !mbar_wait(dq_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+          // a new item starts its dV / dK sums from zero: the previous item's must have been read out
+          if (it == 0 && w > 0 && !mbar_wait(dkv_free, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
-          umma_bf16_lohi(tm_dv, p_mn + k * MNSTEP, do_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+          for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
+            umma_bf16_lohi(tm_dv, p_mn + k * MNSTEP, do_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
 #pragma unroll
-        for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
-          umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+          for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
+            umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
 #pragma unroll
-        for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
-          umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
-        umma_commit(dq_full);
-        umma_commit(&q_empty[s]);
-        ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
+          for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
+            umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
+          umma_commit(dq_full);
+          umma_commit(&q_empty[s]);
+          if (it + 1 == steps) umma_commit(kv_empty);
+          ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
+        }
+        ++w;
       }
     }
   } else {
@@ -515,10 +608,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     if (threadIdx.x != 0) tr = nullptr;
     uint8_t* sdq = smem + L::DQ_OFF + half * ATT_TILE_BYTES;     // this thread's half: [128 rows][32 fp32]
     const bool elected = threadIdx.x == 0;
-    // dQ of step `it`: TMEM -> registers -> swizzled shared tile -> one TMA reduce-add per half into the
-    // fp32 dQ scratch.  The bulk reduction runs asynchronously, so no thread waits on global atomics.
-    auto drain_dq = [&](int it) -> bool {
-      if (!mbar_wait(dq_full, it & 1, abort_flag, status)) return false;
+    uint32_t g = 0;
+    // dQ of global step gs (query rows from row_g, head h): TMEM -> registers -> swizzled shared tile -> one
+    // TMA reduce-add per half into the fp32 dQ scratch.  The bulk reduction runs asynchronously, so no
+    // thread waits on global atomics.
+    auto drain_dq = [&](uint32_t gs, int row_g, int h) -> bool {
+      if (!mbar_wait(dq_full, gs & 1, abort_flag, status)) return false;
       tc_fence_after();
       uint32_t v[32];
       tmem_ld_32x32(tm_dq + lane_addr + half * 32, v);
@@ -535,7 +630,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       fence_proxy_async();
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (elected) {
-        const int row_g = b * T + (j + it) * ATT_BQ;
         if (hs == 64) {
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh)
@@ -552,75 +646,81 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       }
       return true;
     };
-    for (int it = 0; it < steps && ok; ++it) {
-      const int i = j + it;
-      const long long stat = (long long)bh * T + i * ATT_BQ + r;
-      const float lse2 = lse[stat] * 1.4426950408889634f;
-      const float Dr = Dvec[stat];
-      ATT_TRACE(tr, 0, tslot);              // step start
-      // the previous step's MMAs must be done with P / dS before they are overwritten
-      if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }
-      ATT_TRACE(tr, 0, tslot);              // dQ drained
-      if (!mbar_wait(sdp_full, it & 1, abort_flag, status)) { ok = false; break; }
-      tc_fence_after();
-      ATT_TRACE(tr, 0, tslot);              // S, dP arrived
-      const bool diag = it == 0;
-      uint32_t sv_[2][32], dpv[2][32];
-      tmem_ld_32x32(tm_s + lane_addr + half * 64, sv_[0]);
-      tmem_ld_32x32(tm_dp + lane_addr + half * 64, dpv[0]);
-      tmem_ld_wait();
+    for (int rr = 0; rr < rounds && ok; ++rr) {
+      int idx;
+      if (!att_item(rr, cta, G, total, idx)) continue;
+      const int j = idx / n_bh, bh = idx % n_bh;
+      const int b = bh / nh, h = bh - b * nh;
+      const int steps = nq - j;
+      for (int it = 0; it < steps && ok; ++it, ++g) {
+        const int i = j + it;
+        const long long stat = (long long)bh * T + i * ATT_BQ + r;
+        const float lse2 = lse[stat] * 1.4426950408889634f;
+        const float Dr = Dvec[stat];
+        ATT_TRACE(tr, 0, tslot);              // step start
+        if (!mbar_wait(sdp_full, g & 1, abort_flag, status)) { ok = false; break; }
+        tc_fence_after();
+        ATT_TRACE(tr, 0, tslot);              // S, dP arrived
+        // P and dS of this thread's 64 columns, in registers: the previous step's products may still be
+        // reading the shared P / dS tiles
+        uint32_t pk_p[2][16], pk_ds[2][16];
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c0 = half * 64 + cc * 32;
-        if (cc + 1 < 2) {
-          tmem_ld_32x32(tm_s + lane_addr + c0 + 32, sv_[(cc + 1) & 1]);
-          tmem_ld_32x32(tm_dp + lane_addr + c0 + 32, dpv[(cc + 1) & 1]);
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = half * 64 + cc * 32;
+          uint32_t sv_[32], dpv[32];
+          tmem_ld_32x32(tm_s + lane_addr + c0, sv_);
+          tmem_ld_32x32(tm_dp + lane_addr + c0, dpv);
+          tmem_ld_wait();
+          if (it == 0) bwd_row_chunk<true>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
+          else         bwd_row_chunk<false>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
         }
-        float p[32], ds[32];
+        ATT_TRACE(tr, 0, tslot);              // P, dS computed
+        // the previous step's MMAs must be done with P / dS before they are overwritten
+        if (it > 0 && !drain_dq(g - 1, b * T + (i - 1) * ATT_BQ, h)) { ok = false; break; }
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const bool keep = !diag || c0 + c <= r;
-          p[c] = keep ? fast_exp2(__uint_as_float(sv_[cc & 1][c]) * scale_log2 - lse2) : 0.f;
-          ds[c] = p[c] * (__uint_as_float(dpv[cc & 1][c]) - Dr) * scale;
-        }
+        for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          const uint32_t off = p_offset(r, c0 + c);
-          *reinterpret_cast<uint4*>(sp + off) = make_uint4(pack_bf16(p[c], p[c + 1]), pack_bf16(p[c + 2], p[c + 3]),
-                                                            pack_bf16(p[c + 4], p[c + 5]), pack_bf16(p[c + 6], p[c + 7]));
-          *reinterpret_cast<uint4*>(sds + off) = make_uint4(pack_bf16(ds[c], ds[c + 1]), pack_bf16(ds[c + 2], ds[c + 3]),
-                                                             pack_bf16(ds[c + 4], ds[c + 5]), pack_bf16(ds[c + 6], ds[c + 7]));
+          for (int c = 0; c < 32; c += 8) {
+            const uint32_t off = p_offset(r, half * 64 + cc * 32 + c);
+            const int q = c >> 1;
+            *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk_p[cc][q], pk_p[cc][q + 1], pk_p[cc][q + 2], pk_p[cc][q + 3]);
+            *reinterpret_cast<uint4*>(sds + off) = make_uint4(pk_ds[cc][q], pk_ds[cc][q + 1], pk_ds[cc][q + 2], pk_ds[cc][q + 3]);
+          }
         }
-        if (cc + 1 < 2) tmem_ld_wait();
+        ATT_TRACE(tr, 0, tslot);              // dQ drained, P, dS written
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_full);
       }
-      ATT_TRACE(tr, 0, tslot);              // P, dS written
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
-    }
-    if (ok && drain_dq(steps - 1)) {
-      if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
+      // the last step's dQ; its barrier also says that every dV / dK product of the item is done
+      if (!ok || !drain_dq(g - 1, b * T + (nq - 1) * ATT_BQ, h)) { ok = false; break; }
       // dV and dK rows of this kv tile (TMEM lane = kv row)
       __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * hs;
+      uint32_t vk[32], vv[32];
+      tmem_ld_32x32(tm_dk + lane_addr + half * 32, vk);
+      tmem_ld_32x32(tm_dv + lane_addr + half * 32, vv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dkv_free);          // the next item's first products may overwrite the sums
+      if (half * 32 < hs) {
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t src = which == 0 ? tm_dk : tm_dv;
-        __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d) + half * 32;
-        if (half * 32 < hs) {
-          uint32_t v[32];
-          tmem_ld_32x32(src + lane_addr + half * 32, v);
-          tmem_ld_wait();
+        for (int which = 0; which < 2; ++which) {
+          __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d) + half * 32;
 #pragma unroll
-          for (int c = 0; c < 32; c += 8)
+          for (int c = 0; c < 32; c += 8) {
+            const uint32_t* v = which == 0 ? vk : vv;
             *reinterpret_cast<uint4*>(dst + c) = make_uint4(
                 pack_bf16(__uint_as_float(v[c]), __uint_as_float(v[c + 1])),
                 pack_bf16(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])),
                 pack_bf16(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5])),
                 pack_bf16(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7])));
+          }
         }
       }
     }
+    if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
   }
 
   tc_fence_before();
@@ -636,6 +736,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 using namespace dsw;
 
 static long long* g_att_trace = nullptr;
+
+static int att_num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n <= 0)
+      n = 148;
+  }
+  return n;
+}
 // Register (or clear, with nullptr) a device buffer of 512 int64 for the in-kernel timeline.
 extern "C" int dsw_attention_set_trace(long long* buf) { g_att_trace = buf; return 0; }
 
@@ -656,9 +767,11 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
       return -2;
     attr_set = true;
   }
-  dim3 grid((T / ATT_BQ) * B * nh);
-  attention_fwd_kernel<<<grid, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh, hs,
-                                                                   scale * 1.4426950408889634f, status, g_att_trace);
+  // persistent: two CTAs per SM walk the work items
+  const int total = (T / ATT_BQ) * B * nh;
+  const int G = total < 2 * att_num_sms() ? total : 2 * att_num_sms();
+  attention_fwd_kernel<<<G, ATT_THREADS, AttSmem::TOTAL, st>>>(tm, (__nv_bfloat16*)out, lse, T, nh, B * nh, hs,
+                                                               scale * 1.4426950408889634f, status, g_att_trace);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -693,9 +806,11 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   const long long warps = (long long)B * T * nh;
   attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh, hs);
-  dim3 grid((T / ATT_BK) * B * nh);
-  attention_bwd_kernel<<<grid, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, dq_acc,
-                                                                     T, nh, hs, scale, status, g_att_trace);
+  // persistent: one CTA per SM walks the work items
+  const int total = (T / ATT_BK) * B * nh;
+  const int G = total < att_num_sms() ? total : att_num_sms();
+  attention_bwd_kernel<<<G, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, T, nh,
+                                                                       B * nh, hs, scale, status, g_att_trace);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
