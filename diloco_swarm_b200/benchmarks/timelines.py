@@ -87,12 +87,12 @@ def attention_timeline(B, T, nh):
     _, ctx = attention_fwd(qkv, B, T, nh)
     torch.cuda.synchronize()
     show("attention forward, CTA (0,0) (last query tile: all kv tiles), ns since first stamp",
-         ["waitS", "gotS", "pass1", "fold", "pass2"], ["S_issued", "P_ready", "PV_issued"])
+         ["waitS", "gotS", "max", "O_ready", "P_written"], ["S_issued", "P_ready", "PV_issued"])
     tr.zero_()
     attention_bwd(dout, ctx)
     torch.cuda.synchronize()
     show("attention backward, CTA (0,0) (kv tile 0: all query tiles), ns since first stamp",
-         ["start", "S_dP_ready", "P_dS_in_regs", "dQ_drained_P_dS_written"],
+         ["start", "S_dP_ready", "P_dS_in_regs", "P_dS_written"],
          ["P_dS_ready", "next_S_dP_issued", "dV_dK_dQ_issued"], mma_prefix=["S_dP_issued"])
     set_trace(None)
 

@@ -6,10 +6,14 @@
 // [B*T, d] tensor that feeds the output projection, plus the per-row log-sum-exp
 // that the backward pass needs.
 //
-// One CTA per (128 query rows, batch, head).  Warps 0-3 own one query row per
-// thread: they read the score row from tensor memory, do the online softmax and
-// keep the output row (64 fp32) in registers.  Warp 4 issues the MMAs, warp 5
-// the TMA loads.
+// A work item is (128 query rows, batch, head); persistent CTAs walk the items.
+// Warps 0-3 own one query row per thread: they read the score row from tensor
+// memory once, do the online softmax on it in registers and write P to shared
+// memory.  The output row stays in tensor memory: every P V product accumulates
+// onto it, and the row threads rescale it in place only when the running maximum
+// has grown by more than 2^8 since the last rescale (until then P is computed
+// against the older maximum, which is exact algebra and safe in bf16/fp32 range).
+// Warp 4 issues the MMAs, warp 5 the TMA loads.
 //   S = Q K_j^T          A = Q  [128 x 64]  K-major,  B = K_j [128 x 64] K-major   -> TMEM, 128 columns
 //   O_j = P V_j          A = P  [128 x 128] K-major (written by the softmax warps
 //                        in the 128-byte-swizzled layout),  B = V_j [128 x 64] N-major -> TMEM, 64 columns
@@ -106,9 +110,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   uint64_t* kv_empty = bars + 3;      // 2 stages
   uint64_t* s_full = bars + 5;        // S ready in TMEM
   uint64_t* p_full = bars + 6;        // P written to smem (4 warps arrive)
-  uint64_t* o_full = bars + 7;        // P V ready in TMEM
-  uint64_t* o_free = bars + 8;        // P V folded into the output registers (4 warps arrive)
-  uint64_t* s_free = bars + 9;        // S read out of TMEM for the last time (4 warps arrive)
+  uint64_t* o_full = bars + 7;        // P V accumulated in TMEM
+  uint64_t* o_free = bars + 8;        // per item: the output rows have been read out of TMEM (4 warps arrive)
+  uint64_t* s_free = bars + 9;        // S read out of TMEM (4 warps arrive)
   uint64_t* q_empty = bars + 10;      // all S products of the item done: Q may be overwritten
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -213,15 +217,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
             const bool okk = more ? issue_s(g + 1, w, false, j + 2 == n_kv) : issue_s(g + 1, w + 1, true, next_n_kv == 1);
             if (!okk) { ok = false; break; }
           }
-          // P of this tile is in shared memory
+          // P of this tile is in shared memory (and the output rows are rescaled if they had to be)
           if (!mbar_wait(p_full, g & 1, abort_flag, status)) { ok = false; break; }
           ATT_TRACE(tr, 256, tslot);          // P ready
-          if (g > 0 && !mbar_wait(o_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+          // a new item starts its output from zero: the previous item's must have been read out
+          if (j == 0 && w > 0 && !mbar_wait(o_free, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < ATT_BK / 16; ++k)          // P: 32 bytes along the row per step, second k-block after 4
             umma_bf16_lohi(tmem_o, p_lo + (k >> 2) * (ATT_TILE_BYTES >> 4) + (k & 3) * 2, v_lo + k * (2048 >> 4), desc_hi,
-                           idesc_o, k > 0);
+                           idesc_o, (j > 0 || k > 0));
           umma_commit(o_full);
           umma_commit(&kv_empty[s]);
           ATT_TRACE(tr, 256, tslot);          // PV issued
@@ -237,113 +242,122 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     if (threadIdx.x != 0) tr = nullptr;
     uint32_t g = 0;
     bool ok = true;
-    // fold the P V product of global tile gt into o and hand the accumulator back
-    auto fold = [&](float (&o)[ATT_HS], uint32_t gt) -> bool {
-      if (!mbar_wait(o_full, gt & 1, abort_flag, status)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(v[i]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_free);
-      return true;
-    };
     for (int rr = 0; rr < rounds && ok; ++rr) {
       int idx;
       if (!att_item(rr, cta, G, total, idx)) continue;
       const int qi = nq - 1 - idx / n_bh, bh = idx % n_bh;
       const int b = bh / nh, h = bh - b * nh;
       const int n_kv = qi + 1;
-      float o[ATT_HS];
-#pragma unroll
-      for (int i = 0; i < ATT_HS; ++i) o[i] = 0.f;
-      float m = -INFINITY, l = 0.f;
+      float m = -INFINITY, l = 0.f;           // m: the maximum P is computed against (log2 units)
       for (int j = 0; j < n_kv && ok; ++j, ++g) {
         ATT_TRACE(tr, 0, tslot);              // waiting for S
         if (!mbar_wait(s_full, g & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
         ATT_TRACE(tr, 0, tslot);              // S arrived
-        const bool diag = j == qi;
-        // pass 1: row maximum (four independent chains)
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        {
-          uint32_t v[2][32];
-          tmem_ld_32x32(tmem_s + lane_addr, v[0]);
-          tmem_ld_wait();
+        // the whole score row into registers; the score buffer is free for the next tile at once
+        uint32_t v[4][32];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {                 // next chunk's load is in flight during the max
-            if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float x = __uint_as_float(v[c & 1][i]);
-              if (!diag || c * 32 + i <= r) mx4[i & 3] = fmaxf(mx4[i & 3], x);
-            }
-            if (c + 1 < 4) tmem_ld_wait();
-          }
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float m_new = fmaxf(m, mx * scale_log2);
-        const float alpha = fast_exp2(m - m_new);               // 0 on the first tile (m = -inf)
-        ATT_TRACE(tr, 0, tslot);              // pass 1 done
-        // the previous P V product has to be folded in before P is overwritten
-        if (j > 0 && !fold(o, g - 1)) { ok = false; break; }
-#pragma unroll
-        for (int i = 0; i < ATT_HS; ++i) o[i] *= alpha;
-        ATT_TRACE(tr, 0, tslot);              // previous O folded in
-        // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        {
-          uint32_t v[2][32];
-          tmem_ld_32x32(tmem_s + lane_addr, v[0]);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            if (c + 1 < 4) tmem_ld_32x32(tmem_s + lane_addr + (c + 1) * 32, v[(c + 1) & 1]);
-            if (c == 3) {            // the whole score row is in registers: the score buffer may be overwritten
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(s_free);
-            }
-            float p[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float x = __uint_as_float(v[c & 1][i]);
-              p[i] = (!diag || c * 32 + i <= r) ? fast_exp2(x * scale_log2 - m_new) : 0.f;
-              sum4[i & 3] += p[i];
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              const uint4 wv = make_uint4(pack_bf16(p[i], p[i + 1]), pack_bf16(p[i + 2], p[i + 3]),
-                                          pack_bf16(p[i + 4], p[i + 5]), pack_bf16(p[i + 6], p[i + 7]));
-              *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + i)) = wv;
-            }
-            if (c + 1 < 4) tmem_ld_wait();
-          }
-        }
-        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        m = m_new;
-        ATT_TRACE(tr, 0, tslot);              // pass 2 done
-        fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + lane_addr + c * 32, v[c]);
+        tmem_ld_wait();
         tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        const bool diag = j == qi;
+        // row maximum (four independent chains); on the diagonal tile only columns <= r count
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!diag) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i <= r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        ATT_TRACE(tr, 0, tslot);              // maximum done
+        if (j == 0) {
+          m = mx;
+        } else {
+          // the previous product must be done: it reads the P tile that is about to be overwritten, and it
+          // accumulates onto the output rows that may be rescaled here
+          if (!mbar_wait(o_full, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+          const bool grow = mx > m + 8.f;
+          if (__any_sync(0xffffffffu, grow)) {          // rare after the first tiles
+            tc_fence_after();
+            const float alpha = grow ? fast_exp2(m - mx) : 1.f;
+            if (grow) { m = mx; l *= alpha; }
+#pragma unroll
+            for (int c0 = 0; c0 < ATT_HS; c0 += 32) {
+              uint32_t ov[32];
+              tmem_ld_32x32(tmem_o + lane_addr + c0, ov);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st_32x32(tmem_o + lane_addr + c0, ov);
+            }
+            tmem_st_wait();
+          }
+        }
+        ATT_TRACE(tr, 0, tslot);              // output rows ready for the next product
+        // probabilities -> shared memory (bf16, swizzled K-major), row sum
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+          if (!diag) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(__uint_as_float(v[c][i]) * scale_log2 - m);
+              const float p1 = fast_exp2(__uint_as_float(v[c][i + 1]) * scale_log2 - m);
+              sum4[i & 3] += p0; sum4[(i + 1) & 3] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = c * 32 + i <= r ? fast_exp2(__uint_as_float(v[c][i]) * scale_log2 - m) : 0.f;
+              const float p1 = c * 32 + i + 1 <= r ? fast_exp2(__uint_as_float(v[c][i + 1]) * scale_log2 - m) : 0.f;
+              sum4[i & 3] += p0; sum4[(i + 1) & 3] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + 2 * i)) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        ATT_TRACE(tr, 0, tslot);              // P written
+        fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
+        tc_fence_before();            // orders the rescaled output rows before the product that follows the arrive
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
       }
-      if (!ok || !fold(o, g - 1)) { ok = false; break; }
+      if (!ok || !mbar_wait(o_full, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+      tc_fence_after();
       const float inv = 1.f / l;
       const int row0 = b * T + qi * ATT_BQ;                // first global row of this query tile
       __nv_bfloat16* dst = out + (long long)(row0 + r) * d + h * hs;
+      uint32_t ov[2][32];
+      tmem_ld_32x32(tmem_o + lane_addr, ov[0]);
+      tmem_ld_32x32(tmem_o + lane_addr + 32, ov[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);          // the next item's first product may overwrite the rows
 #pragma unroll
       for (int i = 0; i < ATT_HS; i += 8)
-        if (i < hs)
+        if (i < hs) {
+          const uint32_t* o = ov[i >> 5] + (i & 31);
           *reinterpret_cast<uint4*>(dst + i) =
-              make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                         pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+              make_uint4(pack_bf16(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv),
+                         pack_bf16(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv),
+                         pack_bf16(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv),
+                         pack_bf16(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv));
+        }
       // natural-log LSE of the scaled scores
       lse_out[(long long)bh * T + qi * ATT_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
     }
@@ -676,7 +690,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         }
         ATT_TRACE(tr, 0, tslot);              // P, dS computed
         // the previous step's MMAs must be done with P / dS before they are overwritten
-        if (it > 0 && !drain_dq(g - 1, b * T + (i - 1) * ATT_BQ, h)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_full, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
@@ -687,11 +701,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
             *reinterpret_cast<uint4*>(sds + off) = make_uint4(pk_ds[cc][q], pk_ds[cc][q + 1], pk_ds[cc][q + 2], pk_ds[cc][q + 3]);
           }
         }
-        ATT_TRACE(tr, 0, tslot);              // dQ drained, P, dS written
+        ATT_TRACE(tr, 0, tslot);              // P, dS written
         fence_proxy_async();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(pds_full);
+        // the previous step's dQ leaves after the hand-over, off the critical path (the next dQ product
+        // waits for its read-out)
+        if (it > 0 && !drain_dq(g - 1, b * T + (i - 1) * ATT_BQ, h)) { ok = false; break; }
       }
       // the last step's dQ; its barrier also says that every dV / dK product of the item is done
       if (!ok || !drain_dq(g - 1, b * T + (nq - 1) * ATT_BQ, h)) { ok = false; break; }
