@@ -56,7 +56,7 @@ __device__ __forceinline__ long long gtimer() {
 constexpr int ATT_BQ = 128;        // query rows per CTA
 constexpr int ATT_BK = 128;        // kv rows per step
 constexpr int ATT_HS = 64;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 256;          // warps 0-3 softmax, 4 MMA, 5 TMA, 6-7 only lend their registers
 constexpr int ATT_TILE_BYTES = 128 * 64 * 2;     // one [128 x 64] bf16 tile
 
 struct AttSmem {
@@ -70,6 +70,13 @@ struct AttSmem {
   // and the kernel checks that it really is.
   static constexpr int TOTAL = BAR_OFF + 128;
 };
+
+// max(a, b, c) in one instruction (sm_100 has the three-input form)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -142,11 +149,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Two CTAs share the SM's registers: 128 per thread at launch.  The softmax warps keep a whole score row
+  // (128 values) in registers, so their warpgroup takes 216 and the other warpgroup (one MMA-issuing and one
+  // TMA-issuing thread) drops to 40.
+  // (each role changes its own allotment at the top of its branch)
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;            // 128 columns
   const uint32_t tmem_o = tmem_base + 128;      // 64 columns
 
-  if (warp == 5) {
+  if (warp >= 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");          // the whole warpgroup, one instruction
+  }
+  if (warp >= 6) {
+    // nothing to do: these warps exist so that the register hand-over works on whole warpgroups
+  } else if (warp == 5) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
@@ -236,6 +252,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     }
   } else {
     // ------------------------------------------------------------ softmax + output (thread = query row)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int r = warp * 32 + lane;                      // row within the tile = TMEM lane
     const uint32_t lane_addr = uint32_t(warp * 32) << 16;
     uint8_t* sp = smem + AttSmem::P_OFF;
@@ -269,7 +286,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+            for (int i = 0; i < 32; i += 8) {
+              mx4[0] = fmax3(mx4[0], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+              mx4[1] = fmax3(mx4[1], __uint_as_float(v[c][i + 2]), __uint_as_float(v[c][i + 3]));
+              mx4[2] = fmax3(mx4[2], __uint_as_float(v[c][i + 4]), __uint_as_float(v[c][i + 5]));
+              mx4[3] = fmax3(mx4[3], __uint_as_float(v[c][i + 6]), __uint_as_float(v[c][i + 7]));
+            }
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
