@@ -105,6 +105,41 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
 // finish kernel adds the per-block partials into the fp32 gradients in a fixed order.
 constexpr int LN_BWD_WARPS = 8;
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16(w[j]);
+    f[2 * j] = t.x; f[2 * j + 1] = t.y;
+  }
+}
+
+// One row's operands as loaded (bf16, 8 per lane per 256-column chunk) plus its statistics.
+template <int NCH>
+struct LnBwdRow {
+  uint4 x[NCH], dy[NCH], r[NCH];
+  float mean, rstd;
+};
+
+template <int NCH>
+__device__ __forceinline__ void ln_bwd_load(LnBwdRow<NCH>& o, const __nv_bfloat16* __restrict__ dy,
+                                            const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dres,
+                                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                            int row, int d, int nch, int lane) {
+  const long long off = (long long)row * d;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    if (c < nch && col < d) {
+      o.x[c] = *reinterpret_cast<const uint4*>(x + off + col);
+      o.dy[c] = *reinterpret_cast<const uint4*>(dy + off + col);
+      if (dres) o.r[c] = *reinterpret_cast<const uint4*>(dres + off + col);
+    }
+  }
+  o.mean = mean_in[row];
+  o.rstd = rstd_in[row];
+}
+
 template <int LN_MAX_CHUNKS>
 __global__ void __launch_bounds__(32 * LN_BWD_WARPS, 2)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -117,33 +152,66 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   float* mine = sh + (long long)warp * 3 * d;
   for (int i = lane; i < 3 * d; i += 32) mine[i] = 0.f;
   __syncwarp();
-  for (int row = blockIdx.x * LN_BWD_WARPS + warp; row < M; row += gridDim.x * LN_BWD_WARPS) {
+  // Rows stay in the bf16 form they were loaded in and are unpacked in both passes (cheaper in registers
+  // than a row of fp32).  Up to 768 columns the column sums live in registers (72 per thread) and reach the
+  // warp's shared strip once, at the end: a read-modify-write of the strips per row costs more shared-memory
+  // cycles than the whole row costs in DRAM time.  Wider rows add into the strips row by row; up to 1024
+  // columns the next row's loads are issued before the current row is worked on.
+  constexpr bool REG_ACC = LN_MAX_CHUNKS <= 3;
+  constexpr bool PREFETCH = !REG_ACC && LN_MAX_CHUNKS <= 4;
+  constexpr int NACC = REG_ACC ? LN_MAX_CHUNKS : 1;
+  float acc_g[NACC][8], acc_b[NACC][8], acc_r[NACC][8];
+#pragma unroll
+  for (int c = 0; c < NACC; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc_g[c][j] = 0.f; acc_b[c][j] = 0.f; acc_r[c][j] = 0.f; }
+  const int stride = gridDim.x * LN_BWD_WARPS;
+  int row = blockIdx.x * LN_BWD_WARPS + warp;
+  LnBwdRow<LN_MAX_CHUNKS> cur, nxt;
+  if (PREFETCH && row < M) ln_bwd_load(cur, dy, x, dres, mean_in, rstd_in, row, d, nch, lane);
+  for (; row < M; row += stride) {
+    if (PREFETCH) {
+      if (row + stride < M) ln_bwd_load(nxt, dy, x, dres, mean_in, rstd_in, row + stride, d, nch, lane);
+    } else {
+      ln_bwd_load(cur, dy, x, dres, mean_in, rstd_in, row, d, nch, lane);
+    }
     const long long off = (long long)row * d;
-    const float mean = mean_in[row], rstd = rstd_in[row];
-    float xh[LN_MAX_CHUNKS][8], gy[LN_MAX_CHUNKS][8];
+    const float mean = cur.mean, rstd = cur.rstd;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
       const int col = c * 256 + lane * 8;
       if (c < nch && col < d) {
-        float g[8], dv[8];
-        load8(x + off + col, xh[c]);
-        load8(dy + off + col, dv);
+        float g[8], dv[8], xh[8];
+        unpack8(cur.x[c], xh);
+        unpack8(cur.dy[c], dv);
         load8f(gamma + col, g);
-        float4* a0 = reinterpret_cast<float4*>(mine + col);
-        float4* b0 = reinterpret_cast<float4*>(mine + d + col);
-        float4 ag0 = a0[0], ag1 = a0[1], ab0 = b0[0], ab1 = b0[1];
-        float* ag = &ag0.x; float* agh = &ag1.x; float* ab = &ab0.x; float* abh = &ab1.x;
+        if constexpr (REG_ACC) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[c][j] = (xh[c][j] - mean) * rstd;
-          gy[c][j] = dv[j] * g[j];
-          s1 += gy[c][j];
-          s2 += gy[c][j] * xh[c][j];
-          if (j < 4) { ag[j] += dv[j] * xh[c][j]; ab[j] += dv[j]; }
-          else       { agh[j - 4] += dv[j] * xh[c][j]; abh[j - 4] += dv[j]; }
+          for (int j = 0; j < 8; ++j) {
+            const float xhat = (xh[j] - mean) * rstd;
+            const float gy = dv[j] * g[j];
+            s1 += gy;
+            s2 += gy * xhat;
+            acc_g[c][j] += dv[j] * xhat;
+            acc_b[c][j] += dv[j];
+          }
+        } else {
+          float4* a0 = reinterpret_cast<float4*>(mine + col);
+          float4* b0 = reinterpret_cast<float4*>(mine + d + col);
+          float4 ag0 = a0[0], ag1 = a0[1], ab0 = b0[0], ab1 = b0[1];
+          float* ag = &ag0.x; float* agh = &ag1.x; float* ab = &ab0.x; float* abh = &ab1.x;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float xhat = (xh[j] - mean) * rstd;
+            const float gy = dv[j] * g[j];
+            s1 += gy;
+            s2 += gy * xhat;
+            if (j < 4) { ag[j] += dv[j] * xhat; ab[j] += dv[j]; }
+            else       { agh[j - 4] += dv[j] * xhat; abh[j - 4] += dv[j]; }
+          }
+          a0[0] = ag0; a0[1] = ag1; b0[0] = ab0; b0[1] = ab1;
         }
-        a0[0] = ag0; a0[1] = ag1; b0[0] = ab0; b0[1] = ab1;
       }
     }
     s1 = warp_sum(s1) / d;
@@ -152,18 +220,42 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
       const int col = c * 256 + lane * 8;
       if (c < nch && col < d) {
-        float o[8], r[8];
+        float g[8], dv[8], xh[8], o[8], r[8];
+        unpack8(cur.x[c], xh);
+        unpack8(cur.dy[c], dv);
+        load8f(gamma + col, g);
         if (dres) {
-          load8(dres + off + col, r);
-          float4* c0 = reinterpret_cast<float4*>(mine + 2 * d + col);
-          float4 r0 = c0[0], r1 = c0[1];
-          r0.x += r[0]; r0.y += r[1]; r0.z += r[2]; r0.w += r[3];
-          r1.x += r[4]; r1.y += r[5]; r1.z += r[6]; r1.w += r[7];
-          c0[0] = r0; c0[1] = r1;
+          unpack8(cur.r[c], r);
+          if constexpr (REG_ACC) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc_r[c][j] += r[j];
+          } else {
+            float4* c0 = reinterpret_cast<float4*>(mine + 2 * d + col);
+            float4 r0 = c0[0], r1 = c0[1];
+            r0.x += r[0]; r0.y += r[1]; r0.z += r[2]; r0.w += r[3];
+            r1.x += r[4]; r1.y += r[5]; r1.z += r[6]; r1.w += r[7];
+            c0[0] = r0; c0[1] = r1;
+          }
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xh[c][j] * s2) + (dres ? r[j] : 0.f);
+        for (int j = 0; j < 8; ++j)
+          o[j] = rstd * (dv[j] * g[j] - s1 - (xh[j] - mean) * rstd * s2) + (dres ? r[j] : 0.f);
         store8(dx + off + col, o);
+      }
+    }
+    if (PREFETCH) cur = nxt;
+  }
+  if constexpr (REG_ACC) {
+#pragma unroll
+    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (c < nch && col < d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          mine[col + j] = acc_g[c][j];
+          mine[d + col + j] = acc_b[c][j];
+          mine[2 * d + col + j] = acc_r[c][j];
+        }
       }
     }
   }
