@@ -23,6 +23,7 @@ One step touches several GB of weights and activations, far more than the
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -36,7 +37,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 TOPOLOGY = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
-SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+SMI_QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -74,7 +75,10 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self) -> dict:
+    def stop(self, windows=()) -> dict:
+        """Summary of the samples whose timestamp falls inside one of ``windows`` (pairs of
+        ``datetime``; all samples when empty): the sampler is started before the warm-up steps so
+        that its own start-up is not inside a timed region."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
         self.proc.terminate()
@@ -87,11 +91,15 @@ class ClockSampler:
         with open(self.path) as f:
             for line in f:
                 c = [x.strip() for x in line.split(",")]
-                if len(c) < 9:
+                if len(c) < 10:
                     continue
                 try:
+                    ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f")
+                    c = c[1:]
                     clk, mx, pw = float(c[1]), float(c[2]), float(c[3])
                 except ValueError:
+                    continue
+                if windows and not any(a <= ts <= b for a, b in windows):
                     continue
                 smax.append(mx)
                 power.append(pw)
@@ -163,31 +171,38 @@ def run_ours(args) -> dict:
         local, _ = tr.train_step(step_no[0], batches[step_no[0] % 2])
         return local
 
+    windows, per_step, mallocs = [], [], []
+
     def timed(batches, steps):
         tr.world.barrier()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         l0 = _lib.launch_count()
-        e0.record()
+        a0 = torch.cuda.memory_stats().get("num_device_alloc", 0)
+        t0 = datetime.datetime.now()
+        marks[0].record()
         last = None
-        for _ in range(steps):
+        for i in range(steps):
             last = one(batches)
-        e1.record()
+            marks[i + 1].record()
         torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        windows.append((t0, datetime.datetime.now()))
+        mallocs.append(torch.cuda.memory_stats().get("num_device_alloc", 0) - a0)
+        per_step.append([marks[i].elapsed_time(marks[i + 1]) for i in range(steps)])
+        ms = torch.tensor([marks[0].elapsed_time(marks[steps])], dtype=torch.float64, device=dev)
         tr.world.barrier()
         if world_size > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()), _lib.launch_count() - l0, last
 
+    sampler = ClockSampler(rank == 0)          # started ahead of the warm-up; only samples inside the timed windows count
     for _ in range(args.warmup):
         one(resident)
-    sampler = ClockSampler(rank == 0)
     ms_dev, launches, last = timed(resident, args.steps)
     for _ in range(1):
         one(host)
     ms_e2e, _, last_e2e = timed(host, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(windows) if rank == 0 else None
     tokens = args.batch * args.seq * args.steps
     # the loss lives on the last stage (rank 0 may be a first-stage rank); every last-stage replica reports the
     # sum over its own microbatches divided by M/R, so the mean over those replicas is the batch loss
@@ -218,6 +233,8 @@ def run_ours(args) -> dict:
         "gpu_launches": launches,
         "outer_sync_ms_incl_peer_wait": float(osync.item()),
         "loss": float(loss_t.item()),
+        "step_ms_rank0": {"device_resident_inputs": per_step[0], "e2e": per_step[1]},
+        "cuda_mallocs_in_timed_regions_rank0": mallocs,
         "host_enqueue_ms_last_step": tr.last_enqueue_s * 1e3,
         "device_phases_ms_last_step_rank0": tr.last_phase_ms,
     }
