@@ -110,6 +110,7 @@ class TrainConfig(BaseConfig):
     seed: int = 42
     max_norm: float = 1.0
     step_timeout: float = 60
+    deterministic: bool = False  # (added) fixed order of additions in the gradient kernels (sorted embedding scatter, no split-K)
     inner_optimizer: OptimizerConfig
     outer_optimizer: OptimizerConfig
     scheduler: SchedulerConfig = SchedulerConfig()

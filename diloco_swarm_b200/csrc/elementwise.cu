@@ -365,6 +365,53 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
   }
 }
 
+// Deterministic twin of the dwte part: `sorted` holds the token ids of the microbatch in ascending order (stable
+// sort), `perm` the row each came from.  One warp per sorted position; the warp at the head of a run of equal
+// ids adds the rows of the run in their original order and writes the sum with plain stores, so every dwte row
+// has one writer and a fixed order of additions.  d <= 2048.
+__global__ void __launch_bounds__(256)
+embedding_bwd_sorted_kernel(const long long* __restrict__ sorted, const long long* __restrict__ perm,
+                            const __nv_bfloat16* __restrict__ dx, float* __restrict__ dwte, int N, int d, int V) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (i >= N) return;
+  const long long id = sorted[i];
+  if (i > 0 && sorted[i - 1] == id) return;           // not the head of its run
+  const long long tgt = (id < 0 || id >= V) ? 0 : id;  // same clamp as the atomic kernel
+  for (int c0 = 0; c0 < d; c0 += 256) {
+    const int col = c0 + lane * 8;
+    if (col >= d) break;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = i; j < N && sorted[j] == id; ++j) {
+      float v[8];
+      load8(dx + perm[j] * (long long)d + col, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    float* w = dwte + tgt * d + col;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w[k] += acc[k];
+  }
+}
+// dwpe[t, :] += sum_b dx[b, t, :] alone (fixed order over b)
+__global__ void __launch_bounds__(256)
+embedding_bwd_pos_kernel(const __nv_bfloat16* __restrict__ dx, float* __restrict__ dwpe, int B, int T, int d) {
+  const int per_row = d / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)T * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / per_row), col = int(i % per_row) * 8;
+    float pos[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int b = 0; b < B; ++b) {
+      float v[8];
+      load8(dx + (long long)(b * T + t) * d + col, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pos[j] += v[j];
+    }
+    float* p = dwpe + (long long)t * d + col;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] += pos[j];
+  }
+}
+
 // ------------------------------------------------------------------ cross-entropy
 // count[0] = number of rows with mask != 0
 __global__ void mask_count_kernel(const long long* __restrict__ mask, int M, float* __restrict__ count) {
@@ -544,6 +591,19 @@ extern "C" int dsw_embedding_bwd(const long long* ids, const void* dx, float* dw
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Same result as dsw_embedding_bwd with a fixed order of additions: sorted / perm = stable ascending sort of the
+// B*T token ids and the rows they came from.  Ids outside [0, V) fall on row 0 as in the atomic kernel; when both
+// negative and too-large ids occur in one microbatch, row 0 has more than one writer (inputs are validated upstream).
+extern "C" int dsw_embedding_bwd_sorted(const long long* sorted, const long long* perm, const void* dx, float* dwte,
+                                        float* dwpe, int B, int T, int d, int V, cudaStream_t st) {
+  if (d % 8 || d > 2048) return -10;
+  const long long N = (long long)B * T;
+  embedding_bwd_sorted_kernel<<<(unsigned)((N * 32 + 255) / 256), 256, 0, st>>>(sorted, perm, (const bf16*)dx, dwte,
+                                                                                  (int)N, d, V);
+  embedding_bwd_pos_kernel<<<grid_for((long long)T * (d / 8), 256), 256, 0, st>>>((const bf16*)dx, dwpe, B, T, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 // count must be zeroed by the caller before dsw_mask_count.
 extern "C" int dsw_mask_count(const long long* mask, int M, float* count, cudaStream_t st) {
   mask_count_kernel<<<grid_for(M, 256, 64), 256, 0, st>>>(mask, M, count);
@@ -577,6 +637,7 @@ extern "C" int dsw_load_elementwise() {
   L(layernorm_bwd_kernel<1>); L(layernorm_bwd_kernel<2>); L(layernorm_bwd_kernel<3>); L(layernorm_bwd_kernel<4>);
   L(layernorm_bwd_kernel<5>); L(layernorm_bwd_kernel<6>); L(layernorm_bwd_kernel<7>); L(layernorm_bwd_kernel<8>);
   L(layernorm_bwd_finish_kernel); L(colsum_kernel); L(embedding_fwd_kernel); L(embedding_bwd_kernel);
+  L(embedding_bwd_sorted_kernel); L(embedding_bwd_pos_kernel);
   L(mask_count_kernel); L(cross_entropy_kernel); L(cast_f32_bf16_kernel); L(cast_bf16_f32_kernel);
 #undef L
   return bad ? -1 : 0;

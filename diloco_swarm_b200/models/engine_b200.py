@@ -59,6 +59,7 @@ class B200Engine:
         d = cfg.n_embd
         assert d % 8 == 0 and cfg.vocab_size % 8 == 0, "n_embd and vocab_size must be multiples of 8"
         assert cfg.bias, "the b200 engine implements the reference's bias=True model"
+        K.set_deterministic(bool(getattr(config.train, "deterministic", False)))
 
         # ---- flat layout ------------------------------------------------
         self.offsets: Dict[str, Tuple[int, Tuple[int, ...]]] = {}

@@ -29,6 +29,7 @@ _SIGS = {
     "dsw_colsum_accum": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p],
     "dsw_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "dsw_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "dsw_embedding_bwd_sorted": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "dsw_mask_count": [c_void_p, c_int, c_void_p, c_void_p],
     "dsw_cross_entropy": [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int,
                           c_void_p, c_void_p],

@@ -101,9 +101,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Tru
     return out
 
 
+_DETERMINISTIC = False
+
+
+def set_deterministic(on: bool) -> None:
+    """Fixed order of floating-point additions in the gradient kernels that
+    otherwise use atomics: the token-embedding scatter goes through a stable
+    sort with one writer per row, and weight gradients are not split along K
+    (each output tile then has one writer per launch, and launches are ordered
+    by the stream).  Slower; meant for debugging and regression runs."""
+    global _DETERMINISTIC
+    _DETERMINISTIC = bool(on)
+
+
 def wgrad_split(M: int, N: int, K: int) -> int:
     """Split-K factor for dW[M,N] = dy^T x with K = tokens: the weight gradients
     of a block have few output tiles, so K is split until the SMs are full."""
+    if _DETERMINISTIC:
+        return 1
     bm, units = (256, _NUM_SMS // 2) if (_USE_PAIR and M >= 256) else (128, _NUM_SMS)
     tiles = math.ceil(M / bm) * math.ceil(N / 256)
     if tiles >= 4 * units:
@@ -183,6 +198,11 @@ def embedding_bwd(ids: torch.Tensor, dx: torch.Tensor, dwte: torch.Tensor, dwpe:
     B, T = ids.shape
     V, d = dwte.shape
     assert dx.dtype == BF16 and dx.is_contiguous() and dwte.dtype == F32
+    if _DETERMINISTIC:
+        srt, perm = torch.sort(ids.reshape(-1), stable=True)
+        check(cuda_lib().dsw_embedding_bwd_sorted(srt.data_ptr(), perm.data_ptr(), dx.data_ptr(), dwte.data_ptr(),
+                                                  dwpe.data_ptr(), B, T, d, V, stream_ptr()), "dsw_embedding_bwd_sorted")
+        return
     check(cuda_lib().dsw_embedding_bwd(ids.data_ptr(), dx.data_ptr(), dwte.data_ptr(), dwpe.data_ptr(), B, T, d, V,
                                        stream_ptr()), "dsw_embedding_bwd")
 

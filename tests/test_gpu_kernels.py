@@ -127,3 +127,31 @@ def test_sgd_nesterov():
         opt.step()
         K.sgd_step(p, g.clone(), buf, None, 0.1, 0.9, True, None, zero_grad=False)
     assert torch.allclose(p, ref_p.data, atol=1e-5)
+
+
+def test_embedding_bwd_deterministic_mode():
+    """The sorted scatter (one writer per row, rows added in their original order) gives the same
+    gradient as a plain fp32 index_add, twice in a row bit for bit."""
+    from diloco_swarm_b200.ops import kernels as K
+    torch.manual_seed(5)
+    B, T, d, V = 4, 256, 128, 512
+    ids = torch.randint(0, 40, (B, T), device="cuda")            # few distinct ids: long runs
+    ids[0, :7] = V - 1
+    dx = torch.randn(B * T, d, device="cuda").to(torch.bfloat16)
+    outs = []
+    K.set_deterministic(True)
+    try:
+        for _ in range(2):
+            dwte = torch.zeros(V, d, device="cuda")
+            dwpe = torch.zeros(T, d, device="cuda")
+            K.embedding_bwd(ids, dx, dwte, dwpe)
+            torch.cuda.synchronize()
+            outs.append((dwte, dwpe))
+        assert K.wgrad_split(768, 768, 16384) == 1
+    finally:
+        K.set_deterministic(False)
+    ref_wte = torch.zeros(V, d, device="cuda").index_add_(0, ids.view(-1), dx.float())
+    ref_wpe = dx.float().view(B, T, d).sum(0)
+    assert torch.allclose(outs[0][0], ref_wte, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(outs[0][1], ref_wpe, atol=1e-3, rtol=1e-4)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
