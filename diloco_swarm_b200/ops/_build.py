@@ -98,7 +98,7 @@ def build_cuda(force: bool = False, verbose: bool = False, jobs: int = 8) -> str
             msgs.append(open(o).read()[-4000:])
         raise RuntimeError("nvcc failed for " + ", ".join(failed) + "\n" + "\n".join(msgs))
     tmp = CUDA_LIB + f".tmp{os.getpid()}"
-    cmd = [nvcc, "-shared", "-o", tmp] + objs
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp] + objs
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
     subprocess.check_call(cmd)
