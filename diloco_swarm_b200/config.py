@@ -171,6 +171,10 @@ class ElasticConfig(BaseConfig):
     # host-side fault injection for tests: this rank announces a leave and exits after that step
     leave_rank: int = -1
     leave_after_step: int = -1
+    # ... and this rank exits without a word at the start of that step, after the step's routing
+    # has been fixed with it in (the others find out by their transfers failing or timing out)
+    die_rank: int = -1
+    die_at_step: int = -1
 
 
 class CkptConfig(BaseConfig):

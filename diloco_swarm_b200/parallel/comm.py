@@ -42,6 +42,7 @@ class PipelineComm:
         self._next_post = 0
         self._sends: List[Tuple[object, torch.Tensor]] = []
         self.deadline: Optional[float] = None
+        self.tolerant = False        # set with membership tracking: a failed transfer ends the step like a timeout
         self.bytes_sent = 0
 
     # -- set-up --------------------------------------------------------------
@@ -115,7 +116,9 @@ class PipelineComm:
         try:
             work.wait(timeout=datetime.timedelta(seconds=remaining))
         except RuntimeError as e:
-            if "imeout" in str(e) or "timed out" in str(e):
+            # with membership tracking a transfer that fails because its peer is gone ends the step
+            # the same way a timeout does
+            if self.tolerant or "imeout" in str(e) or "timed out" in str(e):
                 raise StepTimeout(str(e)) from e
             raise
 

@@ -13,7 +13,12 @@ this module maintains it on the host, between steps, over a TCP store:
   ``done`` marks of step t-1 from every rank it believed alive, drops the ranks
   that announced a leave or did not report, and publishes ``alive/<t>``; all
   other ranks wait for that key.  Everybody therefore routes step t with the
-  same mask, and nobody launches work for a rank that is gone.
+  same mask, and nobody launches work for a rank that is gone;
+* a rank that dies without a word is noticed inside a step: transfers with it
+  fail or time out.  After its pipeline work every rank votes ``ok/<step>/<rank>``;
+  the coordinator publishes one verdict per step (all present and all fine, or
+  not), so either every live rank applies the step's gradients or none does, and
+  the ranks that did not vote are dropped before the next step.
 
 Failures are only ever injected on the host (a rank that leaves, a rank that
 stops reporting); nothing here touches a device.  The coordinator itself is
@@ -35,6 +40,7 @@ class Membership:
                                    timeout=datetime.timedelta(seconds=max(60.0, 4 * timeout_s)),
                                    wait_for_workers=True)
         self.alive: List[bool] = [True] * world_size
+        self._silent: set = set()          # coordinator: ranks that missed a vote
 
     # -- participants -------------------------------------------------------
     def announce_leave(self, last_step: int) -> None:
@@ -54,9 +60,32 @@ class Membership:
         self.alive = [c == "1" for c in mask]
         return list(self.alive)
 
+    def vote(self, step: int, ok: bool, wait_s: float) -> bool:
+        """Common verdict on ``step``: True when every live rank reports that its part of the step went
+        through.  ``wait_s`` bounds how long the coordinator waits for the votes (a rank may still be
+        inside its step's own timeout)."""
+        self.store.set(f"ok/{step}/{self.rank}", "1" if ok else "0")
+        if self.rank == 0:
+            deadline = time.time() + wait_s
+            pending = [r for r in range(self.world_size) if self.alive[r]]
+            while pending and time.time() < deadline:
+                pending = [r for r in pending if not self.store.check([f"ok/{step}/{r}"])]
+                if pending:
+                    time.sleep(0.01)
+            self._silent.update(pending)
+            fine = not pending and all(self.store.get(f"ok/{step}/{r}") == b"1"
+                                       for r in range(self.world_size) if self.alive[r])
+            self.store.set(f"verdict/{step}", "1" if fine else "0")
+        key = f"verdict/{step}"
+        self.store.wait([key], datetime.timedelta(seconds=wait_s + 4 * self.timeout_s + 30))
+        return self.store.get(key) == b"1"
+
     # -- coordinator ----------------------------------------------------------
     def _publish(self, step: int) -> None:
         alive = list(self.alive)
+        for r in self._silent:                     # missed a vote: gone, no need to wait for its report
+            alive[r] = False
+        self._silent = set()
         if step > 1:
             deadline = time.time() + self.timeout_s
             pending = [r for r in range(self.world_size) if alive[r] and r != 0]

@@ -84,6 +84,7 @@ class Trainer:
             self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
         self.alive: Optional[List[bool]] = None
+        self._step_failed = False    # the last step was dropped by the common verdict
         self.membership = None
         if config.elastic.enable and w.world_size > 1:
             if self.engine.name != "torch":
@@ -91,6 +92,7 @@ class Trainer:
                                           "the fused collectives would have to re-map their peer buffers")
             from .parallel.liveness import Membership
             self.membership = Membership(w.rank, w.world_size, w.master_addr, w.master_port + 1, config.elastic.timeout)
+            self.comm.tolerant = True
         self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
         self.num_train_steps = 0
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
@@ -126,16 +128,28 @@ class Trainer:
                 gone = [r for r, a in enumerate(mask) if not a]
                 self.logger.log_message(f"Step {step}: ranks {gone} are gone, re-routing around them",
                                         master=False, level=Level.WARNING)
-                self.world.regroup(mask)
+                self.world.regroup(mask, rebuild_p2p=self._step_failed)
+                self._step_failed = False
                 self.micro_per_device = max(1, self.num_micro // len(self.world.last_stage_ranks))
                 self.loss_scale = 1.0 / self.micro_per_device
             self.alive = mask
+        if self._step_failed:
+            # the last step was abandoned with transfers in flight and nobody left: fresh pipeline groups
+            # all the same, so that its leftovers cannot meet this step's messages
+            self.world.regroup(mask, rebuild_p2p=True)
+            self._step_failed = False
 
     def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Optional[Outputs]]:
         cfg, w, eng, comm = self.config, self.world, self.engine, self.comm
         start = time.time()
         if self.membership is not None:
             self._update_membership(step)
+            el = cfg.elastic
+            if el.die_rank == w.rank and el.die_at_step == step:
+                # host-side fault injection: the step's routing counts on this rank and it is gone
+                self.logger.log_message(f"Rank {w.rank} dies silently at step {step}", master=False, level=Level.WARNING)
+                self.logger.close()
+                os._exit(0)
         eng.train()
         eng.zero_grad()
         _, ops = self._plan(step, 0, forward_only=False)
@@ -149,10 +163,12 @@ class Trainer:
         # gradient all-reduce, that backward sends each bucket as soon as it is complete
         last_bwd = max((i for i, op in enumerate(ops) if op.kind in (BWD, FWD_BWD)), default=-1)
         sync_here = do_sync and not eng.has_outer
-        comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
         pipeline_phase = self.timer.phase("pipeline")
         pipeline_phase.__enter__()
+        failed = False
+        tolerated = (StepTimeout, RuntimeError) if self.membership is not None else (StepTimeout,)
         try:
+            comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
             for i, op in enumerate(ops):
                 rows = D.micro_batch_rows(op.mb, self.mbs)
                 if op.kind == BWD:
@@ -175,22 +191,35 @@ class Trainer:
                     if op.prev >= 0:
                         comm.send_backward(dx, op.prev)
             comm.end_step()
-        except StepTimeout:
-            self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
+        except tolerated as e:
+            failed = True
+            self.logger.log_message(f"Train step {step} timed out" if isinstance(e, StepTimeout) and "imeout" in str(e)
+                                    else f"Train step {step} failed: {type(e).__name__}: {str(e)[:200]}",
+                                    master=False, level=Level.WARNING)
             comm.abandon_step()
         finally:
             pipeline_phase.__exit__(None, None, None)
 
-        if do_sync and not eng.has_outer:
-            with self.timer.phase("grad_sync"):
-                eng.sync_gradients()
         lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
-        with self.timer.phase("optimizer"):
-            norm = eng.optimizer_step(lr, cfg.train.max_norm)
-        self.opt_steps += 1
-        if do_sync and eng.has_outer:
-            with self.timer.phase("outer_sync"):
-                eng.outer_step()
+        applied = True
+        if self.membership is not None:
+            # one verdict for everybody: either every live rank applies this step or none does
+            applied = self.membership.vote(step, not failed, cfg.train.step_timeout + cfg.elastic.timeout)
+            if not applied:
+                self._step_failed = True
+                self.logger.log_message(f"Step {step} is dropped: not every rank got through it", master=False,
+                                        level=Level.WARNING)
+        norm = 0.0
+        if applied:
+            if do_sync and not eng.has_outer:
+                with self.timer.phase("grad_sync"):
+                    eng.sync_gradients()
+            with self.timer.phase("optimizer"):
+                norm = eng.optimizer_step(lr, cfg.train.max_norm)
+            self.opt_steps += 1
+            if do_sync and eng.has_outer:
+                with self.timer.phase("outer_sync"):
+                    eng.outer_step()
         self.last_enqueue_s = time.time() - start   # host time to queue the whole step
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
         if self.device.type == "cuda":
@@ -202,7 +231,7 @@ class Trainer:
         local = Outputs(step=step, lr=lr, loss=loss_val, tokens=n_local * tokens_per_mb, norm=float(norm),
                         time=step_time, micro_step_time=step_time / self.micro_per_device,
                         num_micro_batches=n_local)
-        stage = sync_outputs(w, local, self.device) if do_sync else None
+        stage = sync_outputs(w, local, self.device) if (do_sync and applied) else None
         if self.membership is not None:
             self.membership.end_step(step)
         return local, stage

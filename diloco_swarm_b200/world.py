@@ -85,10 +85,13 @@ class World:
         self.first_last_stage_group = dist.new_group(fl, timeout=timeout)
         self.barrier()
 
-    def regroup(self, alive: List[bool]) -> None:
+    def regroup(self, alive: List[bool], rebuild_p2p: bool = False) -> None:
         """Shrink this rank's view of the world to the live ranks: stage membership, leaders and the
         stage group used by the collectives (created among the live members only).  Point-to-point
-        groups are left alone: transfers only ever involve two live ranks."""
+        groups are left alone after a clean leave: transfers only ever involve two live ranks.
+        After a step that failed half-way, ``rebuild_p2p`` also replaces the pipeline groups, so that
+        receives still posted for the abandoned step can never match a later send.  Every live rank
+        must make the same call."""
         S = self.num_stages
         self.stage2ranks = {s: [r for r in range(self.world_size) if r % S == s and alive[r]] for s in range(S)}
         for s in range(S):
@@ -100,7 +103,20 @@ class World:
         mine = self.stage2ranks[self.stage]
         self.num_replicas = len(mine)
         self.replica_index = mine.index(self.rank)
-        self.curr_stage_group = (dist.new_group(mine, use_local_synchronization=True) if len(mine) > 1 else None)
+        # Member-only group creation keys its rendezvous on how many groups the process has made so far,
+        # so every live rank makes the same calls in the same order, with one-rank groups as fillers
+        # where it is not a member (two live ranks whose counts differ would wait for each other forever).
+        g = dist.new_group(mine, use_local_synchronization=True)
+        self.curr_stage_group = g if len(mine) > 1 else None
+        if rebuild_p2p:
+            for b in range(S - 1):                 # ascending on every rank: the rendezvous chain starts at boundary 0
+                members = self.stage2ranks[b] + self.stage2ranks[b + 1]
+                if self.rank in members:
+                    self.fwd_groups[b] = dist.new_group(members, use_local_synchronization=True)
+                    self.bwd_groups[b] = dist.new_group(members, use_local_synchronization=True)
+                else:
+                    dist.new_group([self.rank], use_local_synchronization=True)
+                    dist.new_group([self.rank], use_local_synchronization=True)
 
     def barrier(self) -> None:
         if dist.is_initialized():

@@ -160,6 +160,26 @@ def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
     assert f"Rank {leaver} leaves after step 2" in open(f"{LOG}/{name}/{leaver}.log").read()
 
 
+@pytest.mark.parametrize("victim", [3, 2])
+def test_rank_dies_silently_and_the_step_is_dropped(victim):
+    """Host-side failure without notice: a replica exits at the start of step 3, after the step's routing
+    was fixed with it in.  The others' transfers with it fail or time out, the common verdict drops the
+    step on every live rank, the rank that did not vote is removed before step 4 and training goes on
+    (fresh pipeline groups, re-formed stage group)."""
+    name = f"die{victim}"
+    launch(name, 4, 2, ["--elastic.enable", "true", "--elastic.timeout", "6", "--train.step_timeout", "6",
+                        "--elastic.die_rank", str(victim), "--elastic.die_at_step", "3", "--train.max_steps", "6"],
+           timeout=300)
+    losses = global_losses(name)
+    assert len(losses) == 5 and losses[-1] < losses[0], losses          # steps 1, 2, 4, 5, 6
+    logs = {r: open(f"{LOG}/{name}/{r}.log").read() for r in range(4)}
+    assert f"Rank {victim} dies silently at step 3" in logs[victim]
+    for r in range(4):
+        if r != victim:
+            assert "Step 3 is dropped" in logs[r], r
+            assert f"Step 4: ranks [{victim}] are gone" in logs[r], r
+
+
 def test_tiny_diloco_swarm_2x2_matches_single_process_replay():
     """Tiny GPT-2 (2 layers, d 128, 4 heads, tied embeddings requested, vocab 50257, seq 128, fp32) as
     DiLoCo-SWARM on 2 stages x 2 replicas over gloo: microbatch 4, 4 microbatches per step, AdamW 4e-4
