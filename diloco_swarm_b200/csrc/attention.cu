@@ -2,7 +2,7 @@
 //
 // Replaces the reference's F.scaled_dot_product_attention(q, k, v, is_causal=True)
 // (src/model.py:66-67).  Input is the packed [B*T, 3*d] output of the QKV
-// projection (Q | K | V, head h at columns h*64 of each part); output is the
+// projection (Q | K | V, head h at columns h*hs of each part); output is the
 // [B*T, d] tensor that feeds the output projection, plus the per-row log-sum-exp
 // that the backward pass needs.
 //
@@ -45,7 +45,7 @@ __device__ __forceinline__ void att_load_tile(void* dst, const CUtensorMap* tm, 
 }
 
 // Optional in-kernel timeline for tuning: when a trace buffer is registered (dsw_attention_set_trace),
-// CTA (0,0) stores %globaltimer values at its phase boundaries: [0,256) row-warp 0, [256,512) MMA thread.
+// CTA 0 stores %globaltimer values at its phase boundaries: [0,256) row-warp 0, [256,512) MMA thread.
 __device__ __forceinline__ long long gtimer() {
   long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -53,7 +53,7 @@ __device__ __forceinline__ long long gtimer() {
 }
 #define ATT_TRACE(buf, base, slot) do { if ((buf) != nullptr && (slot) < 256) (buf)[(base) + (slot)++] = gtimer(); } while (0)
 
-constexpr int ATT_BQ = 128;        // query rows per CTA
+constexpr int ATT_BQ = 128;        // query rows per work item
 constexpr int ATT_BK = 128;        // kv rows per step
 constexpr int ATT_HS = 64;
 constexpr int ATT_THREADS = 256;          // warps 0-3 softmax, 4 MMA, 5 TMA, 6-7 only lend their registers
