@@ -119,3 +119,45 @@ def test_balanced_routing_gives_equal_shares_and_uniform_marginals():
     for s in (1, 2):
         v = collections.Counter(p[:, s].tolist()).values()
         assert max(v) - min(v) <= 1
+
+
+def test_random_worlds_masks_and_modes_never_deadlock():
+    """Property test: for random stage counts, replica counts, microbatch counts, in-flight caps, routing
+    modes and live masks (at least one live replica per stage), every rank's plan completes when replayed
+    over in-order channels, dead ranks get no work and the cap holds."""
+    hyp = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    @st.composite
+    def worlds(draw):
+        stages = draw(st.integers(1, 4))
+        replicas = draw(st.integers(1, 4))
+        world = stages * replicas
+        alive = [True] * world
+        for s in range(stages):
+            dead = draw(st.lists(st.integers(0, replicas - 1), max_size=replicas - 1, unique=True))
+            for k in dead:
+                alive[s + k * stages] = False
+        return (stages, world, alive, draw(st.integers(1, 24)), draw(st.integers(1, 5)),
+                draw(st.sampled_from(["uniform", "balanced"])), draw(st.integers(0, 1000)), draw(st.integers(1, 50)))
+
+    @settings(max_examples=150, deadline=None)
+    @given(worlds())
+    def check(w):
+        stages, world, alive, M, cap, mode, seed, step = w
+        path = S.route(seed, step, stages, world, M, alive, mode=mode)
+        assert all(alive[int(r)] for r in path.reshape(-1))
+        plans = {r: S.plan(path, world, r, cap) for r in range(world)}
+        for r in range(world):
+            if not alive[r]:
+                assert plans[r] == []
+            inflight = 0
+            for op in plans[r]:
+                if op.kind == S.FWD:
+                    inflight += 1
+                    assert inflight <= cap
+                elif op.kind == S.BWD:
+                    inflight -= 1
+        assert _simulate(plans, world)
+
+    check()
