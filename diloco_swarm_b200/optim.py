@@ -53,3 +53,44 @@ def nesterov_reference(theta_g: torch.Tensor, delta: torch.Tensor, buf: Optional
     buf = delta.clone() if buf is None else momentum * buf + delta
     upd = delta + momentum * buf if nesterov else buf
     return theta_g - lr * upd, buf
+
+
+# ---------------------------------------------------------------------- DiLoCo helpers on modules
+# The engines carry their own outer state (flat fp32 buffers on the GPU, sharded across replicas in the
+# fused path).  These three functions are the module-level form of the same steps, for code written against
+# the reference's helpers (src/utils.py:213-226): the outer copy stays where the caller puts it, by default
+# on the device of the inner model (the reference moves it to the host and pays two copies per outer step).
+def get_outer_model(inner_model: torch.nn.Module, device: Optional[torch.device] = None) -> torch.nn.Module:
+    import copy
+    outer = copy.deepcopy(inner_model)
+    return outer.to(device) if device is not None else outer
+
+
+@torch.no_grad()
+def compute_pseudo_gradient(inner_model: torch.nn.Module, outer_model: torch.nn.Module) -> None:
+    """outer.grad <- outer - inner, parameter by parameter."""
+    for po, pi in zip(outer_model.parameters(), inner_model.parameters()):
+        po.grad = po.detach() - pi.detach().to(po.device, po.dtype)
+
+
+@torch.no_grad()
+def sync_inner_model(outer_model: torch.nn.Module, inner_model: torch.nn.Module) -> None:
+    """inner <- outer, parameter by parameter."""
+    for po, pi in zip(outer_model.parameters(), inner_model.parameters()):
+        pi.copy_(po.detach().to(pi.device, pi.dtype))
+
+
+# ---------------------------------------------------------------------- factories under the reference's names
+def get_optimizer(model, optimizer_config) -> Optional[torch.optim.Optimizer]:
+    """torch optimiser over ``model.parameters()`` (one group), or None for ``type = "None"``
+    (reference: src/utils.py:59-65)."""
+    if optimizer_config.type == "None":
+        return None
+    return make_inner_optimizer(model.parameters(), optimizer_config)
+
+
+def get_scheduler(optimizer: torch.optim.Optimizer, scheduler_config, num_steps: int = 0):
+    """LambdaLR that follows ``lr_factor``: linear warm-up then constant as in the reference
+    (src/utils.py:78-85), or warm-up plus cosine when ``scheduler_config.type == "cosine"``
+    (``num_steps`` is then the length of the run)."""
+    return torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: lr_factor(step, scheduler_config, num_steps))

@@ -37,6 +37,29 @@ from .utils.misc import format_float, format_int, get_device, seed_everything
 from .world import World
 
 
+def _gpt2_config(mc) -> GPT2Config:
+    return GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer, n_head=mc.n_head,
+                      n_embd=mc.n_embd, dropout=mc.dropout, bias=mc.bias, parameter_sharing=mc.parameter_sharing)
+
+
+def get_model(model_config, seed: int = 42):
+    """The whole GPT-2 as one autograd module (reference: get_model, src/utils.py:48-49)."""
+    from .models.gpt2 import TorchStage
+    return TorchStage(_gpt2_config(model_config), 0, 1, seed=seed)
+
+
+def get_sharded_model(model_config, world: World, seed: int = 42, layer_split: str = "even"):
+    """This rank's pipeline stage as an autograd module (reference: get_sharded_model,
+    src/utils.py:51-52).  Only the stage's own tensors are built; the per-tensor seeded init makes them
+    equal to the corresponding tensors of ``get_model`` with the same seed."""
+    from .models.gpt2 import TorchStage
+    return TorchStage(_gpt2_config(model_config), world.stage, world.num_stages, seed=seed, layer_split=layer_split)
+
+
+def get_logger(world: World, logging_config) -> Logger:
+    return Logger(world, logging_config)
+
+
 def make_engine(config: Config, world: World, device: torch.device):
     mc = config.model
     gcfg = GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer,

@@ -203,6 +203,49 @@ def get_micro_batches(batch: Dict[str, torch.Tensor], micro_batch_size: int, fir
         yield first_stage_ranks[mb % r0], mb // r0 + 1, {k: v[rows] for k, v in batch.items()}
 
 
+class BatchData:
+    """A collated batch seen as a dataset of rows (reference: src/sampler.py:6-14)."""
+
+    def __init__(self, batch: Dict[str, torch.Tensor]):
+        self.batch = batch
+
+    def __len__(self) -> int:
+        return next(iter(self.batch.values())).size(0)
+
+    def __getitem__(self, idx: int) -> Dict[str, torch.Tensor]:
+        return {k: (v[idx] if v is not None else None) for k, v in self.batch.items()}
+
+
+class BatchSampler:
+    """Row indices of a batch that belong to ``rank`` when the rows are dealt out to ``ranks`` in
+    round-robin chunks of ``micro_batch_size`` (reference: src/sampler.py:16-39).  The training loop
+    itself does not iterate rows: it slices whole microbatches with ``micro_batch_rows``; this class
+    states the same partition row by row and is checked against it in the tests."""
+
+    def __init__(self, dataset, rank: int, ranks: Sequence[int], micro_batch_size: int):
+        self.n, self.mbs = len(dataset), micro_batch_size
+        self.slot, self.width = list(ranks).index(rank), len(ranks)
+
+    def __iter__(self) -> Iterator[int]:
+        n_chunks = (self.n + self.mbs - 1) // self.mbs
+        for chunk in range(self.slot, n_chunks, self.width):
+            yield from range(chunk * self.mbs, min((chunk + 1) * self.mbs, self.n))
+
+    def __len__(self) -> int:
+        return sum(1 for _ in self)
+
+
+def get_dataloader(dataset: TokenDataset, batch_size: int, shuffle: bool = False, pin_memory: bool = False,
+                   num_workers: int = 0) -> BatchLoader:
+    """The reference's loader factory (src/utils.py:117-118): sequential drop-last batches.  Batches are
+    slices of one resident tensor, so there are no worker processes to start (``num_workers`` is accepted
+    and ignored); ``shuffle`` permutes the dataset once, seeded, before batching."""
+    if shuffle:
+        g = torch.Generator().manual_seed(0)
+        dataset = dataset.select(torch.randperm(len(dataset), generator=g).tolist())
+    return BatchLoader(dataset, batch_size, pin_memory=pin_memory)
+
+
 def get_num_steps(max_steps: int, max_epochs: int, num_examples: int, batch_size: int) -> int:
     """Whichever of max_steps / max_epochs is reached first (src/utils.py:145-152)."""
     if num_examples < batch_size:

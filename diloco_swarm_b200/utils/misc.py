@@ -42,3 +42,30 @@ def format_int(num: float, prec: int = 2) -> str:
 
 def format_float(num: float, prec: int = 2) -> str:
     return f"{num:.{prec}f}"
+
+
+def get_hf_cache_dir() -> str:
+    """Where Hugging Face downloads go (reference: src/utils.py:31-34 reads PERSISTENT_DIR from .env)."""
+    import os
+    base = os.environ.get("PERSISTENT_DIR") or os.environ.get("HF_HOME") or os.path.expanduser("~/.cache/huggingface")
+    return os.path.join(base, "huggingface") if os.environ.get("PERSISTENT_DIR") else base
+
+
+def nullcontext():
+    import contextlib
+    return contextlib.nullcontext()
+
+
+def get_train_pbar_description(metrics, prefix: str) -> str:
+    """One-line progress text from a Metrics object (same fields as the reference's progress bar,
+    src/utils.py:128-137)."""
+    m, n = metrics.compute(), metrics.name
+    g = lambda k: m.get(f"{n}/{k}/current") or 0.0
+    return (f"{prefix} Step: {int(g('step'))} - Time: {g('time'):.1f}s - Loss: {g('loss'):.4f} - "
+            f"Norm: {g('norm'):.4f} - Perplexity: {g('perplexity'):.1f} - Throughput: {g('throughput'):.1f}")
+
+
+def get_eval_pbar_description(metrics, prefix: str) -> str:
+    m, n = metrics.compute(), metrics.name
+    return (f"{prefix} Avg. Loss: {m.get(f'{n}/loss/average') or 0.0:.4f}, "
+            f"Avg. Perplexity: {m.get(f'{n}/perplexity/average') or 0.0:.1f}")

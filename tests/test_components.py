@@ -164,3 +164,66 @@ def test_serializer_and_micro_batch_naming():
     got = [(r, l, mb["input_ids"][0, 0].item()) for r, l, mb in get_micro_batches(batch, 2, [0, 2])]
     # rank 0 owns chunks 0 and 2 (rows 0-1, 4-5), rank 2 owns chunks 1 and 3: [k*R*mbs + i*mbs, +mbs)
     assert got == [(0, 1, 0), (2, 1, 8), (0, 2, 16), (2, 2, 24)]
+
+
+def test_reference_named_helpers():
+    """Helpers that exist under the reference's names: the row sampler states the same partition as the
+    microbatch slices, the module-level DiLoCo helpers reproduce torch's SGD-Nesterov on pseudo-gradients,
+    the factories build what the trainer builds."""
+    import torch
+    from helpers import make_config
+    from diloco_swarm_b200 import optim as O
+    from diloco_swarm_b200.train import get_model, get_sharded_model
+    from diloco_swarm_b200.utils import data as D
+    from diloco_swarm_b200.utils.misc import get_eval_pbar_description, get_train_pbar_description
+    from diloco_swarm_b200.utils.metrics import Outputs, train_metrics
+    from diloco_swarm_b200.world import World
+
+    batch = {"input_ids": torch.arange(22).view(11, 2), "attention_mask": None}
+    ds = D.BatchData(batch)
+    assert len(ds) == 11 and ds[3]["input_ids"].tolist() == [6, 7] and ds[3]["attention_mask"] is None
+    ranks = [0, 2, 4]
+    rows = {r: list(D.BatchSampler(ds, r, ranks, 2)) for r in ranks}
+    assert rows == {0: [0, 1, 6, 7], 2: [2, 3, 8, 9], 4: [4, 5, 10]}
+    assert [len(D.BatchSampler(ds, r, ranks, 2)) for r in ranks] == [4, 4, 3]
+    for root, k, mb in D.get_micro_batches({"input_ids": torch.arange(24).view(12, 2)}, 2, ranks):
+        want = rows[root][2 * (k - 1): 2 * k] if root != 4 or k == 1 else [10, 11]
+        assert (mb["input_ids"][:, 0] // 2).tolist() == want
+
+    cfg = make_config(model={"n_layer": 2, "n_head": 2, "n_embd": 32, "vocab_size": 64, "block_size": 16})
+    whole = get_model(cfg.model, seed=3)
+    import os
+    os.environ.update(RANK="1", WORLD_SIZE="2")
+    try:
+        w = World(2, init=False)          # rank 1 of 2: the second pipeline stage
+    finally:
+        os.environ.pop("RANK"); os.environ.pop("WORLD_SIZE")
+    part = get_sharded_model(cfg.model, w, seed=3)
+    assert part.is_last and not part.is_first
+    sd = whole.state_dict()
+    first_block = part.layers[0]                      # state-dict block numbers are local to the stage
+    for k, v in part.state_dict().items():
+        bits = k.split(".")
+        if bits[1] == "h":
+            bits[2] = str(int(bits[2]) + first_block)
+        assert torch.equal(v, sd[".".join(bits)]), k
+
+    inner = torch.nn.Linear(4, 3)
+    outer = O.get_outer_model(inner)
+    opt = torch.optim.SGD(outer.parameters(), lr=0.7, momentum=0.9, nesterov=True)
+    theta, buf = outer.weight.detach().clone(), None
+    for _ in range(3):
+        with torch.no_grad():
+            inner.weight.add_(torch.randn_like(inner.weight) * 0.1)
+        O.compute_pseudo_gradient(inner, outer)
+        theta, buf = O.nesterov_reference(theta, outer.weight.grad.clone(), buf, 0.7, 0.9)
+        opt.step()
+        O.sync_inner_model(outer, inner)
+        assert torch.allclose(inner.weight, theta, atol=1e-6)
+    sched = O.get_scheduler(O.get_optimizer(inner, cfg.train.inner_optimizer), cfg.train.scheduler)
+    assert sched.get_last_lr()[0] <= cfg.train.inner_optimizer.lr
+
+    m = train_metrics("train/global")
+    m.update(Outputs(step=1, lr=1e-3, loss=2.0, tokens=10, norm=0.5, time=1.0, micro_step_time=0.5, num_micro_batches=2))
+    assert "Loss: 2.0000" in get_train_pbar_description(m, "[TRAIN]")
+    assert "Avg. Loss: 2.0000" in get_eval_pbar_description(m, "[EVAL]")
