@@ -109,6 +109,30 @@ def test_multiprocess_matches_virtual_swarm_diloco():
     assert max(abs(a - b) for a, b in zip(got, want)) < 2e-3, (got, want)
 
 
+def test_memorization_on_a_swarm():
+    """The reference's integration test (tests/test_memorize.py:76-84) on its SWARM topology, 4 processes
+    in 2 stages: train the 4-layer model on one sentence and find the sentence in master.log, where the
+    end-of-training samples are logged.  Offline the tokenizer is byte level (61 tokens instead of 14), so
+    the run is 200 steps of 4 one-row microbatches instead of 40 steps of one."""
+    from diloco_swarm_b200.utils.data import MEMORIZE_SENTENCE
+    shutil.rmtree(f"{LOG}/memorize", ignore_errors=True)
+    _port[0] += 3
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+           "--master-addr", "127.0.0.1", "--master-port", str(_port[0]), "-m", "diloco_swarm_b200.train",
+           "--swarm.num_stages", "2", "--device", "cpu", "--model", "@configs/model/gpt2-tiny.toml",
+           "--data", "@configs/data/memorize.toml", "--data.tokenize", "true", "--data.seq_length", "128",
+           "--train.inner_optimizer", "@configs/optimizer/adamw.toml", "--train.outer_optimizer",
+           "@configs/optimizer/none.toml", "--train.inner_optimizer.lr", "0.006", "--train.max_steps", "200",
+           "--train.batch_size", "4", "--train.micro_batch_size", "1", "--train.max_micro_batches", "2",
+           "--sample.max_new_tokens", "64", "--sample.temperature", "0.1", "--amp.enable", "false",
+           "--eval.enable", "false", "--logging.log_dir", LOG, "--logging.run_id", "memorize",
+           "--logging.console.log_level", "ERROR"]
+    p = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, OMP_NUM_THREADS="1"), timeout=600, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    text = open(f"{LOG}/memorize/master.log").read()
+    assert MEMORIZE_SENTENCE in text.split("Sample 1:")[-1], text[-1500:]
+
+
 def test_three_stage_pipeline_with_eval_and_sampling():
     launch("pp3", 3, 3, ["--eval.enable", "true", "--eval.eval_size", "0.1", "--eval.every_n_steps", "3",
                          "--sample.enable", "true", "--sample.max_new_tokens", "4", "--sample.num_samples", "2"])
