@@ -227,3 +227,25 @@ def test_reference_named_helpers():
     m.update(Outputs(step=1, lr=1e-3, loss=2.0, tokens=10, norm=0.5, time=1.0, micro_step_time=0.5, num_micro_batches=2))
     assert "Loss: 2.0000" in get_train_pbar_description(m, "[TRAIN]")
     assert "Avg. Loss: 2.0000" in get_eval_pbar_description(m, "[EVAL]")
+
+
+def test_pipeline_timing_model():
+    """The timing model replays the trainer's own routing and plans: closed forms for the trivial worlds,
+    more microbatches in flight never slow a pipeline down, balanced routing beats uniform on average."""
+    from diloco_swarm_b200.benchmarks.pipeline_model import simulate
+    one = simulate(1, 1, 8, 1, [2.0], [4.0], steps=3)
+    assert abs(one["step_ms_mean"] - 8 * 6.0) < 1e-9 and abs(one["busiest_rank_utilisation"] - 1.0) < 1e-9
+    # two equal stages, one replica each: with enough microbatches in flight only the fill and the drain are lost
+    deep = simulate(2, 1, 16, 16, [1.0, 1.0], [2.0, 2.0], steps=2)["step_ms_mean"]
+    assert 16 * 3.0 < deep <= 16 * 3.0 + 2 * 3.0 + 1e-9
+    shallow = simulate(2, 1, 16, 1, [1.0, 1.0], [2.0, 2.0], steps=2)["step_ms_mean"]
+    assert abs(shallow - 16 * 6.0) < 1e-9            # one in flight: the stages take turns
+    prev = None
+    for cap in (1, 2, 4, 8):
+        t = simulate(2, 2, 16, cap, [1.0, 1.1], [2.0, 2.1], xfer=0.05, steps=20)["step_ms_mean"]
+        assert prev is None or t <= prev + 1e-9
+        prev = t
+    uni = simulate(2, 4, 32, 8, [1.0, 1.0], [2.0, 2.0], routing="uniform", steps=60)
+    bal = simulate(2, 4, 32, 8, [1.0, 1.0], [2.0, 2.0], routing="balanced", steps=60)
+    assert bal["step_ms_mean"] < uni["step_ms_mean"]
+    assert abs(bal["busiest_last_stage_replica_vs_even_share"] - 1.0) < 1e-9 < uni["busiest_last_stage_replica_vs_even_share"] - 1.0
