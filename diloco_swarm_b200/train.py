@@ -332,10 +332,24 @@ class Trainer:
                 else:
                     ring.send_hidden(out)
             if multi:
-                dist.broadcast(state, src=w.last_stage_leader)
+                self._share_sample_state(state)
             if bool(state[0, total].item()):
                 break
         return [tokenizer.decode(row, skip_special_tokens=True) for row in state[:, :total].cpu()]
+
+    def _share_sample_state(self, state: torch.Tensor) -> None:
+        """New ids and stop flag from the last leader to everybody.  One broadcast while the world is
+        whole; once ranks are gone the broadcast's group would wait for them, so the last leader sends to
+        each live rank instead."""
+        w = self.world
+        if self.alive is None or all(self.alive):
+            dist.broadcast(state, src=w.last_stage_leader)
+        elif w.rank == w.last_stage_leader:
+            for r, a in enumerate(self.alive):
+                if a and r != w.rank:
+                    dist.send(state, dst=r)
+        else:
+            dist.recv(state, src=w.last_stage_leader)
 
     # ------------------------------------------------------------------
     def save_checkpoint(self, step: int) -> None:

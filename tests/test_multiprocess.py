@@ -193,7 +193,8 @@ def test_rank_dies_silently_and_the_step_is_dropped(victim):
     (fresh pipeline groups, re-formed stage group)."""
     name = f"die{victim}"
     launch(name, 4, 2, ["--elastic.enable", "true", "--elastic.timeout", "6", "--train.step_timeout", "6",
-                        "--elastic.die_rank", str(victim), "--elastic.die_at_step", "3", "--train.max_steps", "6"],
+                        "--elastic.die_rank", str(victim), "--elastic.die_at_step", "3", "--train.max_steps", "6",
+                        "--sample.enable", "true", "--sample.max_new_tokens", "3", "--sample.num_samples", "2"],
            timeout=300)
     losses = global_losses(name)
     assert len(losses) == 5 and losses[-1] < losses[0], losses          # steps 1, 2, 4, 5, 6
@@ -203,6 +204,7 @@ def test_rank_dies_silently_and_the_step_is_dropped(victim):
         if r != victim:
             assert "Step 3 is dropped" in logs[r], r
             assert f"Step 4: ranks [{victim}] are gone" in logs[r], r
+    assert "Sample 2:" in open(f"{LOG}/{name}/master.log").read()      # end-of-training sampling among the survivors
 
 
 def test_tiny_diloco_swarm_2x2_matches_single_process_replay():
