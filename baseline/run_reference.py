@@ -22,6 +22,7 @@ metric covers the same region (tokens / time spent in ``train_step``).
 """
 from __future__ import annotations
 
+import datetime
 import json
 import os
 import socket
@@ -143,6 +144,7 @@ def run_reference(args) -> dict:
 
     step_ms = []
     losses = []
+    stamps = []          # wall-clock (start, end) of every step, to pick the clock samples of the timed ones
     orig_step = ref_train.train_step
 
     def timed_step(step, *a, **kw):
@@ -154,10 +156,12 @@ def run_reference(args) -> dict:
             return out
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = datetime.datetime.now()
         e0.record()
         out = orig_step(step, *a, **kw)
         e1.record()
         torch.cuda.synchronize()
+        stamps.append((t0, datetime.datetime.now()))
         step_ms.append(e0.elapsed_time(e1))
         losses.append(out[0].loss)
         return out
@@ -190,7 +194,8 @@ def run_reference(args) -> dict:
         return _unavailable(f"reference run failed: {type(e).__name__}: {e}"[:300]) if rank == 0 else {}
     finally:
         dist.destroy_process_group = orig_destroy
-    clocks = sampler.stop() if (sampler is not None and rank == 0) else None
+    windows = [(stamps[W][0], stamps[W + K - 1][1])] if len(stamps) >= W + K else []
+    clocks = sampler.stop(windows) if (sampler is not None and rank == 0) else None
     if rank != 0 or "ms" not in result or len(step_ms) < W + K:
         return {}
     ms = result["ms"]
