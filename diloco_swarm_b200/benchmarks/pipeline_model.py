@@ -20,15 +20,16 @@ from __future__ import annotations
 import argparse
 import json
 import statistics
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 from ..parallel import schedule as S
 
 
 def step_time(plans: Dict[int, List[S.Op]], num_stages: int, fwd: Sequence[float], bwd: Sequence[float],
-              xfer: float) -> Dict[str, float]:
+              xfer: float, speed: Optional[Sequence[float]] = None) -> Dict[str, float]:
     """Replay one step.  ``fwd[s]`` / ``bwd[s]``: time of one microbatch's forward / backward on stage
-    ``s``; ``xfer``: time for an activation or gradient tile to reach the neighbouring stage.
+    ``s``; ``xfer``: time for an activation or gradient tile to reach the neighbouring stage;
+    ``speed[r]``: relative speed of rank ``r`` (its durations are divided by it).
     Returns the makespan and the busy time of every rank."""
     world = len(plans)
     pos = {r: 0 for r in plans}
@@ -54,6 +55,8 @@ def step_time(plans: Dict[int, List[S.Op]], num_stages: int, fwd: Sequence[float
                         break
                     ready = arrived[key]
                 dur = fwd[st] if op.kind == S.FWD else bwd[st] if op.kind == S.BWD else fwd[st] + bwd[st]
+                if speed is not None:
+                    dur /= speed[r]
                 start = max(free[r], ready)
                 free[r] = start + dur
                 busy[r] += dur
@@ -70,15 +73,20 @@ def step_time(plans: Dict[int, List[S.Op]], num_stages: int, fwd: Sequence[float
 
 def simulate(stages: int, replicas: int, micro_batches: int, cap: int, fwd: Sequence[float], bwd: Sequence[float],
              xfer: float = 0.0, routing: str = "uniform", steps: int = 100, seed: int = 0,
-             tail_ms: float = 0.0) -> Dict[str, float]:
+             tail_ms: float = 0.0, speed: Optional[Sequence[float]] = None,
+             weights: Optional[Sequence[float]] = None) -> Dict[str, float]:
     """Step-time statistics over ``steps`` seeded routings.  ``tail_ms`` is added to every step
-    (optimiser, gradient or outer synchronisation, metrics)."""
+    (optimiser, gradient or outer synchronisation, metrics).  ``speed``: relative speed per rank
+    (heterogeneous replicas); ``weights``: routing weights per rank for ``routing = "weighted"``
+    (default: the speeds)."""
+    if routing == "weighted" and weights is None:
+        weights = speed
     world = stages * replicas
     times, peak_util, mean_util, worst_share = [], [], [], []
     for step in range(1, steps + 1):
-        path = S.route(seed, step, stages, world, micro_batches, mode=routing)
+        path = S.route(seed, step, stages, world, micro_batches, mode=routing, weights=weights)
         plans = {r: S.plan(path, world, r, cap) for r in range(world)}
-        out = step_time(plans, stages, fwd, bwd, xfer)
+        out = step_time(plans, stages, fwd, bwd, xfer, speed)
         t = out["makespan"] + tail_ms
         times.append(t)
         busy = list(out["busy"].values())
@@ -112,12 +120,17 @@ def main():
     ap.add_argument("--xfer-ms", type=float, default=0.07, help="activation / gradient transfer time between stages")
     ap.add_argument("--tail-ms", type=float, default=2.0, help="per-step work after the pipeline (optimiser, syncs)")
     ap.add_argument("--routing", default="uniform", choices=list(S.ROUTING_MODES))
+    ap.add_argument("--speed", default="", help="relative speed per rank, comma separated (default: all 1)")
+    ap.add_argument("--weights", default="", help="routing weights per rank for --routing weighted (default: the speeds)")
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--tokens-per-micro-batch", type=int, default=16 * 1024)
     a = ap.parse_args()
+    world = a.stages * a.replicas
+    speed = _floats(a.speed, world) if a.speed else None
+    weights = _floats(a.weights, world) if a.weights else None
     out = simulate(a.stages, a.replicas, a.micro_batches, a.cap, _floats(a.fwd_ms, a.stages), _floats(a.bwd_ms, a.stages),
-                   a.xfer_ms, a.routing, a.steps, a.seed, a.tail_ms)
+                   a.xfer_ms, a.routing, a.steps, a.seed, a.tail_ms, speed, weights)
     out["tokens_per_s_at_mean_step"] = a.micro_batches * a.tokens_per_micro_batch / (out["step_ms_mean"] / 1e3)
     out["config"] = {k: v for k, v in vars(a).items()}
     print(json.dumps(out, indent=1))

@@ -38,7 +38,16 @@ class SwarmConfig(BaseConfig):
     routing_seed: Optional[int] = None
     # (added) "uniform" = independent uniform draw per hop (reference, src/comm.py:91);
     # "balanced" = seeded random permutation with equal shares per replica.
-    routing: Literal["uniform", "balanced"] = "uniform"
+    routing: Literal["uniform", "balanced", "weighted"] = "uniform"
+    # (added) one relative throughput per rank for routing = "weighted" (empty: all equal)
+    routing_weights: List[float] = []
+
+    @field_validator("routing_weights", mode="before")
+    @classmethod
+    def _split_weights(cls, v):
+        if isinstance(v, str):
+            return [float(x) for x in v.split(",") if x.strip()]
+        return [v] if isinstance(v, (int, float)) else v
     # (added) "even" = reference split (n_layer // S, remainder to the first
     # stages); "balanced" = weigh embedding / LM head when splitting blocks;
     # or an explicit comma list such as "7,5".

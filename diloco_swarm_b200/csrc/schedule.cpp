@@ -121,6 +121,42 @@ int dsw_route(uint64_t seed, uint64_t step, int S, int world, int M,
   return 0;
 }
 
+// Throughput-weighted wiring (the SWARM paper's rule; the reference draws uniformly): the first stage keeps
+// its round-robin chunks, every later hop lands on live replica r of the next stage with probability
+// weights[r] / sum of the live weights of that stage.  Non-positive weights count as zero; a stage whose
+// live weights are all zero falls back to a uniform draw.  Returns 0, or -1 if a stage has no live replica.
+int dsw_route_weighted(uint64_t seed, uint64_t step, int S, int world, int M, const uint8_t* alive,
+                       const double* weights, int32_t* path) {
+  std::vector<std::vector<int>> live(S);
+  for (int r = 0; r < world; ++r)
+    if (!alive || alive[r]) live[r % S].push_back(r);
+  for (int s = 0; s < S; ++s)
+    if (live[s].empty()) return -1;
+  std::vector<std::vector<double>> cum(S);
+  for (int s = 1; s < S; ++s) {
+    double acc = 0.0;
+    for (int r : live[s]) {
+      acc += weights && weights[r] > 0.0 ? weights[r] : 0.0;
+      cum[s].push_back(acc);
+    }
+  }
+  for (int mb = 0; mb < M; ++mb) {
+    path[mb * S + 0] = live[0][mb % int(live[0].size())];
+    for (int s = 1; s < S; ++s) {
+      const uint32_t u = Philox::draw(seed ^ 0x27d4eb2fu, step, uint32_t(mb), uint32_t(s - 1));
+      const double total = cum[s].back();
+      if (total <= 0.0) {
+        path[mb * S + s] = live[s][u % uint32_t(live[s].size())];
+        continue;
+      }
+      const double x = (double(u) + 0.5) / 4294967296.0 * total;
+      const size_t k = size_t(std::upper_bound(cum[s].begin(), cum[s].end(), x) - cum[s].begin());
+      path[mb * S + s] = live[s][std::min(k, live[s].size() - 1)];
+    }
+  }
+  return 0;
+}
+
 // Op record: {kind, mb, prev_rank, next_rank}; kind 0 = forward, 1 = backward,
 // 2 = forward immediately followed by backward (last stage).
 // forward_only = 1 gives the evaluation plan (src/train.py:76-141).

@@ -26,6 +26,9 @@ def _host():
         lib.dsw_route.restype = ctypes.c_int
         lib.dsw_route.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
                                   ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.dsw_route_weighted.restype = ctypes.c_int
+        lib.dsw_route_weighted.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.dsw_plan.restype = ctypes.c_int
         lib.dsw_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
@@ -42,22 +45,37 @@ class Op:
     next: int        # rank that serves it one stage later, or -1
 
 
-ROUTING_MODES = {"uniform": 0, "balanced": 1}
+ROUTING_MODES = {"uniform": 0, "balanced": 1, "weighted": 2}
 
 
 def route(seed: int, step: int, num_stages: int, world_size: int, num_micro_batches: int,
-          alive: Optional[Sequence[bool]] = None, mode: str = "uniform") -> np.ndarray:
+          alive: Optional[Sequence[bool]] = None, mode: str = "uniform",
+          weights: Optional[Sequence[float]] = None) -> np.ndarray:
     """``path[mb, s]`` = rank serving microbatch ``mb`` at stage ``s``.
 
     ``uniform``: every hop is an independent uniform draw, as the reference's
     ``random.choice``.  ``balanced``: a seeded random permutation of an evenly
     filled assignment per stage; the replica of any one microbatch is still
-    uniform, but replicas serve equal shares, so no replica is the straggler."""
+    uniform, but replicas serve equal shares, so no replica is the straggler.
+    ``weighted``: a hop lands on a replica with probability proportional to its
+    entry in ``weights`` (one per rank, e.g. relative throughput), the SWARM
+    paper's wiring rule; without weights it is the uniform draw."""
     path = np.empty((num_micro_batches, num_stages), dtype=np.int32)
     a = None
     if alive is not None:
         a = np.ascontiguousarray(np.asarray(alive, dtype=np.uint8))
         assert a.shape == (world_size,)
+    if mode == "weighted":
+        wv = None
+        if weights is not None and len(weights) > 0:
+            wv = np.ascontiguousarray(np.asarray(weights, dtype=np.float64))
+            assert wv.shape == (world_size,), "routing weights: one per rank"
+        rc = _host().dsw_route_weighted(seed & (2**64 - 1), step, num_stages, world_size, num_micro_batches,
+                                        a.ctypes.data if a is not None else None,
+                                        wv.ctypes.data if wv is not None else None, path.ctypes.data)
+        if rc != 0:
+            raise RuntimeError("routing failed: a stage has no live replica")
+        return path
     rc = _host().dsw_route(seed & (2**64 - 1), step, num_stages, world_size, num_micro_batches,
                            a.ctypes.data if a is not None else None, ROUTING_MODES[mode], path.ctypes.data)
     if rc != 0:

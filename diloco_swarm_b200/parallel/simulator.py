@@ -96,7 +96,8 @@ class VirtualSwarm:
     # ------------------------------------------------------------------
     def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Dict[str, object]:
         cfg, S, W = self.config, self.config.swarm.num_stages, self.world_size
-        path = schedule.route(self.seed, step, S, W, self.num_micro, mode=cfg.swarm.routing)
+        path = schedule.route(self.seed, step, S, W, self.num_micro, mode=cfg.swarm.routing,
+                              weights=cfg.swarm.routing_weights)
         for e in self.engines:
             e.train()
             e.zero_grad()

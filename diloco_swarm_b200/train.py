@@ -129,7 +129,8 @@ class Trainer:
         w = self.world
         # phase separates the routing streams of train / eval / test steps
         path = schedule.route(self.routing_seed + 7919 * phase, step, w.num_stages, w.world_size,
-                              self.num_micro, self.alive, mode=self.config.swarm.routing)
+                              self.num_micro, self.alive, mode=self.config.swarm.routing,
+                              weights=self.config.swarm.routing_weights)
         cap = self.config.train.max_micro_batches
         return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
 

@@ -249,3 +249,8 @@ def test_pipeline_timing_model():
     bal = simulate(2, 4, 32, 8, [1.0, 1.0], [2.0, 2.0], routing="balanced", steps=60)
     assert bal["step_ms_mean"] < uni["step_ms_mean"]
     assert abs(bal["busiest_last_stage_replica_vs_even_share"] - 1.0) < 1e-9 < uni["busiest_last_stage_replica_vs_even_share"] - 1.0
+    # one last-stage replica at half speed: routing by throughput beats both
+    speed = [1, 1, 1, 1, 1, 1, 1, 0.5]
+    het = {m: simulate(2, 4, 32, 8, [1.0, 1.0], [2.0, 2.0], routing=m, steps=60, speed=speed)["step_ms_mean"]
+           for m in ("uniform", "balanced", "weighted")}
+    assert het["weighted"] < 0.9 * min(het["uniform"], het["balanced"])

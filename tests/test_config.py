@@ -49,3 +49,11 @@ def test_presets_exist():
                     "xl": (48, 25, 1600)}.items():
         t = parse_argv(["--model", f"@{ROOT}/configs/model/gpt2-{m}.toml"])["model"]
         assert (t["n_layer"], t["n_head"], t["n_embd"]) == dims
+
+
+def test_added_list_and_flag_fields_parse_from_the_command_line(monkeypatch):
+    monkeypatch.chdir(ROOT)
+    cfg = config_from_argv(BASE + ["--swarm.routing", "weighted", "--swarm.routing_weights", "1,1,2.5,0",
+                                   "--train.deterministic", "true", "--elastic.enable", "true", "--elastic.die_rank", "3"])
+    assert cfg.swarm.routing == "weighted" and cfg.swarm.routing_weights == [1.0, 1.0, 2.5, 0.0]
+    assert cfg.train.deterministic is True and cfg.elastic.die_rank == 3 and cfg.elastic.die_at_step == -1

@@ -161,3 +161,28 @@ def test_random_worlds_masks_and_modes_never_deadlock():
         assert _simulate(plans, world)
 
     check()
+
+
+def test_weighted_routing_follows_the_weights():
+    """Hops land on a replica in proportion to its weight; dead or zero-weight replicas get nothing; the
+    first stage keeps its round-robin chunks; without weights the mode draws uniformly."""
+    stages, world, M = 2, 8, 64
+    w = [1, 1, 1, 1, 1, 3, 1, 0]                      # stage-1 replicas are ranks 1, 3, 5, 7
+    hits = collections.Counter()
+    for step in range(200):
+        p = S.route(3, step, stages, world, M, mode="weighted", weights=w)
+        assert p[:, 0].tolist() == [2 * (i % 4) for i in range(M)]
+        hits.update(p[:, 1].tolist())
+    total = sum(hits.values())
+    assert hits[7] == 0 and set(hits) == {1, 3, 5}
+    assert abs(hits[5] / total - 0.6) < 0.02 and abs(hits[1] / total - 0.2) < 0.02
+    alive = [True] * world
+    alive[5] = False
+    p = S.route(3, 1, stages, world, M, alive, mode="weighted", weights=w)
+    assert set(p[:, 1].tolist()) <= {1, 3}
+    flat = collections.Counter()
+    for step in range(200):
+        flat.update(S.route(3, step, stages, world, M, mode="weighted")[:, 1].tolist())
+    assert max(flat.values()) / min(flat.values()) < 1.15
+    assert (S.route(3, 7, stages, world, M, mode="weighted", weights=w) ==
+            S.route(3, 7, stages, world, M, mode="weighted", weights=w)).all()
