@@ -1,9 +1,13 @@
-"""Console / file / optional wandb logging per rank.
+"""Per-rank logging to files, console and (optionally) wandb.
 
-Directory layout as in the reference (src/logger.py:31-47,90-93):
-``<log_dir>/<run_id>/{<local_rank>.log, master.log, checkpoints/, samples/<step>.txt}``.
-Only the master writes the samples file (in the reference every rank writes
-the same file concurrently).
+What a user of the reference finds unchanged (src/logger.py:31-47,60-93): the run directory
+``<log_dir>/<run_id>/`` with one ``<local_rank>.log`` per rank, ``master.log`` written by the master
+rank, ``checkpoints/`` and ``samples/<step>.txt``; the ``Level`` enum; the five ``log_*`` calls and the
+text they produce.  What differs: messages go through a small table of channels instead of four
+hand-wired loggers, logger names carry the run id and the global rank (two runs in one process, as in
+the tests, do not share handlers), only the master writes the samples file (in the reference every
+rank writes the same file at once), wandb failures on an offline box do not stop the run, and
+``close()`` releases the files.
 """
 from __future__ import annotations
 
@@ -15,6 +19,9 @@ from typing import Any, Dict, List, Optional
 
 import yaml
 
+FILE_FORMAT = "[%(asctime)s][%(levelname)s][{tag}] %(message)s"
+CONSOLE_FORMAT = "[%(levelname)s][{tag}] %(message)s"
+
 
 class Level(Enum):
     DEBUG = logging.DEBUG
@@ -23,51 +30,61 @@ class Level(Enum):
     ERROR = logging.ERROR
 
 
+class _Channel:
+    """One destination: a python logger that owns exactly one handler."""
+
+    def __init__(self, key: str, handler: logging.Handler, fmt: str, tag: str, threshold: str):
+        handler.setFormatter(logging.Formatter(fmt.format(tag=tag)))
+        self.log = logging.getLogger(key)
+        self.log.propagate = False
+        self.log.setLevel(threshold)
+        self.log.addHandler(handler)
+        self.handler = handler
+
+    def emit(self, level: Level, text: str) -> None:
+        self.log.log(level.value, text)
+
+    def close(self) -> None:
+        self.handler.flush()
+        self.handler.close()
+        self.log.removeHandler(self.handler)
+
+
 class Logger:
     def __init__(self, world, config):
         self.world, self.config = world, config
-        self.name = f"rank{world.local_rank}"
-        self.run_id = config.run_id or datetime.now().strftime("%Y%m%d_%H%M%S")
         self.is_master = world.is_master
-        self.wandb_run = None
-        self.log_dir = os.path.join(config.log_dir, self.run_id)
-        self.checkpoint_dir = os.path.join(self.log_dir, "checkpoints")
-        self.samples_dir = os.path.join(self.log_dir, "samples")
-        for d in (self.log_dir, self.checkpoint_dir, self.samples_dir):
-            os.makedirs(d, exist_ok=True)
-        uid = f"{self.run_id}-{world.rank}"
-        self.file_logger = self._file_logger(f"file-{uid}", str(world.local_rank), config.file.log_level)
-        self.console_logger = self._console_logger(f"console-{uid}", str(world.local_rank), config.console.log_level)
-        self.master_file_logger = self.master_console_logger = None
-        if self.is_master:
-            self.master_file_logger = self._file_logger(f"master-file-{uid}", "master", config.file.log_level)
-            self.master_console_logger = self._console_logger(f"master-console-{uid}", "*", config.console.log_level)
-        if config.wandb.enable:
-            try:
-                import wandb
-                self.wandb_run = wandb.init(name=self.name, project=config.wandb.project,
-                                            entity=config.wandb.entity, tags=config.wandb.tags,
-                                            group=config.wandb.group or self.run_id, dir=self.log_dir)
-            except Exception as e:  # offline boxes: keep training
-                self.log_message(f"wandb disabled: {e}", master=False, level=Level.WARNING)
+        self.name = f"rank{world.local_rank}"
+        self.run_id = config.run_id if config.run_id is not None else datetime.now().strftime("%Y%m%d_%H%M%S")
+        root = os.path.join(config.log_dir, self.run_id)
+        self.log_dir, self.checkpoint_dir, self.samples_dir = root, os.path.join(root, "checkpoints"), os.path.join(root, "samples")
+        for path in (self.log_dir, self.checkpoint_dir, self.samples_dir):
+            os.makedirs(path, exist_ok=True)
 
+        # channel table: "own" = this rank's file (sees every message), "local" = what a non-master
+        # message also reaches, "master" = what a master message also reaches (empty on other ranks)
+        uid, tag = f"{self.run_id}.{world.rank}", str(world.local_rank)
+        own = self._file(f"dsw.file.{uid}", tag)
+        self._channels: Dict[str, List[_Channel]] = {
+            "own": [own],
+            "local": [self._console(f"dsw.console.{uid}", tag)],
+            "master": ([self._console(f"dsw.console.master.{uid}", "*"), self._file(f"dsw.file.master.{uid}", "master")]
+                       if self.is_master else []),
+        }
+        self.wandb_run = self._start_wandb() if config.wandb.enable else None
+
+    # ------------------------------------------------------------------ messages
     def log_message(self, message: Any, master: bool, level: Level = Level.INFO) -> None:
-        message = str(message)
-        self.file_logger.log(level.value, message)
-        if master:
-            if self.master_console_logger:
-                self.master_console_logger.log(level.value, message)
-            if self.master_file_logger:
-                self.master_file_logger.log(level.value, message)
-        else:
-            self.console_logger.log(level.value, message)
+        text = str(message)
+        for ch in self._channels["own"] + self._channels["master" if master else "local"]:
+            ch.emit(level, text)
 
     def log_config(self, config) -> None:
-        d = config.model_dump()
-        text = "Setting configuration:\n\t" + yaml.dump(d, sort_keys=False).replace("\n", "\n\t").strip()
-        self.log_message(text, master=True, level=Level.INFO)
+        as_dict = config.model_dump()
+        body = yaml.dump(as_dict, sort_keys=False).strip().replace("\n", "\n\t")
+        self.log_message("Setting configuration:\n\t" + body, master=True, level=Level.INFO)
         if self.wandb_run:
-            self.wandb_run.config.update(d)
+            self.wandb_run.config.update(as_dict)
 
     def log_world(self, world) -> None:
         self.log_message(world, master=False, level=Level.INFO)
@@ -75,43 +92,42 @@ class Logger:
             self.wandb_run.config.update({"world": dict(world)})
 
     def log_metrics(self, metrics: Dict[str, float], step: Optional[int] = None, master: bool = True) -> None:
-        self.log_message(f"{'Global' if master else 'Local'} metrics: {metrics}", master=master, level=Level.DEBUG)
-        if self.wandb_run and (not master or self.is_master):
+        scope = "Global" if master else "Local"
+        self.log_message(f"{scope} metrics: {metrics}", master=master, level=Level.DEBUG)
+        # local metrics go to every rank's wandb run, global ones to the master's only
+        if self.wandb_run and (self.is_master or not master):
             self.wandb_run.log(metrics, step=step)
 
     def log_samples(self, samples: List[str], step: int) -> None:
-        for i, s in enumerate(samples):
-            self.log_message(f"Sample {i + 1}: {s}", master=True, level=Level.INFO)
+        for number, text in enumerate(samples, start=1):
+            self.log_message(f"Sample {number}: {text}", master=True, level=Level.INFO)
         if self.is_master:
             with open(os.path.join(self.samples_dir, f"{step}.txt"), "w") as f:
-                for s in samples:
-                    f.write(s + "\n")
+                f.writelines(text + "\n" for text in samples)
 
     def close(self) -> None:
-        for lg in (self.file_logger, self.console_logger, self.master_file_logger, self.master_console_logger):
-            if lg is None:
-                continue
-            for h in list(lg.handlers):
-                h.flush()
-                h.close()
-                lg.removeHandler(h)
+        for group in self._channels.values():
+            for ch in group:
+                ch.close()
+        self._channels = {"own": [], "local": [], "master": []}
         if self.wandb_run:
             self.wandb_run.finish()
+            self.wandb_run = None
 
-    def _file_logger(self, name: str, short: str, level: str) -> logging.Logger:
-        lg = logging.getLogger(name)
-        lg.setLevel(level)
-        lg.propagate = False
-        h = logging.FileHandler(os.path.join(self.log_dir, f"{short}.log"))
-        h.setFormatter(logging.Formatter(f"[%(asctime)s][%(levelname)s][{short}] %(message)s"))
-        lg.addHandler(h)
-        return lg
+    # ------------------------------------------------------------------ construction
+    def _file(self, key: str, tag: str) -> _Channel:
+        handler = logging.FileHandler(os.path.join(self.log_dir, f"{tag}.log"))
+        return _Channel(key, handler, FILE_FORMAT, tag, self.config.file.log_level)
 
-    def _console_logger(self, name: str, short: str, level: str) -> logging.Logger:
-        lg = logging.getLogger(name)
-        lg.setLevel(level)
-        lg.propagate = False
-        h = logging.StreamHandler()
-        h.setFormatter(logging.Formatter(f"[%(levelname)s][{short}] %(message)s"))
-        lg.addHandler(h)
-        return lg
+    def _console(self, key: str, tag: str) -> _Channel:
+        return _Channel(key, logging.StreamHandler(), CONSOLE_FORMAT, tag, self.config.console.log_level)
+
+    def _start_wandb(self):
+        cfg = self.config.wandb
+        try:
+            import wandb
+            return wandb.init(name=self.name, project=cfg.project, entity=cfg.entity, tags=cfg.tags,
+                              group=cfg.group or self.run_id, dir=self.log_dir)
+        except Exception as e:          # no network, not logged in: training goes on without it
+            self.log_message(f"wandb disabled: {e}", master=False, level=Level.WARNING)
+            return None
