@@ -71,6 +71,7 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--variant", default="nt", choices=["nt", "nn", "tn"])
     ap.add_argument("--split", type=int, default=1)
+    ap.add_argument("--library", action="store_true", help="gemm: time torch.matmul instead of the tcgen05 kernel")
     ap.add_argument("--n", type=int, default=81_000_000)
     ap.add_argument("--R", type=int, default=4)
     ap.add_argument("--bf16-wire", action="store_true")
@@ -83,19 +84,22 @@ def main():
     out = {"case": a.case, "peaks": pk["source"]}
     if a.case == "gemm":
         M, N, Kd = a.M, a.N, a.K
+        # --library times torch.matmul (cuBLAS) on the same operands: the comparison column of the profiles
         if a.variant == "nt":
             x, w = bf(M, Kd), bf(N, Kd)
-            fn = lambda: K.gemm(x, w, bn=a.bn)
+            fn = (lambda: x @ w.t()) if a.library else (lambda: K.gemm(x, w, bn=a.bn))
         elif a.variant == "nn":
             x, w = bf(M, Kd), bf(Kd, N)
-            fn = lambda: K.gemm(x, w, b_t=False, bn=a.bn)
+            fn = (lambda: x @ w) if a.library else (lambda: K.gemm(x, w, b_t=False, bn=a.bn))
         else:
             x, w = bf(Kd, M), bf(Kd, N)
             acc = torch.zeros(M, N, device="cuda")
-            fn = lambda: K.gemm(x, w, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=acc, split_k=a.split, bn=a.bn)
+            fn = (lambda: x.t() @ w) if a.library else (
+                lambda: K.gemm(x, w, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=acc, split_k=a.split, bn=a.bn))
         ms = timeit(fn, a.warmup, a.iters, flush)
         tf = 2.0 * M * N * Kd / ms / 1e9
-        out.update(shape=[M, N, Kd], variant=a.variant, bn=a.bn, ms=ms, tflops=tf, frac_of_peak=tf / pk["bf16_tflops"])
+        out.update(shape=[M, N, Kd], variant=a.variant, bn=a.bn, library=bool(a.library), ms=ms, tflops=tf,
+                   frac_of_peak=tf / pk["bf16_tflops"])
     elif a.case in ("layernorm_fwd", "layernorm_bwd"):
         M, d = a.M, a.K
         x, g, b = bf(M, d, scale=1.0), torch.randn(d, device="cuda"), torch.randn(d, device="cuda")
