@@ -101,6 +101,18 @@ class Membership:
                     alive[r] = False
         self.alive = alive
         self.store.set(f"alive/{step}", "".join("1" if a else "0" for a in alive))
+        self._forget(step - 3)
+
+    def _forget(self, step: int) -> None:
+        """Drop the keys of a step that every rank has long left, so a long run does not grow the store."""
+        if step < 1:
+            return
+        for key in [f"alive/{step}", f"verdict/{step}"] + [f"{kind}/{step}/{r}" for kind in ("done", "ok")
+                                                            for r in range(self.world_size)]:
+            try:
+                self.store.delete_key(key)
+            except Exception:          # a key that was never written
+                pass
 
     def barrier(self, name: str) -> None:
         """Barrier over the ranks currently alive (the process-group barrier would wait for the dead)."""
