@@ -12,7 +12,7 @@ world never agree.
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -60,11 +60,21 @@ class VirtualSwarm:
         self.opt_steps = 0
         self.num_train_steps = 0
         self.master = self.worlds[0].last_stage_leader
+        self.alive: List[bool] = [True] * world_size
 
     # ------------------------------------------------------------------
     def _stage_groups(self) -> List[List[int]]:
         w = self.worlds[0]
-        return [w.stage2ranks[s] for s in range(w.num_stages)]
+        return [[r for r in w.stage2ranks[s] if self.alive[r]] for s in range(w.num_stages)]
+
+    def set_alive(self, alive: Sequence[bool]) -> None:
+        """Ranks that take part from now on (the trainer's membership mask): routing draws from them,
+        the stage groups shrink to them, the microbatch share per last-stage replica follows."""
+        self.alive = list(alive)
+        last = self._stage_groups()[-1]
+        self.micro_per_device = max(1, self.num_micro // len(last))
+        self.loss_scale = 1.0 / self.micro_per_device
+        self.master = last[0]
 
     def _sync_gradients(self) -> None:
         for ranks in self._stage_groups():
@@ -94,9 +104,13 @@ class VirtualSwarm:
                         pi.data.copy_(po.data)
 
     # ------------------------------------------------------------------
-    def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Dict[str, object]:
+    def train_step(self, step: int, batch: Dict[str, torch.Tensor], dropped: bool = False) -> Dict[str, object]:
+        """One step of every live rank.  ``dropped``: the step is abandoned as the trainer abandons a step
+        that not every rank got through (no gradient is applied, the optimiser does not advance)."""
         cfg, S, W = self.config, self.config.swarm.num_stages, self.world_size
-        path = schedule.route(self.seed, step, S, W, self.num_micro, mode=cfg.swarm.routing,
+        if dropped:
+            return {"local": None, "global": None, "do_sync": False}
+        path = schedule.route(self.seed, step, S, W, self.num_micro, self.alive, mode=cfg.swarm.routing,
                               weights=cfg.swarm.routing_weights)
         for e in self.engines:
             e.train()
@@ -124,13 +138,13 @@ class VirtualSwarm:
         if do_sync and not has_outer:
             self._sync_gradients()
         lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
-        norms = [e.optimizer_step(lr, cfg.train.max_norm) for e in self.engines]
+        norms = [e.optimizer_step(lr, cfg.train.max_norm) if self.alive[r] else 0.0 for r, e in enumerate(self.engines)]
         self.opt_steps += 1
         if do_sync and has_outer:
             self._outer_step()
         outs = [Outputs(step=step, time=1.0, loss=loss[r], tokens=count[r] * self.mbs * self.seq,
                         num_micro_batches=count[r], lr=lr, norm=norms[r], micro_step_time=1.0) for r in range(W)]
-        last = self.worlds[0].last_stage_ranks
+        last = self._stage_groups()[-1]
         glob = aggregate_outputs(outs[self.master], [outs[r] for r in last])
         return {"local": outs, "global": glob, "do_sync": do_sync}
 

@@ -205,6 +205,25 @@ def test_rank_dies_silently_and_the_step_is_dropped(victim):
             assert "Step 3 is dropped" in logs[r], r
             assert f"Step 4: ranks [{victim}] are gone" in logs[r], r
     assert "Sample 2:" in open(f"{LOG}/{name}/master.log").read()      # end-of-training sampling among the survivors
+    # the survivors' loss curve is the one a single process gets when it drops step 3 and takes the victim
+    # out of the routing from step 4 on
+    from diloco_swarm_b200.parallel.simulator import VirtualSwarm
+    from diloco_swarm_b200.utils import data as D
+    cfg = make_config(model={"n_layer": 2, "n_head": 4, "n_embd": 128, "vocab_size": 50257, "block_size": 1024},
+                      data={"path": "synthetic:zipf", "seq_length": 32, "num_examples": 400, "vocab_limit": 50257},
+                      train={"micro_batch_size": 4, "batch_size": 16, "max_steps": 6, "max_micro_batches": 2, "seed": 0,
+                             "inner_optimizer": {"type": "AdamW", "lr": 4e-4}}, swarm={"num_stages": 2})
+    train, _ = D.get_dataset(cfg.data, D.ByteTokenizer(), seed=0).train_test_split(cfg.eval.eval_size, seed=0)
+    vs = VirtualSwarm(cfg, 4)
+    vs.num_train_steps = 6
+    want, it = [], iter(D.BatchLoader(train, 16))
+    for step in range(1, 7):
+        if step == 4:
+            vs.set_alive([r != victim for r in range(4)])
+        out = vs.train_step(step, next(it), dropped=(step == 3))
+        if out["global"] is not None:
+            want.append(out["global"].loss)
+    assert max(abs(a - b) for a, b in zip(losses, want)) < 2e-3, (losses, want)
 
 
 def test_tiny_diloco_swarm_2x2_matches_single_process_replay():
