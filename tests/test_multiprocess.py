@@ -171,6 +171,28 @@ def launch_keep(run_id, nproc, stages, extra):
         shutil.rmtree = real_rmtree
 
 
+def replay_with_membership(gone, from_step, dropped_step, steps):
+    """Global losses of a single-process replay (VirtualSwarm) of the launch() configuration in which rank
+    ``gone`` is out of the routing from ``from_step`` on and ``dropped_step`` (or None) is abandoned."""
+    from diloco_swarm_b200.parallel.simulator import VirtualSwarm
+    from diloco_swarm_b200.utils import data as D
+    cfg = make_config(model={"n_layer": 2, "n_head": 4, "n_embd": 128, "vocab_size": 50257, "block_size": 1024},
+                      data={"path": "synthetic:zipf", "seq_length": 32, "num_examples": 400, "vocab_limit": 50257},
+                      train={"micro_batch_size": 4, "batch_size": 16, "max_steps": steps, "max_micro_batches": 2, "seed": 0,
+                             "inner_optimizer": {"type": "AdamW", "lr": 4e-4}}, swarm={"num_stages": 2})
+    train, _ = D.get_dataset(cfg.data, D.ByteTokenizer(), seed=0).train_test_split(cfg.eval.eval_size, seed=0)
+    vs = VirtualSwarm(cfg, 4)
+    vs.num_train_steps = steps
+    out, it = [], iter(D.BatchLoader(train, 16))
+    for step in range(1, steps + 1):
+        if step == from_step:
+            vs.set_alive([r != gone for r in range(4)])
+        res = vs.train_step(step, next(it), dropped=(step == dropped_step))
+        if res["global"] is not None:
+            out.append(res["global"].loss)
+    return out
+
+
 @pytest.mark.parametrize("leaver", [3, 2])
 def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
     """Host-side failure: one replica announces a leave, finishes its step and exits; the others learn
@@ -183,6 +205,8 @@ def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
     text = open(f"{LOG}/{name}/master.log").read() + open(f"{LOG}/{name}/0.log").read()
     assert f"ranks [{leaver}] are gone" in text
     assert f"Rank {leaver} leaves after step 2" in open(f"{LOG}/{name}/{leaver}.log").read()
+    want = replay_with_membership(gone=leaver, from_step=3, dropped_step=None, steps=5)
+    assert max(abs(a - b) for a, b in zip(losses, want)) < 2e-3, (losses, want)
 
 
 @pytest.mark.parametrize("victim", [2])          # a first-stage replica: last-stage replicas wait for its activations
@@ -207,22 +231,7 @@ def test_rank_dies_silently_and_the_step_is_dropped(victim):
     assert "Sample 2:" in open(f"{LOG}/{name}/master.log").read()      # end-of-training sampling among the survivors
     # the survivors' loss curve is the one a single process gets when it drops step 3 and takes the victim
     # out of the routing from step 4 on
-    from diloco_swarm_b200.parallel.simulator import VirtualSwarm
-    from diloco_swarm_b200.utils import data as D
-    cfg = make_config(model={"n_layer": 2, "n_head": 4, "n_embd": 128, "vocab_size": 50257, "block_size": 1024},
-                      data={"path": "synthetic:zipf", "seq_length": 32, "num_examples": 400, "vocab_limit": 50257},
-                      train={"micro_batch_size": 4, "batch_size": 16, "max_steps": 6, "max_micro_batches": 2, "seed": 0,
-                             "inner_optimizer": {"type": "AdamW", "lr": 4e-4}}, swarm={"num_stages": 2})
-    train, _ = D.get_dataset(cfg.data, D.ByteTokenizer(), seed=0).train_test_split(cfg.eval.eval_size, seed=0)
-    vs = VirtualSwarm(cfg, 4)
-    vs.num_train_steps = 6
-    want, it = [], iter(D.BatchLoader(train, 16))
-    for step in range(1, 7):
-        if step == 4:
-            vs.set_alive([r != victim for r in range(4)])
-        out = vs.train_step(step, next(it), dropped=(step == 3))
-        if out["global"] is not None:
-            want.append(out["global"].loss)
+    want = replay_with_membership(gone=victim, from_step=4, dropped_step=3, steps=6)
     assert max(abs(a - b) for a, b in zip(losses, want)) < 2e-3, (losses, want)
 
 
