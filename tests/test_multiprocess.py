@@ -171,7 +171,7 @@ def launch_keep(run_id, nproc, stages, extra):
         shutil.rmtree = real_rmtree
 
 
-def replay_with_membership(gone, from_step, dropped_step, steps):
+def replay_with_membership(gone, from_step, dropped_step, steps, **over):
     """Global losses of a single-process replay (VirtualSwarm) of the launch() configuration in which rank
     ``gone`` is out of the routing from ``from_step`` on and ``dropped_step`` (or None) is abandoned."""
     from diloco_swarm_b200.parallel.simulator import VirtualSwarm
@@ -180,6 +180,10 @@ def replay_with_membership(gone, from_step, dropped_step, steps):
                       data={"path": "synthetic:zipf", "seq_length": 32, "num_examples": 400, "vocab_limit": 50257},
                       train={"micro_batch_size": 4, "batch_size": 16, "max_steps": steps, "max_micro_batches": 2, "seed": 0,
                              "inner_optimizer": {"type": "AdamW", "lr": 4e-4}}, swarm={"num_stages": 2})
+    base = cfg.model_dump()
+    for k, v in over.items():
+        base[k].update(v)
+    cfg = make_config(**base)
     train, _ = D.get_dataset(cfg.data, D.ByteTokenizer(), seed=0).train_test_split(cfg.eval.eval_size, seed=0)
     vs = VirtualSwarm(cfg, 4)
     vs.num_train_steps = steps
@@ -188,7 +192,7 @@ def replay_with_membership(gone, from_step, dropped_step, steps):
         if step == from_step:
             vs.set_alive([r != gone for r in range(4)])
         res = vs.train_step(step, next(it), dropped=(step == dropped_step))
-        if res["global"] is not None:
+        if res["global"] is not None and res["do_sync"]:          # the trainer logs global metrics on sync steps
             out.append(res["global"].loss)
     return out
 
@@ -206,6 +210,21 @@ def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
     assert f"ranks [{leaver}] are gone" in text
     assert f"Rank {leaver} leaves after step 2" in open(f"{LOG}/{name}/{leaver}.log").read()
     want = replay_with_membership(gone=leaver, from_step=3, dropped_step=None, steps=5)
+    assert max(abs(a - b) for a, b in zip(losses, want)) < 2e-3, (losses, want)
+
+
+def test_rank_leaves_under_diloco():
+    """A last-stage replica leaves between two outer steps: the next pseudo-gradient average runs over the
+    replicas that are left, and the losses on the outer steps equal the single-process replay."""
+    outer = {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
+    launch("leave_diloco", 4, 2, ["--elastic.enable", "true", "--elastic.timeout", "20", "--elastic.leave_rank", "3",
+                                  "--elastic.leave_after_step", "3", "--train.max_steps", "6",
+                                  "--train.outer_optimizer.type", "SGD", "--train.outer_optimizer.lr", "0.7",
+                                  "--train.outer_optimizer.nesterov", "true", "--swarm.sync_every_n_steps", "2"])
+    losses = global_losses("leave_diloco")
+    want = replay_with_membership(gone=3, from_step=4, dropped_step=None, steps=6,
+                                  train={"outer_optimizer": outer}, swarm={"sync_every_n_steps": 2})
+    assert len(losses) == len(want) == 3          # global metrics exist on the outer steps 2, 4, 6
     assert max(abs(a - b) for a, b in zip(losses, want)) < 2e-3, (losses, want)
 
 
