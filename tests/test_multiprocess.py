@@ -197,7 +197,7 @@ def replay_with_membership(gone, from_step, dropped_step, steps, **over):
     return out
 
 
-@pytest.mark.parametrize("leaver", [3, 2])
+@pytest.mark.parametrize("leaver", [2])          # a first-stage replica; the DiLoCo test below takes a last-stage one
 def test_rank_leaves_between_steps_and_the_swarm_reroutes(leaver):
     """Host-side failure: one replica announces a leave, finishes its step and exits; the others learn
     of it from the store before their next step, route around it and keep training."""
