@@ -4,8 +4,8 @@
 //
 // Who needs it: code that runs where cudaMalloc (or any allocating library
 // call, torch's caching allocator included) is off limits.  Examples are a
-// plugin that is called inside someone else's CUDA-graph capture or inside a
-// framework that has handed all device memory to its own pool, a real-time
+// plugin that runs inside a framework that has handed all device memory to
+// its own pool, a real-time
 // loop that may not take the allocator's locks, and a process that is close
 // to the memory limit of a shared GPU and cannot risk an out-of-memory error
 // in the middle of a step.  dsw_layernorm_bwd needs a scratch array for its

@@ -1,7 +1,7 @@
 """The allocation-free LayerNorm backward against the normal entry point.
 
 Some callers of this library cannot allocate device memory: code running inside
-another framework's memory pool or graph capture, latency-critical loops that
+another framework's memory pool, latency-critical loops that
 must stay off the allocator, processes at the edge of a shared GPU's memory.
 ``dsw_layernorm_bwd_noalloc`` serves them with a scratch array built into the
 library.  The test calls it through its exported C symbol (ctypes, no wrapper),
