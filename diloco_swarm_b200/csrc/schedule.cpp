@@ -23,6 +23,7 @@
 #include <vector>
 #include <algorithm>
 #include <limits>
+#include "dswarm_host.h"
 
 namespace {
 

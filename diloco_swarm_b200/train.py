@@ -61,10 +61,7 @@ def get_logger(world: World, logging_config) -> Logger:
 
 
 def make_engine(config: Config, world: World, device: torch.device):
-    mc = config.model
-    gcfg = GPT2Config(block_size=mc.block_size, vocab_size=mc.vocab_size, n_layer=mc.n_layer,
-                      n_head=mc.n_head, n_embd=mc.n_embd, dropout=mc.dropout, bias=mc.bias,
-                      parameter_sharing=mc.parameter_sharing)
+    gcfg = _gpt2_config(config.model)
     kind = config.engine
     if kind == "auto":
         kind = "b200" if device.type == "cuda" else "torch"
