@@ -7,10 +7,14 @@ text they produce.  What differs: messages go through a small table of channels 
 hand-wired loggers, logger names carry the run id and the global rank (two runs in one process, as in
 the tests, do not share handlers), only the master writes the samples file (in the reference every
 rank writes the same file at once), wandb failures on an offline box do not stop the run, and
-``close()`` releases the files.
+``close()`` releases the files.  Added for boxes without wandb: every ``log_metrics`` call also appends
+one JSON line to ``metrics/<local_rank>.jsonl`` (local metrics) or ``metrics/master.jsonl`` (global and
+evaluation metrics, master only), and the master saves the configuration and the world size as
+``config.yaml``; ``utils/results.py`` builds the reference's result tables from these files.
 """
 from __future__ import annotations
 
+import json
 import logging
 import os
 from datetime import datetime
@@ -58,8 +62,10 @@ class Logger:
         self.run_id = config.run_id if config.run_id is not None else datetime.now().strftime("%Y%m%d_%H%M%S")
         root = os.path.join(config.log_dir, self.run_id)
         self.log_dir, self.checkpoint_dir, self.samples_dir = root, os.path.join(root, "checkpoints"), os.path.join(root, "samples")
-        for path in (self.log_dir, self.checkpoint_dir, self.samples_dir):
+        self.metrics_dir = os.path.join(root, "metrics")
+        for path in (self.log_dir, self.checkpoint_dir, self.samples_dir, self.metrics_dir):
             os.makedirs(path, exist_ok=True)
+        self._history: Dict[str, Any] = {}          # open metric files by name
 
         # channel table: "own" = this rank's file (sees every message), "local" = what a non-master
         # message also reaches, "master" = what a master message also reaches (empty on other ranks)
@@ -83,6 +89,10 @@ class Logger:
         as_dict = config.model_dump()
         body = yaml.dump(as_dict, sort_keys=False).strip().replace("\n", "\n\t")
         self.log_message("Setting configuration:\n\t" + body, master=True, level=Level.INFO)
+        if self.is_master:
+            with open(os.path.join(self.log_dir, "config.yaml"), "w") as f:
+                yaml.dump({**as_dict, "world": {"world_size": self.world.world_size,
+                                                "num_stages": self.world.num_stages}}, f, sort_keys=False)
         if self.wandb_run:
             self.wandb_run.config.update(as_dict)
 
@@ -94,6 +104,8 @@ class Logger:
     def log_metrics(self, metrics: Dict[str, float], step: Optional[int] = None, master: bool = True) -> None:
         scope = "Global" if master else "Local"
         self.log_message(f"{scope} metrics: {metrics}", master=master, level=Level.DEBUG)
+        if metrics and (self.is_master or not master):
+            self._append_history("master" if master else str(self.world.local_rank), step, metrics)
         # local metrics go to every rank's wandb run, global ones to the master's only
         if self.wandb_run and (self.is_master or not master):
             self.wandb_run.log(metrics, step=step)
@@ -105,7 +117,17 @@ class Logger:
             with open(os.path.join(self.samples_dir, f"{step}.txt"), "w") as f:
                 f.writelines(text + "\n" for text in samples)
 
+    def _append_history(self, name: str, step: Optional[int], metrics: Dict[str, float]) -> None:
+        f = self._history.get(name)
+        if f is None:
+            f = self._history[name] = open(os.path.join(self.metrics_dir, f"{name}.jsonl"), "a")
+        f.write(json.dumps({"_step": step, **metrics}) + "\n")
+        f.flush()
+
     def close(self) -> None:
+        for f in self._history.values():
+            f.close()
+        self._history = {}
         for group in self._channels.values():
             for ch in group:
                 ch.close()
