@@ -7,12 +7,21 @@ package falls back to a byte-level tokenizer and to built-in generators:
 * ``mikasenghaas/memorize`` / ``memorize``: one sentence repeated 1000 times
   (the reference's memorisation set, tests/test_memorize.py:80);
 * ``synthetic:zipf``: token ids iid Zipf(s) over [0, vocab_limit) from a seed.
+
+Local data needs no hub either: ``tokens:<file.npy>`` is a pre-tokenised matrix
+of rows of at least seq_length + 1 ids (memory-mapped, so a multi-gigabyte file
+costs no memory until its rows are batched), ``text:<file.txt>`` is one example
+per non-empty line, tokenised on load.  ``prepare_tokens`` (also the module's
+command line) writes such a matrix from a text file, which is what the
+reference's data notebook does for its hub datasets (notebooks/1.0-data.ipynb:
+pre-tokenised rows of 1025 ids).
 """
 from __future__ import annotations
 
 import os
 from typing import Dict, Iterator, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 MEMORIZE_SENTENCE = "I am a large language model and I can memorize this sentence."
@@ -93,6 +102,10 @@ class TokenDataset:
     def __len__(self) -> int:
         return self.input_ids.size(0)
 
+    def rows(self, lo: int, hi: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """ids and mask of rows [lo, hi) as int64 tensors."""
+        return self.input_ids[lo:hi], self.attention_mask[lo:hi]
+
     def select(self, idx) -> "TokenDataset":
         return TokenDataset(self.input_ids[idx], self.attention_mask[idx])
 
@@ -103,6 +116,48 @@ class TokenDataset:
         g = torch.Generator().manual_seed(seed)
         perm = torch.randperm(n, generator=g) if shuffle else torch.arange(n)
         return self.select(perm[n_test:]), self.select(perm[:n_test])
+
+
+class MappedTokenDataset(TokenDataset):
+    """Rows of a token matrix on disk.  The matrix (any integer dtype, [N, >= width]) stays
+    memory-mapped; ``select`` and the train/validation split only permute an index, and a batch
+    copies just its own rows.  ``mask``: optional matrix of the same shape (1 = real token);
+    without it every token counts."""
+
+    def __init__(self, ids: np.ndarray, width: int, mask: Optional[np.ndarray] = None,
+                 index: Optional[np.ndarray] = None):
+        if ids.ndim != 2 or ids.shape[1] < width:
+            raise ValueError(f"token matrix of shape {ids.shape} cannot give rows of {width} ids")
+        if mask is not None and mask.shape != ids.shape:
+            raise ValueError("the mask matrix must have the shape of the token matrix")
+        self.ids, self.mask, self.width = ids, mask, width
+        self.index = np.arange(ids.shape[0], dtype=np.int64) if index is None else np.asarray(index, dtype=np.int64)
+
+    def __len__(self) -> int:
+        return int(self.index.shape[0])
+
+    def rows(self, lo: int, hi: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        idx = self.index[lo:hi]
+        contiguous = idx.size > 0 and np.all(np.diff(idx) == 1)
+        take = (lambda m: m[idx[0]:idx[-1] + 1, :self.width]) if contiguous else (lambda m: m[np.sort(idx), :self.width])
+        ids = np.asarray(take(self.ids)).astype(np.int64)
+        mask = np.ones_like(ids) if self.mask is None else np.asarray(take(self.mask)).astype(np.int64)
+        if not contiguous and idx.size > 0:           # rows were read in file order; put them in index order
+            back = np.argsort(np.argsort(idx))
+            ids, mask = ids[back], mask[back]
+        return torch.from_numpy(ids), torch.from_numpy(mask)
+
+    @property
+    def input_ids(self) -> torch.Tensor:          # whole dataset in memory: small sets and tests only
+        return self.rows(0, len(self))[0]
+
+    @property
+    def attention_mask(self) -> torch.Tensor:
+        return self.rows(0, len(self))[1]
+
+    def select(self, idx) -> "MappedTokenDataset":
+        idx = idx.numpy() if isinstance(idx, torch.Tensor) else np.asarray(idx, dtype=np.int64)
+        return MappedTokenDataset(self.ids, self.width, self.mask, self.index[idx])
 
 
 def zipf_tokens(num: int, length: int, vocab: int, s: float, seed: int) -> torch.Tensor:
@@ -127,11 +182,65 @@ def get_dataset(cfg, tokenizer, seed: int, split: str = "train") -> TokenDataset
         n = cfg.num_examples or 1000
         t = tokenize(MEMORIZE_SENTENCE, tokenizer, max_length=width)
         ds = TokenDataset(t["input_ids"].repeat(n, 1), t["attention_mask"].repeat(n, 1))
+    elif path.startswith("tokens:"):
+        ds = load_token_file(path[len("tokens:"):], width)
+    elif path.startswith("text:"):
+        ds = _load_text(path[len("text:"):], tokenizer, width)
     else:
         ds = _load_hf(cfg, tokenizer, width, split)
     if cfg.subset_size < 1.0:
         ds = ds.select(torch.arange(int(len(ds) * cfg.subset_size)))
     return ds
+
+
+def load_token_file(path: str, width: int) -> MappedTokenDataset:
+    """``path``: a .npy matrix of token ids; a sibling ``<stem>.mask.npy`` is used as the mask if present."""
+    ids = np.load(path, mmap_mode="r")
+    stem = path[:-4] if path.endswith(".npy") else path
+    mask = np.load(stem + ".mask.npy", mmap_mode="r") if os.path.exists(stem + ".mask.npy") else None
+    return MappedTokenDataset(ids, width, mask)
+
+
+def _read_examples(path: str) -> List[str]:
+    with open(path, encoding="utf-8") as f:
+        return [line.strip() for line in f if line.strip()]
+
+
+def _load_text(path: str, tokenizer, width: int) -> TokenDataset:
+    rows = [tokenize(text, tokenizer, width) for text in _read_examples(path)]
+    if not rows:
+        raise ValueError(f"{path} has no non-empty line")
+    return TokenDataset(torch.cat([r["input_ids"] for r in rows]), torch.cat([r["attention_mask"] for r in rows]))
+
+
+def prepare_tokens(text_path: str, out_path: str, seq_length: int, tokenizer=None, pack: bool = False) -> Tuple[int, int]:
+    """Tokenise a text file (one example per non-empty line) into ``out_path`` (.npy, int32 rows of
+    seq_length + 1 ids) for ``--data.path tokens:<out_path>``.  Default: one row per line, truncated or
+    padded with eos, plus ``<stem>.mask.npy``.  ``pack``: all lines joined by eos and cut into full
+    rows (no padding, no mask file; a trailing partial row is dropped).  Returns (rows, width)."""
+    tokenizer = tokenizer or get_tokenizer()
+    width = seq_length + 1
+    stem = out_path[:-4] if out_path.endswith(".npy") else out_path
+    examples = _read_examples(text_path)
+    if pack:
+        stream: List[int] = []
+        for text in examples:
+            stream.extend(tokenizer.encode(text))
+            stream.append(tokenizer.eos_token_id)
+        n = len(stream) // width
+        ids = np.asarray(stream[:n * width], dtype=np.int32).reshape(n, width)
+        if os.path.exists(stem + ".mask.npy"):
+            os.remove(stem + ".mask.npy")
+    else:
+        rows = [tokenize(text, tokenizer, width) for text in examples]
+        n = len(rows)
+        ids = torch.cat([r["input_ids"] for r in rows]).numpy().astype(np.int32) if rows else np.zeros((0, width), np.int32)
+        np.save(stem + ".mask.npy", torch.cat([r["attention_mask"] for r in rows]).numpy().astype(np.uint8)
+                if rows else np.zeros((0, width), np.uint8))
+    if n == 0:
+        raise ValueError(f"{text_path} gives no row of {width} tokens")
+    np.save(stem + ".npy", ids)
+    return n, width
 
 
 def _load_hf(cfg, tokenizer, width: int, split: str) -> TokenDataset:
@@ -159,7 +268,7 @@ def _load_hf(cfg, tokenizer, width: int, split: str) -> TokenDataset:
 
 def collate(ds: TokenDataset, lo: int, hi: int) -> Dict[str, torch.Tensor]:
     """inputs = ids[:, :-1], targets = ids[:, 1:], mask = mask[:, :-1] (src/utils.py:107-115)."""
-    ids, mask = ds.input_ids[lo:hi], ds.attention_mask[lo:hi]
+    ids, mask = ds.rows(lo, hi)
     return {"input_ids": ids[:, :-1].contiguous(), "target_ids": ids[:, 1:].contiguous(),
             "attention_mask": mask[:, :-1].contiguous()}
 
@@ -267,3 +376,19 @@ def get_train_setup(steps: int, batch_size: int, seq_length: int, micro_batch_si
             "total_tokens": steps * tokens_per_step,
             "avg_token_repetitions": steps * tokens_per_step / max(1, num_examples * seq_length),
             "grad_accumulation_steps": batch_size // micro_batch_size if micro_batch_size > 0 else 1}
+
+
+def _main() -> None:
+    import argparse
+    ap = argparse.ArgumentParser(description="Tokenise a text file into a token matrix for --data.path tokens:<file>")
+    ap.add_argument("--text", required=True, help="text file, one example per non-empty line")
+    ap.add_argument("--out", required=True, help="output .npy file")
+    ap.add_argument("--seq-length", type=int, default=1024)
+    ap.add_argument("--pack", action="store_true", help="join the lines with eos and cut full rows instead of padding")
+    a = ap.parse_args()
+    n, width = prepare_tokens(a.text, a.out, a.seq_length, pack=a.pack)
+    print(f"wrote {n} rows of {width} token ids to {a.out}")
+
+
+if __name__ == "__main__":
+    _main()

@@ -254,3 +254,41 @@ def test_pipeline_timing_model():
     het = {m: simulate(2, 4, 32, 8, [1.0, 1.0], [2.0, 2.0], routing=m, steps=60, speed=speed)["step_ms_mean"]
            for m in ("uniform", "balanced", "weighted")}
     assert het["weighted"] < 0.9 * min(het["uniform"], het["balanced"])
+
+
+def test_local_token_and_text_datasets(tmp_path):
+    """tokens:<file.npy> (memory-mapped, lazy split) and text:<file.txt>, and the tool that makes the former."""
+    import numpy as np
+    from diloco_swarm_b200.config import DataConfig
+    from diloco_swarm_b200.utils import data as D
+    tok = D.ByteTokenizer()
+    lines = ["hello world", "", "a second line that is longer than the row", "x"]
+    text = tmp_path / "t.txt"
+    text.write_text("\n".join(lines) + "\n")
+    n, width = D.prepare_tokens(str(text), str(tmp_path / "a.npy"), 16, tok)
+    assert (n, width) == (3, 17)
+    ds = D.get_dataset(DataConfig(path=f"tokens:{tmp_path / 'a.npy'}", seq_length=16), tok, seed=0)
+    assert isinstance(ds, D.MappedTokenDataset) and len(ds) == 3
+    ids, mask = ds.rows(0, 3)
+    assert ids.dtype == torch.long and mask.sum(1).tolist() == [11, 17, 1]
+    assert tok.decode(ids[0][:11]) == "hello world" and int(ids[2, 1]) == tok.pad_token_id
+    # the same rows from the text file directly
+    ds_t = D.get_dataset(DataConfig(path=f"text:{text}", seq_length=16), tok, seed=0)
+    assert torch.equal(ds_t.input_ids, ids) and torch.equal(ds_t.attention_mask, mask)
+    # split and select permute an index, the matrix stays on disk; rows come back in index order
+    tr, te = ds.train_test_split(0.34, seed=1)
+    assert len(tr) == 2 and len(te) == 1 and sorted(tr.index.tolist() + te.index.tolist()) == [0, 1, 2]
+    assert tr.ids is ds.ids
+    assert torch.equal(tr.rows(0, 2)[0], ids[torch.from_numpy(tr.index)])
+    b = D.collate(tr, 0, 2)
+    assert b["input_ids"].shape == (2, 16) and torch.equal(b["target_ids"][:, :-1], b["input_ids"][:, 1:])
+    # a row narrower than seq_length + 1 is refused
+    with pytest.raises(ValueError):
+        D.load_token_file(str(tmp_path / "a.npy"), 18)
+    # packed: one stream cut into full rows, no padding and no mask file
+    n2, w2 = D.prepare_tokens(str(text), str(tmp_path / "b.npy"), 7, tok, pack=True)
+    stream = sum((list(l.encode()) + [tok.eos_token_id] for l in lines if l), [])
+    assert (n2, w2) == (len(stream) // 8, 8) and not (tmp_path / "b.mask.npy").exists()
+    packed = D.load_token_file(str(tmp_path / "b.npy"), 8)
+    assert packed.rows(0, n2)[0].reshape(-1).tolist() == stream[:n2 * 8] and int(packed.rows(0, 1)[1].min()) == 1
+    assert np.load(tmp_path / "b.npy").dtype == np.int32
