@@ -470,6 +470,12 @@ class B200Engine:
     def outer_state(self) -> Optional[dict]:
         return self.outer.gather_state() if self.outer is not None else None
 
+    def reset_outer(self) -> None:
+        """Global weights := current weights, outer momentum := 0 (after loading weights that come
+        without their DiLoCo state, e.g. a checkpoint moved to another topology)."""
+        if self.outer is not None:
+            self.outer.reset()
+
     def load_outer_state(self, st: Optional[dict]) -> None:
         if st is not None and self.outer is not None:
             self.outer.load_state(st)

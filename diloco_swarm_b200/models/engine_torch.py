@@ -181,6 +181,16 @@ class TorchEngine:
             return None
         return {"params": [p.detach().cpu() for p in self.outer_params], "opt": self.outer_opt.state_dict()}
 
+    def reset_outer(self) -> None:
+        """Global weights := current weights, outer momentum := 0 (after loading weights that come
+        without their DiLoCo state, e.g. a checkpoint moved to another topology)."""
+        if not self.has_outer:
+            return
+        with torch.no_grad():
+            for po, pi in zip(self.outer_params, self.model.parameters()):
+                po.copy_(pi)
+        self.outer_opt.state.clear()
+
     def load_outer_state(self, st: Optional[dict]) -> None:
         if st is None or not self.has_outer:
             return

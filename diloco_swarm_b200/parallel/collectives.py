@@ -70,6 +70,13 @@ class OuterSync:
         dist.all_gather(mo, self.mom, group=self.group)
         return {"theta_g": torch.cat(tg)[:self.n].cpu(), "momentum": torch.cat(mo)[:self.n].cpu()}
 
+    def reset(self) -> None:
+        """This replica's shard of the global weights := the same slice of its current weights; momentum := 0."""
+        k = self.hi - self.lo
+        self.theta_g.zero_()
+        self.theta_g[:k].copy_(self.theta.view(torch.float32, self.n)[self.lo:self.hi])
+        self.mom.zero_()
+
     def load_state(self, st) -> None:
         full_t = torch.zeros(self.shard * self.R)
         full_m = torch.zeros(self.shard * self.R)

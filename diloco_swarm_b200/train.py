@@ -373,7 +373,11 @@ class Trainer:
         if opt is not None:
             self.engine.load_optim_state(opt["engine"])
             self.opt_steps = int(opt["opt_steps"])
-        self.engine.load_outer_state(self.ckpt.load_extra(step, "outer"))
+        outer = self.ckpt.load_extra(step, "outer")
+        if outer is not None:
+            self.engine.load_outer_state(outer)
+        elif self.engine.has_outer:
+            self.engine.reset_outer()       # weights without their DiLoCo state (a resharded checkpoint)
         self.world.barrier()
         return step
 

@@ -161,6 +161,30 @@ def test_checkpoint_and_resume():
     assert max(abs(a - b) for a, b in zip(resumed, full[3:])) < 1e-4, (resumed, full)
 
 
+def test_checkpoint_moves_to_another_topology():
+    """A 2 x 2 swarm's checkpoint, merged and re-cut by utils/ckpt.py, resumes as one process and as a
+    plain 2-stage pipeline: the first step after the move sees the same weights and the same batch, so its loss
+    is the loss the swarm itself reports for that step."""
+    from diloco_swarm_b200.utils import ckpt as C
+    # balanced routing: with the uniform draw a last-stage replica can end a step without a microbatch,
+    # and the logged loss (a mean over the replicas that saw data, as in the reference) is then scaled
+    launch("ckmove", 4, 2, ["--ckpt.enable", "true", "--ckpt.every_n_steps", "3", "--train.max_steps", "4",
+                            "--swarm.routing", "balanced"])
+    want = global_losses("ckmove")[3]
+    src = f"{LOG}/ckmove/checkpoints/step_3"
+    full = C.merge_model(src)
+    assert "transformer.h.1.mlp.c_proj.weight" in full and "lm_head.weight" in full and len(full) == 2 + 2 * 12 + 2 + 1
+    mean = C.merge_model(src, average_replicas=True)          # replicas agree right after a synchronisation
+    assert all(torch.allclose(full[k], mean[k], atol=1e-6) for k in full)
+    for run_id, nproc, stages in (("ckmove1", 1, 1), ("ckmove2", 2, 2)):
+        shutil.rmtree(f"{LOG}/{run_id}", ignore_errors=True)
+        meta = C.reshard(src, f"{LOG}/{run_id}/checkpoints/step_3", stages, nproc // stages)
+        assert meta["world_size"] == nproc and meta["resharded_from"]["world_size"] == 4
+        launch_keep(run_id, nproc, stages, ["--ckpt.resume", "true", "--train.max_steps", "4"])
+        got = global_losses(run_id)
+        assert len(got) == 1 and abs(got[0] - want) < 2e-4, (run_id, got, want)
+
+
 def launch_keep(run_id, nproc, stages, extra):
     """Like launch() but keeps the existing run directory."""
     real_rmtree = shutil.rmtree
