@@ -125,13 +125,19 @@ def test_memorization_on_a_swarm():
            "@configs/optimizer/none.toml", "--train.inner_optimizer.lr", "0.006", "--train.max_steps", "170",
            "--train.batch_size", "4", "--train.micro_batch_size", "1", "--train.max_micro_batches", "2",
            "--sample.max_new_tokens", "64", "--sample.temperature", "0.1", "--sample.num_samples", "2",
-           "--logging.file.log_level", "INFO", "--amp.enable", "false",
+           "--logging.file.log_level", "INFO", "--amp.enable", "false", "--ckpt.enable", "true",
            "--eval.enable", "false", "--logging.log_dir", LOG, "--logging.run_id", "memorize",
            "--logging.console.log_level", "ERROR"]
     p = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, OMP_NUM_THREADS="1"), timeout=600, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr[-3000:]
     text = open(f"{LOG}/memorize/master.log").read()
     assert MEMORIZE_SENTENCE in text.split("Sample 1:")[-1], text[-1500:]
+    # the swarm's final checkpoint, merged into one model, says the same in the one-process sampler
+    from diloco_swarm_b200 import generate as G
+    from diloco_swarm_b200.utils import data as D
+    model = G.load_model(f"{LOG}/memorize/checkpoints/step_170")
+    out = G.generate(model, D.get_tokenizer(), "I am", max_new_tokens=64, temperature=0.0, num_samples=1)
+    assert MEMORIZE_SENTENCE in out[0], out
 
 
 def test_three_stage_pipeline_with_eval_and_sampling():
