@@ -6,6 +6,7 @@ its outputs.  The docstrings name the reference call site each one replaces.
 """
 from __future__ import annotations
 
+import functools
 import math
 import os
 from typing import Optional, Tuple
@@ -32,6 +33,7 @@ def _efficiency(M: int, N: int, splits: int, bm: int, bn: int, units: int) -> fl
     return useful * tiles / (waves * units)
 
 
+@functools.lru_cache(maxsize=None)          # a training run asks for a handful of shapes, thousands of times a step
 def _pick_bn(M: int, N: int, splits: int = 1) -> int:
     """Tile choice: 512 = 256x256 on a CTA pair (least operand traffic per FLOP),
     256 = 128x256 on one CTA, 128 = 128x128.  A wider tile wins unless a
@@ -117,8 +119,11 @@ def set_deterministic(on: bool) -> None:
 def wgrad_split(M: int, N: int, K: int) -> int:
     """Split-K factor for dW[M,N] = dy^T x with K = tokens: the weight gradients
     of a block have few output tiles, so K is split until the SMs are full."""
-    if _DETERMINISTIC:
-        return 1
+    return 1 if _DETERMINISTIC else _wgrad_split(M, N, K)
+
+
+@functools.lru_cache(maxsize=None)
+def _wgrad_split(M: int, N: int, K: int) -> int:
     bm, units = (256, _NUM_SMS // 2) if (_USE_PAIR and M >= 256) else (128, _NUM_SMS)
     tiles = math.ceil(M / bm) * math.ceil(N / 256)
     if tiles >= 4 * units:
