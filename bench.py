@@ -54,6 +54,9 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--cap", type=int, default=8, help="max_micro_batches (in-flight microbatches per rank)")
     ap.add_argument("--layer-split", default="balanced")
+    ap.add_argument("--engine", default="b200", choices=["b200", "torch"],
+                    help="b200 = the sm_100a kernels (the product); torch = this framework's autograd engine on "
+                         "library ops (cuBLAS, SDPA, NCCL), a library twin of the same algorithm for comparison")
     ap.add_argument("--collective", default="fused")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "balanced"])
     ap.add_argument("--no-outer", action="store_true", help="plain SWARM (per-step gradient all-reduce)")
@@ -132,7 +135,7 @@ def build_config(args, S: int):
         eval={"enable": False}, sample={"enable": False},
         logging={"log_dir": os.path.join(tempfile.gettempdir(), "dswarm_bench"), "run_id": f"bench{os.getpid()}",
                  "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"}},
-        engine="b200"), H
+        engine=args.engine), H
 
 
 def run_ours(args) -> dict:
@@ -225,7 +228,8 @@ def run_ours(args) -> dict:
         "config": {"model": f"gpt2-{args.model}", "global_batch": args.batch, "seq_len": args.seq,
                    "micro_batch": args.micro_batch, "parallelism": f"{S} stages x {R} replicas",
                    "algorithm": "swarm" if args.no_outer else f"diloco-swarm H={H}",
-                   "max_micro_batches": args.cap, "layer_split": args.layer_split, "collective": args.collective,
+                   "max_micro_batches": args.cap, "layer_split": args.layer_split, "engine": args.engine,
+                   "collective": args.collective,
                    "routing": args.routing, "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
