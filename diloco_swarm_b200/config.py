@@ -38,9 +38,16 @@ class SwarmConfig(BaseConfig):
     routing_seed: Optional[int] = None
     # (added) "uniform" = independent uniform draw per hop (reference, src/comm.py:91);
     # "balanced" = seeded random permutation with equal shares per replica.
-    routing: Literal["uniform", "balanced", "weighted"] = "uniform"
+    # "weighted" = draw proportional to routing_weights; "adaptive" = the same with weights measured while
+    # training: the inverse of every rank's compute time per microbatch, shared after each step.
+    routing: Literal["uniform", "balanced", "weighted", "adaptive"] = "uniform"
     # (added) one relative throughput per rank for routing = "weighted" (empty: all equal)
     routing_weights: List[float] = []
+    # (added) weight of the newest measurement in the running mean that "adaptive" keeps per rank
+    adaptive_ema: float = 0.5
+    # (added) host-side heterogeneity injector for tests: this rank sleeps so long per microbatch op
+    straggler_rank: int = -1
+    straggler_ms: float = 0.0
 
     @field_validator("routing_weights", mode="before")
     @classmethod

@@ -14,6 +14,7 @@ synchronisations.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import sys
 import time
@@ -113,6 +114,13 @@ class Trainer:
             from .parallel.liveness import Membership
             self.membership = Membership(w.rank, w.world_size, w.master_addr, w.master_port + 1, config.elastic.timeout)
             self.comm.tolerant = True
+        # routing weights: fixed ones from the configuration, or (routing = "adaptive") measured ones
+        self.adaptive = config.swarm.routing == "adaptive"
+        self.route_weights: Optional[List[float]] = list(config.swarm.routing_weights) or None
+        self.rank_ms: List[float] = [0.0] * w.world_size      # running compute time per microbatch, per rank
+        if self.adaptive and config.elastic.enable:
+            raise NotImplementedError("adaptive routing shares its measurements over the whole world and does "
+                                      "not follow membership changes; use routing = weighted with elastic runs")
         self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
         self.num_train_steps = 0
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
@@ -125,11 +133,44 @@ class Trainer:
     def _plan(self, step: int, phase: int, forward_only: bool):
         w = self.world
         # phase separates the routing streams of train / eval / test steps
+        mode = "weighted" if self.adaptive else self.config.swarm.routing
         path = schedule.route(self.routing_seed + 7919 * phase, step, w.num_stages, w.world_size,
-                              self.num_micro, self.alive, mode=self.config.swarm.routing,
-                              weights=self.config.swarm.routing_weights)
+                              self.num_micro, self.alive, mode=mode, weights=self.route_weights)
         cap = self.config.train.max_micro_batches
         return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
+
+    def _compute(self):
+        """Brackets one forward / backward of the step when routing adapts to measured speeds: device time
+        on GPUs (events on the compute stream, after the wait for the op's input), wall time on CPU."""
+        if not self.adaptive:
+            return contextlib.nullcontext()
+        sw = self.config.swarm
+        if sw.straggler_rank == self.world.rank and sw.straggler_ms > 0:
+            return self._slowed(sw.straggler_ms)
+        return self.timer.phase("compute")
+
+    @contextlib.contextmanager
+    def _slowed(self, ms: float):
+        with self.timer.phase("compute"):
+            time.sleep(ms / 1e3)          # injected heterogeneity: this rank is that much slower per op
+            yield
+
+    def _share_speeds(self, compute_ms: float, n_ops: int) -> None:
+        """Every rank contributes its compute time per microbatch of this step; the running means become
+        the routing weights (1 / time) of the following steps, the same on every rank.  The first stage
+        keeps its round-robin chunks, so only later stages are rebalanced."""
+        w, a = self.world, self.config.swarm.adaptive_ema
+        mine = torch.tensor([compute_ms / n_ops if n_ops else 0.0], dtype=torch.float64, device=self.device)
+        got = [torch.zeros_like(mine) for _ in range(w.world_size)]
+        dist.all_gather(got, mine)
+        for r, t in enumerate(got):
+            v = float(t.item())
+            if v > 0:
+                self.rank_ms[r] = v if self.rank_ms[r] == 0 else (1 - a) * self.rank_ms[r] + a * v
+        known = [t for t in self.rank_ms if t > 0]
+        if known:
+            default = sum(known) / len(known)         # a rank that has not worked yet counts as average
+            self.route_weights = [1.0 / (t if t > 0 else default) for t in self.rank_ms]
 
     def _stage_batch(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         """Move what this stage needs of the global batch to the device."""
@@ -194,7 +235,8 @@ class Trainer:
                 rows = D.micro_batch_rows(op.mb, self.mbs)
                 if op.kind == BWD:
                     dy = comm.recv(i)
-                    dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
+                    with self._compute():
+                        dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
                     if op.prev >= 0:
                         comm.send_backward(dx, op.prev)
                     continue
@@ -202,12 +244,14 @@ class Trainer:
                 ids = dev["input_ids"][rows] if eng.is_first else None
                 hidden = comm.recv(i) if op.prev >= 0 else None
                 if op.kind == FWD:
-                    y = eng.forward(op.mb, ids, hidden)
+                    with self._compute():
+                        y = eng.forward(op.mb, ids, hidden)
                     comm.send_forward(y, op.next)
                 else:
-                    loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
-                                                    dev["attention_mask"][rows], self.loss_scale,
-                                                    sync=sync_here and i == last_bwd)
+                    with self._compute():
+                        loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
+                                                        dev["attention_mask"][rows], self.loss_scale,
+                                                        sync=sync_here and i == last_bwd)
                     loss_acc += loss
                     if op.prev >= 0:
                         comm.send_backward(dx, op.prev)
@@ -247,6 +291,8 @@ class Trainer:
             torch.cuda.synchronize(self.device)
         eng.check_status()
         self.last_phase_ms = self.timer.collect()
+        if self.adaptive and w.world_size > 1:
+            self._share_speeds(self.last_phase_ms.get("compute", 0.0), len(ops))
         self.logger.log_message(f"Step {step} device phases (ms): {self.last_phase_ms}", master=False, level=Level.DEBUG)
         step_time = time.time() - start
         local = Outputs(step=step, lr=lr, loss=loss_val, tokens=n_local * tokens_per_mb, norm=float(norm),

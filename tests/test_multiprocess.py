@@ -191,6 +191,23 @@ def test_checkpoint_moves_to_another_topology():
         assert len(got) == 1 and abs(got[0] - want) < 2e-4, (run_id, got, want)
 
 
+def test_adaptive_routing_moves_work_away_from_a_slow_replica():
+    """routing = adaptive on 2 x 2: last-stage replica 3 is slowed on the host (a sleep per microbatch op);
+    every rank shares its compute time per microbatch after each step and the next steps draw replicas in
+    proportion to the measured speeds, so the slow replica ends up with clearly less than its even share."""
+    from diloco_swarm_b200.utils import results
+    launch("adaptive", 4, 2, ["--swarm.routing", "adaptive", "--swarm.straggler_rank", "3", "--swarm.straggler_ms", "80",
+                              "--train.batch_size", "32", "--train.micro_batch_size", "2", "--train.max_steps", "10",
+                              "--train.max_micro_batches", "4"])
+    key = "train/local/num_micro_batches/current"
+    per_step = lambda total: [b - a for a, b in zip([0] + total[:-1], total)]      # the metric is a running count
+    fast = per_step(results.load_history(f"{LOG}/adaptive", "1")[key].tolist())
+    slow = per_step(results.load_history(f"{LOG}/adaptive", "3")[key].tolist())
+    assert len(fast) == 10 and all(f + s == 16 for f, s in zip(fast, slow))       # every microbatch is served once
+    assert sum(slow[2:]) < 0.6 * sum(fast[2:]), (fast, slow)
+    assert len(global_losses("adaptive")) == 10
+
+
 def launch_keep(run_id, nproc, stages, extra):
     """Like launch() but keeps the existing run directory."""
     real_rmtree = shutil.rmtree
