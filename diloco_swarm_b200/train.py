@@ -22,6 +22,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+from tqdm import tqdm
 
 from .config import Config, config_from_argv
 from .models.gpt2 import GPT2Config, sample_next
@@ -34,7 +35,7 @@ from .utils.ckpt import Checkpoint
 from .utils.logger import Level, Logger
 from .utils.metrics import Outputs, eval_metrics, train_metrics
 from .utils.timers import PhaseTimer
-from .utils.misc import format_float, format_int, get_device, seed_everything
+from .utils.misc import format_float, format_int, get_device, get_train_pbar_description, seed_everything
 from .world import World
 
 
@@ -201,6 +202,38 @@ class Trainer:
             self.world.regroup(mask, rebuild_p2p=True)
             self._step_failed = False
 
+    def _run_plan(self, ops, dev: Dict[str, torch.Tensor], loss_acc: torch.Tensor, sync_here: bool, last_bwd: int) -> None:
+        """This rank's forwards and backwards of one training step in plan order, with their transfers.
+        ``loss_acc`` collects the last stage's scaled losses; ``self._served`` counts the microbatches
+        started, so that a step that is cut short still reports what it did."""
+        eng, comm = self.engine, self.comm
+        comm.begin_step(ops, timeout_s=self.config.train.step_timeout)
+        for i, op in enumerate(ops):
+            rows = D.micro_batch_rows(op.mb, self.mbs)
+            if op.kind == BWD:
+                dy = comm.recv(i)
+                with self._compute():
+                    dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
+                if op.prev >= 0:
+                    comm.send_backward(dx, op.prev)
+                continue
+            self._served += 1
+            ids = dev["input_ids"][rows] if eng.is_first else None
+            hidden = comm.recv(i) if op.prev >= 0 else None
+            if op.kind == FWD:
+                with self._compute():
+                    y = eng.forward(op.mb, ids, hidden)
+                comm.send_forward(y, op.next)
+            else:
+                with self._compute():
+                    loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
+                                                    dev["attention_mask"][rows], self.loss_scale,
+                                                    sync=sync_here and i == last_bwd)
+                loss_acc += loss
+                if op.prev >= 0:
+                    comm.send_backward(dx, op.prev)
+        comm.end_step()
+
     def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Optional[Outputs]]:
         cfg, w, eng, comm = self.config, self.world, self.engine, self.comm
         start = time.time()
@@ -218,52 +251,25 @@ class Trainer:
         dev = self._stage_batch(batch)
         tokens_per_mb = self.mbs * self.seq
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
-        n_local = 0
         H = cfg.swarm.sync_every_n_steps
         do_sync = (H > 0 and step % H == 0) or step == self.num_train_steps
         # the static plan tells which backward is this rank's last one: when the step ends with a
         # gradient all-reduce, that backward sends each bucket as soon as it is complete
         last_bwd = max((i for i, op in enumerate(ops) if op.kind in (BWD, FWD_BWD)), default=-1)
         sync_here = do_sync and not eng.has_outer
-        pipeline_phase = self.timer.phase("pipeline")
-        pipeline_phase.__enter__()
         failed = False
         tolerated = (StepTimeout, RuntimeError) if self.membership is not None else (StepTimeout,)
-        try:
-            comm.begin_step(ops, timeout_s=cfg.train.step_timeout)
-            for i, op in enumerate(ops):
-                rows = D.micro_batch_rows(op.mb, self.mbs)
-                if op.kind == BWD:
-                    dy = comm.recv(i)
-                    with self._compute():
-                        dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
-                    if op.prev >= 0:
-                        comm.send_backward(dx, op.prev)
-                    continue
-                n_local += 1
-                ids = dev["input_ids"][rows] if eng.is_first else None
-                hidden = comm.recv(i) if op.prev >= 0 else None
-                if op.kind == FWD:
-                    with self._compute():
-                        y = eng.forward(op.mb, ids, hidden)
-                    comm.send_forward(y, op.next)
-                else:
-                    with self._compute():
-                        loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
-                                                        dev["attention_mask"][rows], self.loss_scale,
-                                                        sync=sync_here and i == last_bwd)
-                    loss_acc += loss
-                    if op.prev >= 0:
-                        comm.send_backward(dx, op.prev)
-            comm.end_step()
-        except tolerated as e:
-            failed = True
-            self.logger.log_message(f"Train step {step} timed out" if isinstance(e, StepTimeout) and "imeout" in str(e)
-                                    else f"Train step {step} failed: {type(e).__name__}: {str(e)[:200]}",
-                                    master=False, level=Level.WARNING)
-            comm.abandon_step()
-        finally:
-            pipeline_phase.__exit__(None, None, None)
+        self._served = 0             # microbatches this rank has started in this step
+        with self.timer.phase("pipeline"):
+            try:
+                self._run_plan(ops, dev, loss_acc, sync_here, last_bwd)
+            except tolerated as e:
+                failed = True
+                self.logger.log_message(f"Train step {step} timed out" if isinstance(e, StepTimeout) and "imeout" in str(e)
+                                        else f"Train step {step} failed: {type(e).__name__}: {str(e)[:200]}",
+                                        master=False, level=Level.WARNING)
+                comm.abandon_step()
+        n_local = self._served
 
         lr = cfg.train.inner_optimizer.lr * lr_factor(self.opt_steps, cfg.train.scheduler, self.num_train_steps)
         applied = True
@@ -446,6 +452,10 @@ class Trainer:
         for _ in range(start_step):      # sequential loader: skip what was consumed
             next(it)
         step = start_step
+        # progress bar on the master's terminal, as in the reference (src/train.py:311); off when the
+        # output is not a terminal so that logs and test captures stay clean
+        bar = tqdm(total=num_train_steps, initial=start_step, position=0, leave=False,
+                   disable=not (w.is_master and sys.stderr.isatty()))
         for step in range(start_step + 1, num_train_steps + 1):
             batch = next(it)
             el = cfg.elastic
@@ -454,8 +464,10 @@ class Trainer:
             local, stage = self.train_step(step, batch)
             local_m.update(local)
             log.log_metrics(local_m.compute(), step=step, master=False)
+            bar.update(1)
             if w.is_master and stage is not None:
                 global_m.update(stage)
+                bar.set_description(get_train_pbar_description(global_m, "[TRAIN]"))
                 last = global_m.compute()
                 log.log_metrics(last, step=step, master=True)
                 g = last
@@ -473,7 +485,9 @@ class Trainer:
             if self.membership is not None and el.leave_rank == w.rank and el.leave_after_step == step:
                 log.log_message(f"Rank {w.rank} leaves after step {step}", master=False, level=Level.WARNING)
                 self.left = True
+                bar.close()
                 return last
+        bar.close()
         if cfg.eval.enable:
             out = self.eval_loop("test", eval_loader, eval_m)
             log.log_metrics(out, step=step, master=True)
