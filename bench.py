@@ -62,6 +62,10 @@ def parse_args():
     ap.add_argument("--no-outer", action="store_true", help="plain SWARM (per-step gradient all-reduce)")
     ap.add_argument("--stages", type=int, default=0, help="pipeline stages (default: 1 for one GPU, else 2)")
     ap.add_argument("--H", type=int, default=0, help="DiLoCo sync interval (default: min(50, steps))")
+    ap.add_argument("--timeline-steps", type=int, default=0,
+                    help="diagnosis: record every rank's forwards and backwards of this many timed steps into "
+                         "<log-dir>/bench<pid>/timeline (utils/timeline.py); adds events to the timed region")
+    ap.add_argument("--log-dir", default=os.path.join(tempfile.gettempdir(), "dswarm_bench"))
     return ap.parse_args()
 
 
@@ -133,8 +137,9 @@ def build_config(args, S: int):
         swarm={"num_stages": S, "sync_every_n_steps": 1 if args.no_outer else H, "layer_split": args.layer_split,
                "collective": args.collective, "routing": args.routing},
         eval={"enable": False}, sample={"enable": False},
-        logging={"log_dir": os.path.join(tempfile.gettempdir(), "dswarm_bench"), "run_id": f"bench{os.getpid()}",
-                 "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"}},
+        logging={"log_dir": args.log_dir, "run_id": f"bench{os.getpid()}" if args.timeline_steps == 0 else "bench",
+                 "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"},
+                 "timeline_steps": args.timeline_steps, "timeline_start": args.warmup + 1},
         engine=args.engine), H
 
 
@@ -230,7 +235,8 @@ def run_ours(args) -> dict:
                    "algorithm": "swarm" if args.no_outer else f"diloco-swarm H={H}",
                    "max_micro_batches": args.cap, "layer_split": args.layer_split, "engine": args.engine,
                    "collective": args.collective,
-                   "routing": args.routing, "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
+                   "routing": args.routing, **({"timeline_steps": args.timeline_steps} if args.timeline_steps else {}),
+                   "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},

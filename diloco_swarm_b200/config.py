@@ -177,6 +177,10 @@ class LoggingConfig(BaseConfig):
     console: ConsoleLoggingConfig = ConsoleLoggingConfig()
     file: FileLoggingConfig = FileLoggingConfig()
     wandb: WandbLoggingConfig = WandbLoggingConfig()
+    # (added) record start and end of every forward / backward of this many training steps, beginning
+    # with step timeline_start, into <run>/timeline/<rank>.jsonl (utils/timeline.py); 0 = off
+    timeline_steps: int = 0
+    timeline_start: int = 2
 
 
 class ElasticConfig(BaseConfig):

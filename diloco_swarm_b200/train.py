@@ -122,6 +122,10 @@ class Trainer:
         if self.adaptive and config.elastic.enable:
             raise NotImplementedError("adaptive routing shares its measurements over the whole world and does "
                                       "not follow membership changes; use routing = weighted with elastic runs")
+        self.timeline = None
+        if config.logging.timeline_steps > 0:
+            from .utils.timeline import StepTimeline
+            self.timeline = StepTimeline(self.device, os.path.join(self.logger.log_dir, "timeline"), w.rank)
         self.opt_steps = 0           # optimiser steps taken so far (drives the LR schedule)
         self.num_train_steps = 0
         self.ckpt = Checkpoint(self.logger.checkpoint_dir)
@@ -140,15 +144,29 @@ class Trainer:
         cap = self.config.train.max_micro_batches
         return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
 
-    def _compute(self):
-        """Brackets one forward / backward of the step when routing adapts to measured speeds: device time
-        on GPUs (events on the compute stream, after the wait for the op's input), wall time on CPU."""
-        if not self.adaptive:
-            return contextlib.nullcontext()
+    def _traced(self, name: str):
+        """A named span on this rank's lane of the timeline, when one is being recorded."""
+        if self.timeline is not None and self.timeline.step is not None:
+            return self.timeline.op(name)
+        return contextlib.nullcontext()
+
+    def _compute(self, name: str):
+        """Brackets one forward / backward of the step: a span on the timeline, and the compute time per
+        microbatch when routing adapts to measured speeds (device time on GPUs, events on the compute
+        stream after the wait for the op's input; wall time on CPU)."""
+        return self._both(self._traced(name), self._measured()) if self.adaptive else self._traced(name)
+
+    def _measured(self):
         sw = self.config.swarm
         if sw.straggler_rank == self.world.rank and sw.straggler_ms > 0:
             return self._slowed(sw.straggler_ms)
         return self.timer.phase("compute")
+
+    @staticmethod
+    @contextlib.contextmanager
+    def _both(a, b):
+        with a, b:
+            yield
 
     @contextlib.contextmanager
     def _slowed(self, ms: float):
@@ -212,7 +230,7 @@ class Trainer:
             rows = D.micro_batch_rows(op.mb, self.mbs)
             if op.kind == BWD:
                 dy = comm.recv(i)
-                with self._compute():
+                with self._compute(f"B{op.mb}"):
                     dx = eng.backward(op.mb, dy, sync=sync_here and i == last_bwd)
                 if op.prev >= 0:
                     comm.send_backward(dx, op.prev)
@@ -221,11 +239,11 @@ class Trainer:
             ids = dev["input_ids"][rows] if eng.is_first else None
             hidden = comm.recv(i) if op.prev >= 0 else None
             if op.kind == FWD:
-                with self._compute():
+                with self._compute(f"F{op.mb}"):
                     y = eng.forward(op.mb, ids, hidden)
                 comm.send_forward(y, op.next)
             else:
-                with self._compute():
+                with self._compute(f"FB{op.mb}"):
                     loss, dx = eng.forward_backward(op.mb, ids, hidden, dev["target_ids"][rows],
                                                     dev["attention_mask"][rows], self.loss_scale,
                                                     sync=sync_here and i == last_bwd)
@@ -245,6 +263,9 @@ class Trainer:
                 self.logger.log_message(f"Rank {w.rank} dies silently at step {step}", master=False, level=Level.WARNING)
                 self.logger.close()
                 os._exit(0)
+        lg = cfg.logging
+        if self.timeline is not None and lg.timeline_start <= step < lg.timeline_start + lg.timeline_steps:
+            self.timeline.begin_step(step)
         eng.train()
         eng.zero_grad()
         _, ops = self._plan(step, 0, forward_only=False)
@@ -283,13 +304,13 @@ class Trainer:
         norm = 0.0
         if applied:
             if do_sync and not eng.has_outer:
-                with self.timer.phase("grad_sync"):
+                with self.timer.phase("grad_sync"), self._traced("grad_sync"):
                     eng.sync_gradients()
-            with self.timer.phase("optimizer"):
+            with self.timer.phase("optimizer"), self._traced("optimizer"):
                 norm = eng.optimizer_step(lr, cfg.train.max_norm)
             self.opt_steps += 1
             if do_sync and eng.has_outer:
-                with self.timer.phase("outer_sync"):
+                with self.timer.phase("outer_sync"), self._traced("outer_sync"):
                     eng.outer_step()
         self.last_enqueue_s = time.time() - start   # host time to queue the whole step
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
@@ -297,6 +318,8 @@ class Trainer:
             torch.cuda.synchronize(self.device)
         eng.check_status()
         self.last_phase_ms = self.timer.collect()
+        if self.timeline is not None:
+            self.timeline.end_step()
         if self.adaptive and w.world_size > 1:
             self._share_speeds(self.last_phase_ms.get("compute", 0.0), len(ops))
         self.logger.log_message(f"Step {step} device phases (ms): {self.last_phase_ms}", master=False, level=Level.DEBUG)

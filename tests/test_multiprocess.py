@@ -208,6 +208,34 @@ def test_adaptive_routing_moves_work_away_from_a_slow_replica():
     assert len(global_losses("adaptive")) == 10
 
 
+def test_step_timeline_of_a_swarm():
+    """--logging.timeline_steps: every rank records its forwards and backwards of two steps; the merged
+    trace has one lane per rank, spans that do not overlap within a lane, every microbatch once per stage,
+    and a last stage that only starts after the first stage's first forward."""
+    from diloco_swarm_b200.utils import timeline as T
+    launch("timeline", 4, 2, ["--logging.timeline_steps", "2", "--logging.timeline_start", "2", "--train.max_steps", "4"])
+    recs = T.load(f"{LOG}/timeline/timeline")
+    assert sorted((r["rank"], r["step"]) for r in recs) == [(r, s) for r in range(4) for s in (2, 3)]
+    for r in recs:
+        spans = sorted((o["start_ms"], o["end_ms"]) for o in r["ops"])
+        assert all(a[1] <= b[0] + 1e-6 for a, b in zip(spans, spans[1:])), r
+        assert {"optimizer", "grad_sync"} <= {o["name"] for o in r["ops"]}
+    step2 = [r for r in recs if r["step"] == 2]
+    fwd_first = sorted(o["name"] for r in step2 if r["rank"] % 2 == 0 for o in r["ops"] if o["name"].startswith("F"))
+    last = sorted(o["name"] for r in step2 if r["rank"] % 2 == 1 for o in r["ops"] if o["name"].startswith("FB"))
+    assert fwd_first == sorted(f"F{m}" for m in range(4)) and last == sorted(f"FB{m}" for m in range(4))
+    trace = T.chrome_trace(recs)
+    assert {e["pid"] for e in trace["traceEvents"]} == {0, 1, 2, 3}
+    origin = min(r["t0"] for r in step2)
+    start = lambda r, prefix: min((r["t0"] - origin) * 1e3 + o["start_ms"] for o in r["ops"] if o["name"].startswith(prefix))
+    first_fwd_end = min((r["t0"] - origin) * 1e3 + o["end_ms"] for r in step2 if r["rank"] % 2 == 0
+                        for o in r["ops"] if o["name"].startswith("F"))
+    assert all(start(r, "FB") >= first_fwd_end - 1.0 for r in step2 if r["rank"] % 2 == 1 and
+               any(o["name"].startswith("FB") for o in r["ops"]))
+    util = T.utilisation(recs)
+    assert set(util) == {2, 3} and all(0 < v <= 1.0 + 1e-6 for k, v in util[2].items() if k.endswith("_busy"))
+
+
 def launch_keep(run_id, nproc, stages, extra):
     """Like launch() but keeps the existing run directory."""
     real_rmtree = shutil.rmtree
