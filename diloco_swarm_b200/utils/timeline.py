@@ -4,7 +4,8 @@ The reference times a whole step with ``time.time()`` (src/train.py:162,272) and
 where inside a step a rank computes and where it waits.  With ``--logging.timeline_steps N`` every
 rank records the start and end of each forward / backward of N steps (CUDA events on the compute
 stream on GPUs, the wall clock on CPU; nothing is synchronised beyond the step's own sync) and
-appends them to ``<run>/timeline/<rank>.jsonl``.  This module's command line merges the per-rank
+appends them to ``<run>/timeline/<rank>.jsonl`` (on GPUs also when the host queued each of them, which
+shows whether the device waits for the host or for a peer).  This module's command line merges the per-rank
 files into one trace that chrome://tracing or Perfetto shows as a pipeline diagram, and prints how
 busy every rank was:
 
@@ -36,9 +37,10 @@ class StepTimeline:
         self._t0_host = 0.0
         self._t0_event = None
         self._ops: List[Tuple[str, object, object]] = []
+        self._host: List[Tuple[str, float, float]] = []
 
     def begin_step(self, step: int) -> None:
-        self.step, self._ops = step, []
+        self.step, self._ops, self._host = step, [], []
         if self.cuda:
             self._t0_event = torch.cuda.Event(enable_timing=True)
             torch.cuda.current_stream().synchronize()      # host clock and device clock meet here
@@ -54,12 +56,14 @@ class StepTimeline:
             return
         if self.cuda:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            h0 = time.time()
             e0.record()
             try:
                 yield
             finally:
                 e1.record()
                 self._ops.append((name, e0, e1))
+                self._host.append((name, h0, time.time()))     # when the host queued the same work
         else:
             t0 = time.time()
             try:
@@ -78,9 +82,12 @@ class StepTimeline:
             else:
                 start, end = (a - self._t0_host) * 1e3, (b - self._t0_host) * 1e3
             rows.append({"name": name, "start_ms": start, "end_ms": end})
+        host = [{"name": n, "start_ms": (a - self._t0_host) * 1e3, "end_ms": (b - self._t0_host) * 1e3}
+                for n, a, b in self._host]
         with open(self.path, "a") as f:
-            f.write(json.dumps({"rank": self.rank, "step": self.step, "t0": self._t0_host, "ops": rows}) + "\n")
-        self.step, self._ops = None, []
+            f.write(json.dumps({"rank": self.rank, "step": self.step, "t0": self._t0_host, "ops": rows,
+                                "host": host}) + "\n")
+        self.step, self._ops, self._host = None, [], []
 
 
 # ---------------------------------------------------------------------- merging and reading
@@ -103,6 +110,9 @@ def chrome_trace(records: List[dict]) -> dict:
         base_us = (r["t0"] - origin) * 1e6
         for op in r["ops"]:
             events.append({"name": op["name"], "cat": f"step {r['step']}", "ph": "X", "pid": r["rank"], "tid": 0,
+                           "ts": base_us + op["start_ms"] * 1e3, "dur": max(0.0, op["end_ms"] - op["start_ms"]) * 1e3})
+        for op in r.get("host", []):        # GPUs only: the host's enqueue of the same operations, on a second lane
+            events.append({"name": op["name"], "cat": f"step {r['step']}", "ph": "X", "pid": r["rank"], "tid": 1,
                            "ts": base_us + op["start_ms"] * 1e3, "dur": max(0.0, op["end_ms"] - op["start_ms"]) * 1e3})
     for rank in sorted({r["rank"] for r in records}):
         events.append({"name": "process_name", "ph": "M", "pid": rank, "args": {"name": f"rank {rank}"}})
