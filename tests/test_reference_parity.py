@@ -1,0 +1,245 @@
+"""This framework's host-side components against the reference's own code, on CPU.
+
+The unmodified reference is installed under ``baseline/_ref`` for the benchmark's reference arm.  Where it
+is present, its classes serve as the oracle here: the same weights give the same logits, the same loss,
+the same parameters after optimiser steps, the same DiLoCo outer step, the same layer split, the same
+microbatch partition, learning-rate schedule and metric values.  Skipped when the install is missing.
+"""
+import math
+import os
+import sys
+import types
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _import_reference():
+    if not os.path.isdir(os.path.join(REF, "src")):
+        pytest.skip("baseline/_ref is not installed")
+    sys.modules.setdefault("autorootcwd", types.ModuleType("autorootcwd"))      # only changes directory
+    try:
+        import pydantic_config
+        if not hasattr(pydantic_config, "parse_argv"):
+            pydantic_config.parse_argv = lambda: {}                                # imported, never called here
+        if REF not in sys.path:
+            sys.path.insert(0, REF)
+        import src.ckpt as rckpt
+        import src.config as rc
+        import src.metrics as rm
+        import src.model as rmodel
+        import src.sampler as rs
+        import src.utils as ru
+    except Exception as e:                                                         # missing optional packages
+        pytest.skip(f"the reference does not import here: {type(e).__name__}: {e}")
+    return types.SimpleNamespace(ckpt=rckpt, config=rc, metrics=rm, model=rmodel, sampler=rs, utils=ru)
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return _import_reference()
+
+
+def _pair(ref, tied=False, n_layer=2):
+    """The reference's model and ours holding the same weights."""
+    from diloco_swarm_b200.models.gpt2 import GPT2Config, TorchStage
+    kw = dict(block_size=64, vocab_size=512, n_layer=n_layer, n_head=4, n_embd=64, dropout=0.0, bias=True,
+              parameter_sharing=tied)
+    torch.manual_seed(0)
+    theirs = ref.model.GPT2(ref.model.GPT2Config(**kw))
+    ours = TorchStage(GPT2Config(**kw), 0, 1)
+    assert set(ours.state_dict()) == set(theirs.state_dict())
+    ours.load_state_dict(theirs.state_dict())
+    return theirs, ours
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_same_weights_same_logits(ref, tied):
+    theirs, ours = _pair(ref, tied)
+    ids = torch.randint(0, 512, (3, 33), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        a, b = theirs(ids), ours(input_ids=ids)
+    assert a.shape == b.shape == (3, 33, 512) and torch.allclose(a, b, atol=1e-6, rtol=0)
+    assert ours.num_parameters() == theirs.num_parameters()
+
+
+def test_masked_loss_and_adamw_steps(ref):
+    """Three steps of forward, masked loss, backward, clipping and AdamW (weight decay on every tensor)."""
+    from diloco_swarm_b200.config import OptimizerConfig
+    from diloco_swarm_b200.optim import get_optimizer
+    theirs, ours = _pair(ref)
+    opt_t = ref.utils.get_optimizer(theirs, ref.config.OptimizerConfig(type="AdamW", lr=1e-2))
+    opt_o = get_optimizer(ours, OptimizerConfig(type="AdamW", lr=1e-2))
+    assert opt_o.defaults["weight_decay"] == opt_t.defaults["weight_decay"] == 0.1
+    assert tuple(opt_o.defaults["betas"]) == tuple(opt_t.defaults["betas"]) == (0.9, 0.95)
+    g = torch.Generator().manual_seed(2)
+    loss_fn = torch.nn.CrossEntropyLoss()
+    for _ in range(3):
+        ids = torch.randint(0, 512, (4, 17), generator=g)
+        mask = (torch.rand(4, 16, generator=g) > 0.3).long()
+        inp, tgt = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()      # as the reference's collate_batch
+        la = loss_fn(*ref.utils.filter_logits_targets(theirs(inp), tgt, mask))
+        logits = ours(input_ids=inp)
+        keep = mask.reshape(-1).bool()
+        lb = torch.nn.functional.cross_entropy(logits.reshape(-1, 512)[keep], tgt.reshape(-1)[keep])
+        assert torch.allclose(la, lb, atol=1e-6)
+        for model, loss, opt in ((theirs, la, opt_t), (ours, lb, opt_o)):
+            opt.zero_grad()
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+            opt.step()
+    sa, sb = theirs.state_dict(), ours.state_dict()
+    assert all(torch.allclose(sa[k], sb[k], atol=1e-6) for k in sa)
+
+
+def test_diloco_outer_step_matches_the_reference_helpers(ref):
+    """One replica: H inner steps, then pseudo-gradient, outer SGD-Nesterov and copy back, done with the
+    reference's helpers (src/utils.py:213-226) and with this framework's autograd engine."""
+    from helpers import make_config, single_world
+    from diloco_swarm_b200.models.engine_torch import TorchEngine
+    from diloco_swarm_b200.models.gpt2 import GPT2Config
+    kw = dict(block_size=64, vocab_size=512, n_layer=2, n_head=4, n_embd=64, dropout=0.0, bias=True, parameter_sharing=False)
+    cfg = make_config(model={k: kw[k] for k in ("block_size", "vocab_size", "n_layer", "n_head", "n_embd")},
+                      train={"inner_optimizer": {"type": "AdamW", "lr": 1e-2},
+                             "outer_optimizer": {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}},
+                      swarm={"num_stages": 1}, amp={"enable": False})
+    eng = TorchEngine(GPT2Config(**kw), single_world(), cfg, torch.device("cpu"))
+    inner = ref.model.GPT2(ref.model.GPT2Config(**kw))
+    inner.load_state_dict(eng.model.state_dict())
+    eng.reset_outer()
+    outer = ref.utils.get_outer_model(inner)
+    opt_in = ref.utils.get_optimizer(inner, ref.config.OptimizerConfig(type="AdamW", lr=1e-2))
+    opt_out = ref.utils.get_optimizer(outer, ref.config.OptimizerConfig(type="SGD", lr=0.7, nesterov=True))
+    g = torch.Generator().manual_seed(3)
+    loss_fn = torch.nn.CrossEntropyLoss()
+    for round_ in range(2):                       # two outer steps, so that the momentum buffer matters
+        for _ in range(2):
+            ids = torch.randint(0, 512, (2, 17), generator=g)
+            inp, tgt, mask = ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), torch.ones(2, 16, dtype=torch.long)
+            opt_in.zero_grad()
+            loss_fn(*ref.utils.filter_logits_targets(inner(inp), tgt, mask)).backward()
+            torch.nn.utils.clip_grad_norm_(inner.parameters(), 1.0)
+            opt_in.step()
+            eng.train()
+            eng.zero_grad()
+            eng.forward_backward(0, inp, None, tgt, mask, 1.0)
+            eng.optimizer_step(1e-2, 1.0)
+        ref.utils.compute_pseudo_gradient(inner, outer)
+        opt_out.step()
+        opt_out.zero_grad()
+        ref.utils.sync_inner_model(outer, inner)
+        eng.outer_step()
+        sa, sb = inner.state_dict(), eng.model.state_dict()
+        assert all(torch.allclose(sa[k], sb[k], atol=2e-6) for k in sa), round_
+
+
+@pytest.mark.parametrize("n_layer,stages", [(12, 2), (12, 5), (4, 3), (24, 4)])
+def test_layer_split_and_stage_shards(ref, n_layer, stages):
+    """Block ranges per stage as ShardedGPT2.distribute_layers gives them (src/model.py:195-198), and for
+    the small cases the stage modules themselves: a stage of ours holds the tensors of the reference's shard
+    under the same (stage-local) names."""
+    from diloco_swarm_b200.models.gpt2 import GPT2Config, TorchStage, split_layers
+    ours = split_layers(n_layer, stages, "even")
+    for s in range(stages):
+        w = types.SimpleNamespace(num_stages=stages, stage=s)
+        assert ours[s] == ref.model.ShardedGPT2.distribute_layers(None, w, n_layer)
+    if n_layer <= 4:
+        kw = dict(block_size=32, vocab_size=256, n_layer=n_layer, n_head=2, n_embd=32, dropout=0.0, bias=True,
+                  parameter_sharing=False)
+        for s in range(stages):
+            w = types.SimpleNamespace(num_stages=stages, stage=s, is_first_stage=s == 0, is_last_stage=s == stages - 1)
+            shard = ref.model.ShardedGPT2(ref.model.GPT2(ref.model.GPT2Config(**kw)), w)
+            mine = TorchStage(GPT2Config(**kw), s, stages)
+            theirs = {k: tuple(v.shape) for k, v in shard.state_dict().items()}
+            assert {k: tuple(v.shape) for k, v in mine.state_dict().items()} == theirs
+
+
+def test_microbatch_partition_and_sampler(ref):
+    """Rows of a batch per first-stage rank: the reference's BatchSampler (src/sampler.py:16-39) and ours."""
+    from diloco_swarm_b200.utils import data as D
+    batch = {"input_ids": torch.arange(22 * 3).reshape(22, 3)}
+    for ranks, mbs in (([0, 2, 4], 4), ([0], 8), ([1, 3], 2)):
+        for r in ranks:
+            a = list(ref.sampler.BatchSampler(ref.sampler.BatchData(batch), r, ranks, mbs))
+            b = list(D.BatchSampler(D.BatchData(batch), r, ranks, mbs))
+            assert a == b, (ranks, mbs, r)
+
+
+def test_learning_rate_schedule(ref):
+    from diloco_swarm_b200.config import SchedulerConfig
+    from diloco_swarm_b200.optim import lr_factor
+    p = [torch.nn.Parameter(torch.zeros(1))]
+    opt = torch.optim.SGD(p, lr=1.0)
+    sched = ref.utils.get_scheduler(opt, ref.config.SchedulerConfig(enable=True, num_warmup_steps=5))
+    ours = SchedulerConfig(enable=True, num_warmup_steps=5)
+    for step in range(12):
+        assert sched.get_last_lr()[0] == pytest.approx(lr_factor(step, ours, 100))
+        opt.step()
+        sched.step()
+
+
+def test_metric_values(ref):
+    """The same sequence of step outputs through the reference's Metrics and ours: same keys, same values
+    (perplexity averaged arithmetically, throughput = tokens / time, totals and running means)."""
+    from diloco_swarm_b200.utils import metrics as M
+    rm = ref.metrics
+    theirs = rm.Metrics([rm.Step(), rm.Time(), rm.MicroTime(), rm.Tokens(), rm.NumMicroBatches(), rm.Norm(), rm.Loss(),
+                         rm.Perplexity(), rm.Throughput(), rm.LearningRate()], name="train/global")
+    ours = M.train_metrics("train/global")
+    e_t = rm.Metrics([rm.Throughput(), rm.Loss(), rm.Perplexity()], name="eval")
+    e_o = M.eval_metrics("eval")
+    for step in range(1, 5):
+        kw = dict(step=step, time=0.5 + 0.1 * step, loss=3.0 / step, tokens=4096 * step, num_micro_batches=4,
+                  lr=1e-3 * step, norm=1.0 + step, micro_step_time=0.05 * step)
+        theirs.update(rm.Outputs(**kw))
+        ours.update(M.Outputs(**kw))
+        e_t.update(rm.Outputs(step=step, time=kw["time"], loss=kw["loss"], tokens=kw["tokens"]))
+        e_o.update(M.Outputs(step=step, time=kw["time"], loss=kw["loss"], tokens=kw["tokens"]))
+        for a, b in ((theirs.compute(), ours.compute()), (e_t.compute(), e_o.compute())):
+            assert set(a) == set(b)
+            for k in a:
+                assert (a[k] is None and b[k] is None) or a[k] == pytest.approx(b[k]), k
+    assert ours.compute()["train/global/perplexity/average"] == pytest.approx(
+        sum(math.exp(3.0 / s) for s in range(1, 5)) / 4)
+
+
+@pytest.mark.parametrize("world_size,local_rank", [(1, 0), (4, 3)])
+def test_checkpoint_files_are_interchangeable(ref, tmp_path, world_size, local_rank):
+    """A stage saved by the reference's Checkpoint is loaded by ours and the other way round: same
+    directory and file names (src/ckpt.py:45-51), same state-dict keys."""
+    from diloco_swarm_b200.utils.ckpt import Checkpoint
+    theirs_model, ours_model = _pair(ref)
+    world = types.SimpleNamespace(world_size=world_size, local_rank=local_rank)
+    a, b = ref.ckpt.Checkpoint(str(tmp_path / "a")), Checkpoint(str(tmp_path / "a"))
+    a.setup(world)
+    b.setup(world)
+    path = a.save(7, theirs_model)
+    assert os.path.basename(path) == ("model.pt" if world_size == 1 else f"model.{local_rank}.pt")
+    assert b.get_latest_step() == a.get_latest_step() == 7
+    ours_model.load_state_dict(b.load(7))
+    c, d = Checkpoint(str(tmp_path / "b")), ref.ckpt.Checkpoint(str(tmp_path / "b"))
+    c.setup(world)
+    d.setup(world)
+    assert os.path.relpath(c.save(9, ours_model), tmp_path / "b") == os.path.relpath(path, tmp_path / "a").replace("step_7", "step_9")
+    theirs_model.load_state_dict(d.load(9))
+
+
+def test_every_reference_config_field_exists_with_its_default(ref):
+    """The configuration schema (src/config.py:5-95): same classes, every field present, same defaults;
+    fields that only this framework has are additions on top."""
+    import diloco_swarm_b200.config as ours
+    classes = [n for n in dir(ref.config) if n.endswith("Config") and n != "BaseConfig"]
+    assert len(classes) >= 13
+    for name in classes:
+        theirs_cls, ours_cls = getattr(ref.config, name), getattr(ours, name)
+        for field, info in theirs_cls.model_fields.items():
+            assert field in ours_cls.model_fields, f"{name}.{field} is missing"
+            a, b = info.default, ours_cls.model_fields[field].default
+            if hasattr(a, "model_dump"):
+                a, b = a.model_dump(), {k: v for k, v in b.model_dump().items() if k in a.model_dump()}
+            assert repr(a) == repr(b), f"{name}.{field}: {a!r} vs {b!r}"
+    # the comma-separated list of wandb tags (src/config.py:84-88)
+    assert ours.WandbLoggingConfig(tags="a,b").tags == ref.config.WandbLoggingConfig(tags="a,b").tags == ["a", "b"]
