@@ -243,3 +243,50 @@ def test_every_reference_config_field_exists_with_its_default(ref):
             assert repr(a) == repr(b), f"{name}.{field}: {a!r} vs {b!r}"
     # the comma-separated list of wandb tags (src/config.py:84-88)
     assert ours.WandbLoggingConfig(tags="a,b").tags == ref.config.WandbLoggingConfig(tags="a,b").tags == ["a", "b"]
+
+
+def test_batching_helpers(ref):
+    """collate_batch, get_micro_batches, get_num_steps, get_train_setup, the number formats and the
+    progress texts (src/utils.py:107-182) against their counterparts."""
+    from diloco_swarm_b200.utils import data as D
+    from diloco_swarm_b200.utils import metrics as M
+    from diloco_swarm_b200.utils import misc
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 1000, (12, 9), generator=g)
+    mask = (torch.rand(12, 9, generator=g) > 0.2).long()
+    theirs = ref.utils.collate_batch([{"input_ids": r.tolist(), "attention_mask": m.tolist()} for r, m in zip(ids, mask)])
+    ours = D.collate(D.TokenDataset(ids, mask), 0, 12)
+    assert set(theirs) == set(ours) and all(torch.equal(theirs[k], ours[k]) for k in theirs)
+    # the (root rank, local micro step) naming of microbatches and their rows
+    world = types.SimpleNamespace(first_stage_ranks=[0, 2, 4])
+    a = {(r, s): mb for r, s, mb in ref.utils.get_micro_batches(theirs, 2, world)}
+    b = {(r, s): mb for r, s, mb in D.get_micro_batches(ours, 2, [0, 2, 4])}
+    assert set(a) == set(b) and all(torch.equal(a[k]["input_ids"], b[k]["input_ids"]) for k in a)
+    for args in ((10, -1, 100, 8), (-1, 2, 100, 8), (10, 1, 100, 8), (1000, 3, 64, 16)):
+        assert ref.utils.get_num_steps(*args) == D.get_num_steps(*args)
+    assert ref.utils.get_train_setup(20, 64, 128, 8, 5000) == D.get_train_setup(20, 64, 128, 8, 5000)
+    for n in (7, 999, 1000, 123456, 7_654_321, 12_345_678_901):
+        assert ref.utils.format_int(n) == misc.format_int(n) and ref.utils.format_int(n, 1) == misc.format_int(n, 1)
+    assert ref.utils.format_float(3.14159, 3) == misc.format_float(3.14159, 3)
+    rm = ref.metrics
+    tm = rm.Metrics([rm.Step(), rm.Time(), rm.MicroTime(), rm.Tokens(), rm.NumMicroBatches(), rm.Norm(), rm.Loss(),
+                     rm.Perplexity(), rm.Throughput(), rm.LearningRate()], name="train/global")
+    om = M.train_metrics("train/global")
+    kw = dict(step=3, time=0.7, loss=2.5, tokens=8192, num_micro_batches=4, lr=1e-3, norm=1.5, micro_step_time=0.1)
+    tm.update(rm.Outputs(**kw))
+    om.update(M.Outputs(**kw))
+    assert ref.utils.get_train_pbar_description(tm, "[TRAIN]") == misc.get_train_pbar_description(om, "[TRAIN]")
+    assert ref.utils.get_eval_pbar_description(tm, "[EVAL]") == misc.get_eval_pbar_description(om, "[EVAL]")
+
+
+@pytest.mark.parametrize("temperature,top_k", [(1.0, None), (0.7, 5), (1.3, 50)])
+def test_single_process_sampler(ref, temperature, top_k):
+    """GPT2.generate (src/model.py:160-175): with the same weights and the same random stream both
+    samplers emit the same tokens."""
+    theirs, ours = _pair(ref)
+    prompt = torch.randint(0, 512, (3, 5), generator=torch.Generator().manual_seed(9))
+    torch.manual_seed(11)
+    a = theirs.generate(prompt.clone(), 12, temperature=temperature, top_k=top_k)
+    torch.manual_seed(11)
+    b = ours.generate(prompt.clone(), 12, temperature=temperature, top_k=top_k)
+    assert torch.equal(a, b)
