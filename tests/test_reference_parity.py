@@ -290,3 +290,45 @@ def test_single_process_sampler(ref, temperature, top_k):
     torch.manual_seed(11)
     b = ours.generate(prompt.clone(), 12, temperature=temperature, top_k=top_k)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("is_master", [True, False])
+def test_logger_files_and_lines(ref, tmp_path, is_master):
+    """Same calls into the reference's Logger (src/logger.py:21-111) and ours: the same files with the same
+    lines (timestamps aside; the reference's file format opens the rank tag with a doubled bracket).  Ours
+    adds the metric history and the saved configuration next to them."""
+    import re
+    import src.logger as rl
+    from helpers import make_config
+    from diloco_swarm_b200.utils import logger as ol
+    world = types.SimpleNamespace(rank=1, local_rank=1, world_size=2, num_stages=2, is_master=is_master)
+    cfg = make_config()
+
+    def drive(mod, log_dir):
+        lc = (ref.config.LoggingConfig if mod is rl else type(cfg.logging))(
+            log_dir=str(log_dir), run_id="run", console={"log_level": "ERROR"}, file={"log_level": "DEBUG"})
+        lg = mod.Logger(world, lc)
+        lg.log_message("hello", master=False, level=mod.Level.INFO)
+        lg.log_message("to the master", master=True, level=mod.Level.WARNING)
+        lg.log_config(cfg)
+        lg.log_metrics({"train/local/loss/current": 1.5}, step=1, master=False)
+        lg.log_metrics({"train/global/loss/current": 1.25}, step=1, master=True)
+        lg.log_samples(["first sample", "second sample"], step=4)
+        for h in [h for name in list(__import__("logging").root.manager.loggerDict) for h in
+                  __import__("logging").getLogger(name).handlers if getattr(h, "baseFilename", "").startswith(str(log_dir))]:
+            h.flush()
+        return os.path.join(str(log_dir), "run")
+
+    a, b = drive(rl, tmp_path / "theirs"), drive(ol, tmp_path / "ours")
+    files = lambda root: sorted(os.path.relpath(os.path.join(d, f), root) for d, _, fs in os.walk(root) for f in fs)
+    dirs = lambda root: sorted(os.path.relpath(os.path.join(d, x), root) for d, xs, _ in os.walk(root) for x in xs)
+    # in the reference every rank writes samples/<step>.txt (all ranks, the same file at once); here the master does
+    expected = set(files(a)) - (set() if is_master else {"samples/4.txt"})
+    assert expected <= set(files(b)) and set(dirs(a)) <= set(dirs(b))
+    assert set(files(b)) - set(files(a)) <= {"config.yaml", "metrics/1.jsonl", "metrics/master.jsonl"}
+    norm = lambda path: [re.sub(r"^\[[^\]]*\]", "", line).replace("[[", "[") for line in open(path).read().splitlines()]
+    for f in files(a):
+        if f.endswith(".log"):
+            assert norm(os.path.join(a, f)) == norm(os.path.join(b, f)), f
+    if is_master:
+        assert open(os.path.join(a, "samples/4.txt")).read() == open(os.path.join(b, "samples/4.txt")).read()
