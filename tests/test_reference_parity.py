@@ -332,3 +332,32 @@ def test_logger_files_and_lines(ref, tmp_path, is_master):
             assert norm(os.path.join(a, f)) == norm(os.path.join(b, f)), f
     if is_master:
         assert open(os.path.join(a, "samples/4.txt")).read() == open(os.path.join(b, "samples/4.txt")).read()
+
+
+@pytest.mark.parametrize("world_size,stages", [(1, 1), (2, 1), (2, 2), (4, 2), (9, 3), (8, 2), (8, 4), (7, 3)])
+def test_world_rank_arithmetic(ref, monkeypatch, world_size, stages):
+    """Stage, leaders, master and neighbours of every rank (src/world.py:10-118), with the reference's
+    process-group calls replaced by no-ops so that all ranks can be built in one process."""
+    import src.world as rw
+    from diloco_swarm_b200.world import World
+    fake = types.SimpleNamespace(TCPStore=lambda **kw: None, init_process_group=lambda **kw: None,
+                                 new_group=lambda *a, **kw: tuple(a[0]) if a else None, barrier=lambda: None)
+    monkeypatch.setattr(rw, "dist", fake)
+    for rank in range(world_size):
+        for k, v in (("RANK", rank), ("LOCAL_RANK", rank), ("WORLD_SIZE", world_size), ("LOCAL_WORLD_SIZE", world_size),
+                     ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", 29400)):
+            monkeypatch.setenv(k, str(v))
+        theirs = rw.World(ref.config.SwarmConfig(num_stages=stages))
+        ours = World(stages, init=False)
+        for attr in ("rank", "local_rank", "world_size", "local_world_size", "master_addr", "master_port", "num_stages",
+                     "stage", "is_first_stage", "is_last_stage", "is_leader", "is_master", "first_stage_leader",
+                     "last_stage_leader", "first_stage_ranks", "has_next_stage", "has_prev_stage"):
+            assert getattr(theirs, attr) == getattr(ours, attr), (rank, attr)
+        # the reference keeps default dicts, which grow when a neighbour that does not exist is asked for
+        assert {s: theirs.stage2ranks[s] for s in range(stages)} == ours.stage2ranks
+        assert {s: theirs.stage2leader[s] for s in range(stages)} == ours.stage2leader
+        if ours.has_next_stage:
+            assert theirs.next_stage_leader == ours.next_stage_leader
+        if ours.has_prev_stage:
+            assert theirs.prev_stage_leader == ours.prev_stage_leader
+        assert repr(theirs) == repr(ours) and dict(theirs) == dict(ours)
