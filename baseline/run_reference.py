@@ -127,8 +127,14 @@ def run_reference(args) -> dict:
     ref_train.get_tokenizer = lambda: _Tokenizer()
 
     model_dims = {"tiny": (4, 4, 128), "small": (12, 12, 768), "medium": (24, 16, 1024), "large": (36, 20, 1280)}[args.model]
-    outer = ({"type": "None", "lr": 0.0} if args.no_outer
-             else {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True})
+    if args.no_outer:
+        # this image's pydantic_config turns the string "None" into None before validation, which the
+        # reference's Literal["SGD", "AdamW", "None"] then refuses: build that one object without validation
+        from src.config import OptimizerConfig
+        outer = OptimizerConfig.model_construct(type="None", lr=0.0, nesterov=False, momentum=0.9, weight_decay=0.1,
+                                                betas=[0.9, 0.95])
+    else:
+        outer = {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
     cfg = ref_train.SwarmConfig(
         model={"n_layer": model_dims[0], "n_head": model_dims[1], "n_embd": model_dims[2]},
         data={"path": "synthetic-zipf", "seq_length": args.seq, "num_workers": 0, "pin_memory": True},

@@ -361,3 +361,71 @@ def test_world_rank_arithmetic(ref, monkeypatch, world_size, stages):
         if ours.has_prev_stage:
             assert theirs.prev_stage_leader == ours.prev_stage_leader
         assert repr(theirs) == repr(ours) and dict(theirs) == dict(ours)
+
+
+def _global_losses(master_log):
+    import ast
+    import re
+    out = []
+    for text in re.findall(r"Global metrics: (\{[^}]*\})", open(master_log).read()):
+        m = ast.literal_eval(text)
+        if "train/global/loss/current" in m:
+            out.append(m["train/global/loss/current"])
+    return out
+
+
+@pytest.mark.parametrize("name,nproc,stages,H,outer", [
+    ("single", 1, 1, 1, "None"),            # one process
+    ("pipeline", 2, 2, 1, "None"),          # two stages, one replica each
+    ("diloco_dp", 2, 1, 2, "nesterov"),     # two replicas of one stage, DiLoCo with an outer step every 2 steps
+])
+def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, H, outer):
+    """The reference's own training run (its main(), gloo, CPU) and this framework's, from the same starting
+    weights on the same batches: the loss curves agree to float32 rounding.  The reference's start weights
+    are saved by the probe and enter here as a step-0 checkpoint; the token file is laid out so that this
+    framework's seeded shuffle-split yields the reference's row order."""
+    import subprocess
+    import numpy as np
+    from diloco_swarm_b200.utils.data import zipf_tokens
+    steps, batch, mbs, seq, eval_size, seed = 4, 8, 2, 32, 0.1, 42
+    ids = zipf_tokens(80, seq + 1, 50257, 1.0, seed=0).numpy().astype(np.int32)
+    np.save(tmp_path / "ref_tokens.npy", ids)
+    n = ids.shape[0]
+    k = max(1, int(round(n * eval_size)))
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(seed)).numpy()
+    mine = np.empty_like(ids)
+    mine[perm[k:]], mine[perm[:k]] = ids[k:], ids[:k]
+    np.save(tmp_path / "our_tokens.npy", mine)
+    port = 29600 + 7 * (os.getpid() % 50) + {"single": 0, "pipeline": 2, "diloco_dp": 4}[name]
+    run = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1"]
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    p = subprocess.run(run + ["--master-port", str(port), os.path.join(ROOT, "tests", "reference_probe.py"),
+                              "--tokens", str(tmp_path / "ref_tokens.npy"), "--out", str(tmp_path / "ref"),
+                              "--stages", str(stages), "--steps", str(steps), "--batch", str(batch), "--mbs", str(mbs),
+                              "--seq", str(seq), "--H", str(H), "--outer", outer, "--eval-size", str(eval_size)],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    theirs = _global_losses(tmp_path / "ref" / "ref" / "master.log")
+    ck = tmp_path / "ours" / "run" / "checkpoints" / "step_0"
+    os.makedirs(ck)
+    for r in range(nproc):
+        torch.save(torch.load(tmp_path / "ref" / f"w0.{r}.pt"), ck / ("model.pt" if nproc == 1 else f"model.{r}.pt"))
+    outer_toml = "@configs/optimizer/none.toml" if outer == "None" else "@configs/optimizer/nesterov.toml"
+    p = subprocess.run(run + ["--master-port", str(port + 10), "-m", "diloco_swarm_b200.train",
+                              "--swarm.num_stages", str(stages), "--swarm.sync_every_n_steps", str(H), "--device", "cpu",
+                              "--amp.enable", "false", "--model", "@configs/model/gpt2-tiny.toml",
+                              "--data.path", f"tokens:{tmp_path / 'our_tokens.npy'}", "--data.seq_length", str(seq),
+                              "--train.inner_optimizer", "@configs/optimizer/adamw.toml", "--train.inner_optimizer.lr", "6e-4",
+                              "--train.outer_optimizer", outer_toml, "--train.outer_optimizer.lr", "0.7",
+                              "--train.max_steps", str(steps), "--train.max_epochs", "-1", "--train.batch_size", str(batch),
+                              "--train.micro_batch_size", str(mbs), "--train.max_micro_batches", "2", "--train.seed", str(seed),
+                              "--eval.enable", "false", "--eval.eval_size", str(eval_size), "--sample.enable", "false",
+                              "--ckpt.resume", "true", "--ckpt.step", "0", "--logging.log_dir", str(tmp_path / "ours"),
+                              "--logging.run_id", "run", "--logging.console.log_level", "ERROR"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    ours = _global_losses(tmp_path / "ours" / "run" / "master.log")
+    assert len(theirs) == len(ours) == steps // H, (theirs, ours)
+    assert max(abs(a - b) for a, b in zip(theirs, ours)) < 2e-4, (theirs, ours)
+    assert theirs[-1] < theirs[0]
