@@ -53,6 +53,10 @@ def main() -> None:
         return stock_loop(num_train_steps, inner_model, *rest, **kw)
 
     ref_train.train_loop = save_start_then_train
+    # the reference draws the next-stage replica with Python's unseeded `random`; a seed per process makes
+    # the probe's runs repeatable (which replica serves a microbatch does not change the gradients)
+    import random
+    random.seed(1000 + rank)
     if a.outer == "None":
         # this image's pydantic_config turns the string "None" into None before validation, which the
         # reference's Literal["SGD", "AdamW", "None"] then refuses: build that one object without validation

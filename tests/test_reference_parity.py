@@ -378,6 +378,7 @@ def _global_losses(master_log):
     ("single", 1, 1, 1, "None"),            # one process
     ("pipeline", 2, 2, 1, "None"),          # two stages, one replica each
     ("diloco_dp", 2, 1, 2, "nesterov"),     # two replicas of one stage, DiLoCo with an outer step every 2 steps
+    ("swarm", 4, 2, 1, "None"),             # 2 stages x 2 replicas, stochastic wiring, gradient sync every step
 ])
 def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, H, outer):
     """The reference's own training run (its main(), gloo, CPU) and this framework's, from the same starting
@@ -387,8 +388,8 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     import subprocess
     import numpy as np
     from diloco_swarm_b200.utils.data import zipf_tokens
-    steps, batch, mbs, seq, eval_size, seed = 4, 8, 2, 32, 0.1, 42
-    ids = zipf_tokens(80, seq + 1, 50257, 1.0, seed=0).numpy().astype(np.int32)
+    steps, batch, mbs, seq, eval_size, seed = 4, (16 if name == "swarm" else 8), 2, 32, 0.1, 42
+    ids = zipf_tokens(120, seq + 1, 50257, 1.0, seed=0).numpy().astype(np.int32)
     np.save(tmp_path / "ref_tokens.npy", ids)
     n = ids.shape[0]
     k = max(1, int(round(n * eval_size)))
@@ -396,7 +397,7 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     mine = np.empty_like(ids)
     mine[perm[k:]], mine[perm[:k]] = ids[k:], ids[:k]
     np.save(tmp_path / "our_tokens.npy", mine)
-    port = 29600 + 7 * (os.getpid() % 50) + {"single": 0, "pipeline": 2, "diloco_dp": 4}[name]
+    port = 29600 + 7 * (os.getpid() % 50) + {"single": 0, "pipeline": 2, "diloco_dp": 4, "swarm": 6}[name]
     run = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1"]
     env = dict(os.environ, OMP_NUM_THREADS="1")
@@ -421,6 +422,10 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
                               "--train.max_steps", str(steps), "--train.max_epochs", "-1", "--train.batch_size", str(batch),
                               "--train.micro_batch_size", str(mbs), "--train.max_micro_batches", "2", "--train.seed", str(seed),
                               "--eval.enable", "false", "--eval.eval_size", str(eval_size), "--sample.enable", "false",
+                              # which replica serves a microbatch does not change the gradients; the logged loss is a
+                              # mean over the replicas that saw data, so both sides must leave no replica empty:
+                              # balanced routing here, a seeded draw that happens to do so in the probe
+                              "--swarm.routing", "balanced",
                               "--ckpt.resume", "true", "--ckpt.step", "0", "--logging.log_dir", str(tmp_path / "ours"),
                               "--logging.run_id", "run", "--logging.console.log_level", "ERROR"],
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
