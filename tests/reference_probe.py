@@ -30,6 +30,7 @@ def main() -> None:
     ap.add_argument("--H", type=int, default=1)
     ap.add_argument("--outer", default="None", choices=["None", "nesterov"])
     ap.add_argument("--eval-size", type=float, default=0.1)
+    ap.add_argument("--eval-every", type=int, default=0, help="0 = no evaluation")
     a = ap.parse_args()
 
     from baseline.run_reference import REF, _Tokenizer, _ZipfDataset
@@ -71,7 +72,7 @@ def main() -> None:
         train={"max_steps": a.steps, "max_epochs": -1, "micro_batch_size": a.mbs, "batch_size": a.batch,
                "max_micro_batches": 2, "inner_optimizer": {"type": "AdamW", "lr": 6e-4}, "outer_optimizer": outer},
         device="cpu", amp={"enable": False}, swarm={"num_stages": a.stages, "sync_every_n_steps": a.H},
-        eval={"enable": False, "eval_size": a.eval_size}, sample={"enable": False},
+        eval={"enable": a.eval_every > 0, "every_n_steps": a.eval_every if a.eval_every > 0 else -1, "eval_size": a.eval_size}, sample={"enable": False},
         logging={"log_dir": a.out, "run_id": "ref", "console": {"log_level": "ERROR"}, "wandb": {"enable": False}})
     ref_train.main(cfg)
 

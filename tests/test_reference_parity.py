@@ -363,14 +363,14 @@ def test_world_rank_arithmetic(ref, monkeypatch, world_size, stages):
         assert repr(theirs) == repr(ours) and dict(theirs) == dict(ours)
 
 
-def _global_losses(master_log):
+def _global_losses(master_log, key="train/global/loss/current"):
     import ast
     import re
     out = []
     for text in re.findall(r"Global metrics: (\{[^}]*\})", open(master_log).read()):
         m = ast.literal_eval(text)
-        if "train/global/loss/current" in m:
-            out.append(m["train/global/loss/current"])
+        if key in m:
+            out.append(m[key])
     return out
 
 
@@ -389,6 +389,7 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     import numpy as np
     from diloco_swarm_b200.utils.data import zipf_tokens
     steps, batch, mbs, seq, eval_size, seed = 4, (16 if name == "swarm" else 8), 2, 32, 0.1, 42
+    eval_every = 2 if name in ("single", "pipeline") else 0      # these two also evaluate: before, during, after
     ids = zipf_tokens(120, seq + 1, 50257, 1.0, seed=0).numpy().astype(np.int32)
     np.save(tmp_path / "ref_tokens.npy", ids)
     n = ids.shape[0]
@@ -404,7 +405,8 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     p = subprocess.run(run + ["--master-port", str(port), os.path.join(ROOT, "tests", "reference_probe.py"),
                               "--tokens", str(tmp_path / "ref_tokens.npy"), "--out", str(tmp_path / "ref"),
                               "--stages", str(stages), "--steps", str(steps), "--batch", str(batch), "--mbs", str(mbs),
-                              "--seq", str(seq), "--H", str(H), "--outer", outer, "--eval-size", str(eval_size)],
+                              "--seq", str(seq), "--H", str(H), "--outer", outer, "--eval-size", str(eval_size),
+                              "--eval-every", str(eval_every)],
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
     assert p.returncode == 0, p.stderr[-3000:]
     theirs = _global_losses(tmp_path / "ref" / "ref" / "master.log")
@@ -421,7 +423,8 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
                               "--train.outer_optimizer", outer_toml, "--train.outer_optimizer.lr", "0.7",
                               "--train.max_steps", str(steps), "--train.max_epochs", "-1", "--train.batch_size", str(batch),
                               "--train.micro_batch_size", str(mbs), "--train.max_micro_batches", "2", "--train.seed", str(seed),
-                              "--eval.enable", "false", "--eval.eval_size", str(eval_size), "--sample.enable", "false",
+                              "--eval.enable", "true" if eval_every else "false", "--eval.every_n_steps",
+                              str(eval_every if eval_every else -1), "--eval.eval_size", str(eval_size), "--sample.enable", "false",
                               # which replica serves a microbatch does not change the gradients; the logged loss is a
                               # mean over the replicas that saw data, so both sides must leave no replica empty:
                               # balanced routing here, a seeded draw that happens to do so in the probe
@@ -434,3 +437,7 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     assert len(theirs) == len(ours) == steps // H, (theirs, ours)
     assert max(abs(a - b) for a, b in zip(theirs, ours)) < 2e-4, (theirs, ours)
     assert theirs[-1] < theirs[0]
+    if eval_every:
+        ev_t = _global_losses(tmp_path / "ref" / "ref" / "master.log", "eval/loss/average")
+        ev_o = _global_losses(tmp_path / "ours" / "run" / "master.log", "eval/loss/average")
+        assert len(ev_t) == len(ev_o) >= 3 and max(abs(a - b) for a, b in zip(ev_t, ev_o)) < 2e-4, (ev_t, ev_o)
