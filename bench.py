@@ -66,6 +66,7 @@ def parse_args():
                     help="diagnosis: record every rank's forwards and backwards of this many timed steps into "
                          "<log-dir>/bench<pid>/timeline (utils/timeline.py); adds events to the timed region")
     ap.add_argument("--log-dir", default=os.path.join(tempfile.gettempdir(), "dswarm_bench"))
+    ap.add_argument("--recv-prefetch", type=int, default=2, help="pipeline receives posted this many operations ahead")
     return ap.parse_args()
 
 
@@ -135,7 +136,7 @@ def build_config(args, S: int):
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
         swarm={"num_stages": S, "sync_every_n_steps": 1 if args.no_outer else H, "layer_split": args.layer_split,
-               "collective": args.collective, "routing": args.routing},
+               "collective": args.collective, "routing": args.routing, "recv_prefetch": args.recv_prefetch},
         eval={"enable": False}, sample={"enable": False},
         logging={"log_dir": args.log_dir, "run_id": f"bench{os.getpid()}" if args.timeline_steps == 0 else "bench",
                  "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"},

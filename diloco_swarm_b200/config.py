@@ -64,6 +64,9 @@ class SwarmConfig(BaseConfig):
     collective: Literal["fused", "nccl"] = "fused"
     # (added) wire dtype of the per-step gradient all-reduce
     grad_wire_dtype: Literal["float32", "bfloat16"] = "float32"
+    # (added) pipeline receives posted this many operations ahead of their use (a posted NCCL receive is a
+    # resident kernel that waits for its sender, so more look-ahead hides latency but holds SM resources)
+    recv_prefetch: int = 2
 
 
 class ModelConfig(BaseConfig):

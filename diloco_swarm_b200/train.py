@@ -101,7 +101,7 @@ class Trainer:
         self.loss_scale = 1.0 / self.micro_per_device
         self.routing_seed = config.swarm.routing_seed if config.swarm.routing_seed is not None else tc.seed
         self.comm = PipelineComm(w, (self.mbs, self.seq, config.model.n_embd), self.engine.act_dtype,
-                                 self.device, prefetch=2)
+                                 self.device, prefetch=max(1, config.swarm.recv_prefetch))
         if hasattr(self.engine, "warmup"):
             self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
