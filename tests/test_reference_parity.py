@@ -379,6 +379,8 @@ def _global_losses(master_log, key="train/global/loss/current"):
     ("pipeline", 2, 2, 1, "None"),          # two stages, one replica each
     ("diloco_dp", 2, 1, 2, "nesterov"),     # two replicas of one stage, DiLoCo with an outer step every 2 steps
     ("swarm", 4, 2, 1, "None"),             # 2 stages x 2 replicas, stochastic wiring, gradient sync every step
+    ("sparse_sync", 2, 1, 2, "None"),       # no outer optimiser but H = 2: gradients are averaged on every second
+                                            # step only and the replicas are never re-aligned (src/train.py:248-251)
 ])
 def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, H, outer):
     """The reference's own training run (its main(), gloo, CPU) and this framework's, from the same starting
@@ -398,7 +400,7 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     mine = np.empty_like(ids)
     mine[perm[k:]], mine[perm[:k]] = ids[k:], ids[:k]
     np.save(tmp_path / "our_tokens.npy", mine)
-    port = 29600 + 7 * (os.getpid() % 50) + {"single": 0, "pipeline": 2, "diloco_dp": 4, "swarm": 6}[name]
+    port = 29600 + 11 * (os.getpid() % 30) + {"single": 0, "pipeline": 2, "diloco_dp": 4, "swarm": 6, "sparse_sync": 8}[name]
     run = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1"]
     env = dict(os.environ, OMP_NUM_THREADS="1")
