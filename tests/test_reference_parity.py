@@ -66,15 +66,22 @@ def test_same_weights_same_logits(ref, tied):
     assert ours.num_parameters() == theirs.num_parameters()
 
 
-def test_masked_loss_and_adamw_steps(ref):
-    """Three steps of forward, masked loss, backward, clipping and AdamW (weight decay on every tensor)."""
+@pytest.mark.parametrize("kind", ["AdamW", "SGD", "nesterov"])
+def test_masked_loss_and_optimiser_steps(ref, kind):
+    """Three steps of forward, masked loss, backward, clipping and the optimiser: AdamW (weight decay on
+    every tensor), SGD with momentum, SGD-Nesterov (src/utils.py:59-65)."""
     from diloco_swarm_b200.config import OptimizerConfig
     from diloco_swarm_b200.optim import get_optimizer
     theirs, ours = _pair(ref)
-    opt_t = ref.utils.get_optimizer(theirs, ref.config.OptimizerConfig(type="AdamW", lr=1e-2))
-    opt_o = get_optimizer(ours, OptimizerConfig(type="AdamW", lr=1e-2))
-    assert opt_o.defaults["weight_decay"] == opt_t.defaults["weight_decay"] == 0.1
-    assert tuple(opt_o.defaults["betas"]) == tuple(opt_t.defaults["betas"]) == (0.9, 0.95)
+    kw = dict(type="AdamW", lr=1e-2) if kind == "AdamW" else dict(type="SGD", lr=1e-2, nesterov=kind == "nesterov")
+    opt_t = ref.utils.get_optimizer(theirs, ref.config.OptimizerConfig(**kw))
+    opt_o = get_optimizer(ours, OptimizerConfig(**kw))
+    if kind == "AdamW":
+        assert opt_o.defaults["weight_decay"] == opt_t.defaults["weight_decay"] == 0.1
+        assert tuple(opt_o.defaults["betas"]) == tuple(opt_t.defaults["betas"]) == (0.9, 0.95)
+    else:
+        assert {k: opt_o.defaults[k] for k in ("momentum", "nesterov", "weight_decay")} == \
+            {k: opt_t.defaults[k] for k in ("momentum", "nesterov", "weight_decay")}
     g = torch.Generator().manual_seed(2)
     loss_fn = torch.nn.CrossEntropyLoss()
     for _ in range(3):
