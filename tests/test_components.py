@@ -292,3 +292,29 @@ def test_local_token_and_text_datasets(tmp_path):
     packed = D.load_token_file(str(tmp_path / "b.npy"), 8)
     assert packed.rows(0, n2)[0].reshape(-1).tolist() == stream[:n2 * 8] and int(packed.rows(0, 1)[1].min()) == 1
     assert np.load(tmp_path / "b.npy").dtype == np.int32
+
+
+def test_hub_dataset_from_the_local_cache(tmp_path, monkeypatch):
+    """Datasets named like the reference's hub ids (src/utils.py:88-100) load from the on-disk cache under
+    $PERSISTENT_DIR/huggingface without a network: pre-tokenised rows as they are, text rows through the
+    tokenizer when data.tokenize is set."""
+    datasets = pytest.importorskip("datasets")
+    from diloco_swarm_b200.config import DataConfig
+    from diloco_swarm_b200.utils import data as D
+    monkeypatch.setenv("PERSISTENT_DIR", str(tmp_path))
+    tok = D.ByteTokenizer()
+    rows = torch.randint(0, 1000, (6, 17), generator=torch.Generator().manual_seed(0))
+    mask = torch.ones_like(rows)
+    mask[2, 10:] = 0
+    pre = datasets.DatasetDict({"train": datasets.Dataset.from_dict(
+        {"input_ids": rows.tolist(), "attention_mask": mask.tolist()})})
+    pre.save_to_disk(str(tmp_path / "huggingface" / "someone" / "pretokenized"))
+    ds = D.get_dataset(DataConfig(path="someone/pretokenized", seq_length=16), tok, seed=0)
+    assert len(ds) == 6 and torch.equal(ds.input_ids, rows) and torch.equal(ds.attention_mask, mask)
+    text = datasets.DatasetDict({"train": datasets.Dataset.from_dict({"text": ["hello", "a longer line of text"]})})
+    text.save_to_disk(str(tmp_path / "huggingface" / "someone" / "raw"))
+    ds = D.get_dataset(DataConfig(path="someone/raw", seq_length=8, tokenize=True), tok, seed=0)
+    assert ds.input_ids.shape == (2, 9) and ds.attention_mask.sum(1).tolist() == [5, 9]
+    assert tok.decode(ds.input_ids[0][:5]) == "hello"
+    half = D.get_dataset(DataConfig(path="someone/pretokenized", seq_length=16, subset_size=0.5), tok, seed=0)
+    assert len(half) == 3
