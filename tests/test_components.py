@@ -318,3 +318,29 @@ def test_hub_dataset_from_the_local_cache(tmp_path, monkeypatch):
     assert tok.decode(ds.input_ids[0][:5]) == "hello"
     half = D.get_dataset(DataConfig(path="someone/pretokenized", seq_length=16, subset_size=0.5), tok, seed=0)
     assert len(half) == 3
+
+
+def test_wandb_run_per_rank_in_offline_mode(tmp_path, monkeypatch):
+    """logging.wandb.enable (src/logger.py:50-58): one run per rank, grouped by the run id, fed by
+    log_config / log_world / log_metrics; wandb's offline mode stands in for the service."""
+    pytest.importorskip("wandb")
+    from types import SimpleNamespace
+    from diloco_swarm_b200.config import LoggingConfig
+    from diloco_swarm_b200.utils.logger import Logger
+    monkeypatch.setenv("WANDB_MODE", "offline")
+    monkeypatch.setenv("WANDB_SILENT", "true")
+    lc = LoggingConfig(log_dir=str(tmp_path), run_id="w", console={"log_level": "ERROR"},
+                       wandb={"enable": True, "project": "diloco-swarm", "tags": "bench,b200"})
+    assert lc.wandb.tags == ["bench", "b200"]
+    world = single_world()
+    lg = Logger(world, lc)
+    assert lg.wandb_run is not None and lg.wandb_run.group == "w" and lg.wandb_run.name == "rank0"
+    lg.log_config(make_config())
+    lg.log_world(world)
+    lg.log_metrics({"train/global/loss/current": 1.0}, step=1, master=True)
+    lg.log_metrics({"train/local/loss/current": 1.5}, step=1, master=False)
+    assert lg.wandb_run.config["model"]["n_layer"] == make_config().model.n_layer
+    assert lg.wandb_run.config["world"]["world_size"] == 1
+    lg.close()
+    assert lg.wandb_run is None
+    assert any(d.startswith("offline-run") for d in os.listdir(tmp_path / "w" / "wandb"))
