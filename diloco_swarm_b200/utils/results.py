@@ -16,13 +16,15 @@ directories into the notebook's tables:
 
     python -m diloco_swarm_b200.utils.results logs/run_a logs/run_b [--table throughput] [--latex]
 
-Figures need matplotlib, which is optional: ``plot_curves`` raises a clear
-error when it is missing; the tables never need it.
+``plot_curves`` draws the notebook's two figures (perplexity against steps and
+against communication volume): with matplotlib when it is installed, as a plain
+SVG file otherwise.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 from typing import Dict, Mapping, Optional
 
@@ -151,22 +153,85 @@ def throughput_table(runs: Mapping[str, str], key: str = THROUGHPUT) -> pd.DataF
     return pd.DataFrame(rows).sort_values("peak tokens/s", ascending=False).reset_index(drop=True)
 
 
-def plot_curves(runs: Mapping[str, str], path: str, key: str = PERPLEXITY, x: str = "step") -> None:
-    """Metric against steps (or against ``comm_bytes``) for several runs, written to ``path``."""
-    try:
-        import matplotlib
-        matplotlib.use("Agg")
-        from matplotlib import pyplot as plt
-    except ImportError as e:
-        raise RuntimeError("plot_curves needs matplotlib, which is not installed; the tables do not") from e
-    fig, ax = plt.subplots(figsize=(6, 4), dpi=200)
+def _series_for_plot(runs: Mapping[str, str], key: str, x: str) -> Dict[str, tuple]:
+    out = {}
     for label, run_dir in runs.items():
         h = load_history(run_dir)
         if x == "comm_bytes":
             h = with_comm_cost(h, load_config(run_dir))
+        if key not in h.columns:
+            continue
         h = h.dropna(subset=[key])
-        ax.plot(h["_step"] if x == "step" else h[x] / 1e12, h[key], label=label)
-    ax.set_xlabel("Training steps" if x == "step" else "Communication cost (TB)")
+        xs = h["_step"].tolist() if x == "step" else (h[x] / 1e12).tolist()
+        out[label] = (xs, h[key].tolist())
+    return out
+
+
+_COLOURS = ["#1b9e77", "#d95f02", "#7570b3", "#e7298a", "#66a61e", "#e6ab02", "#a6761d", "#666666"]
+
+
+def _nice_ticks(lo: float, hi: float, n: int = 5) -> list:
+    if hi <= lo:
+        return [lo]
+    raw = (hi - lo) / n
+    mag = 10 ** math.floor(math.log10(raw))
+    step = min((m * mag for m in (1, 2, 5, 10)), key=lambda s_: abs(s_ - raw))
+    first = math.ceil(lo / step) * step
+    return [round(first + i * step, 10) for i in range(int((hi - first) / step) + 1)]
+
+
+def write_svg(series: Dict[str, tuple], path: str, xlabel: str, ylabel: str, width: int = 640, height: int = 420) -> None:
+    """A line chart as a plain SVG file: what ``plot_curves`` falls back to without matplotlib.
+    ``series``: label -> (xs, ys)."""
+    pts = [(x, y) for xs, ys in series.values() for x, y in zip(xs, ys)]
+    if not pts:
+        raise ValueError("nothing to plot")
+    x0, x1 = min(p[0] for p in pts), max(p[0] for p in pts)
+    y0, y1 = min(p[1] for p in pts), max(p[1] for p in pts)
+    x1, y1 = (x1 if x1 > x0 else x0 + 1), (y1 if y1 > y0 else y0 + 1)
+    L, R, T, B = 70, 20, 20, 50
+    sx = lambda v: L + (v - x0) / (x1 - x0) * (width - L - R)
+    sy = lambda v: height - B - (v - y0) / (y1 - y0) * (height - T - B)
+    fmt = lambda v: f"{v:g}"
+    o = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="sans-serif" font-size="12">',
+         f'<rect width="{width}" height="{height}" fill="white"/>']
+    for t in _nice_ticks(x0, x1):
+        o.append(f'<line x1="{sx(t):.1f}" y1="{T}" x2="{sx(t):.1f}" y2="{height - B}" stroke="#dddddd"/>')
+        o.append(f'<text x="{sx(t):.1f}" y="{height - B + 16}" text-anchor="middle">{fmt(t)}</text>')
+    for t in _nice_ticks(y0, y1):
+        o.append(f'<line x1="{L}" y1="{sy(t):.1f}" x2="{width - R}" y2="{sy(t):.1f}" stroke="#dddddd"/>')
+        o.append(f'<text x="{L - 6}" y="{sy(t) + 4:.1f}" text-anchor="end">{fmt(t)}</text>')
+    o.append(f'<rect x="{L}" y="{T}" width="{width - L - R}" height="{height - T - B}" fill="none" stroke="black"/>')
+    o.append(f'<text x="{(L + width - R) / 2:.1f}" y="{height - 10}" text-anchor="middle">{xlabel}</text>')
+    o.append(f'<text x="16" y="{(T + height - B) / 2:.1f}" text-anchor="middle" transform="rotate(-90 16 {(T + height - B) / 2:.1f})">{ylabel}</text>')
+    for i, (label, (xs, ys)) in enumerate(series.items()):
+        colour = _COLOURS[i % len(_COLOURS)]
+        path_d = " ".join(f"{'M' if j == 0 else 'L'}{sx(x):.1f},{sy(y):.1f}" for j, (x, y) in enumerate(zip(xs, ys)))
+        o.append(f'<path d="{path_d}" fill="none" stroke="{colour}" stroke-width="2"/>')
+        o.append(f'<rect x="{width - R - 170}" y="{T + 8 + 18 * i}" width="12" height="3" fill="{colour}"/>')
+        o.append(f'<text x="{width - R - 152}" y="{T + 14 + 18 * i}">{label} ({fmt(round(ys[-1], 2))})</text>')
+    o.append("</svg>")
+    with open(path, "w") as f:
+        f.write("\n".join(o) + "\n")
+
+
+def plot_curves(runs: Mapping[str, str], path: str, key: str = PERPLEXITY, x: str = "step") -> None:
+    """Metric against steps (or against ``comm_bytes``, the cumulative communication volume in TB) for
+    several runs, the reference notebook's two figures (cells 14 and 20).  With matplotlib the file type
+    follows ``path``; without it the chart is written as SVG by ``write_svg``."""
+    series = _series_for_plot(runs, key, x)
+    xlabel = "Training steps" if x == "step" else "Communication cost (TB)"
+    try:
+        import matplotlib
+        matplotlib.use("Agg")
+        from matplotlib import pyplot as plt
+    except ImportError:
+        write_svg(series, path if path.endswith(".svg") else path + ".svg", xlabel, key)
+        return
+    fig, ax = plt.subplots(figsize=(6, 4), dpi=200)
+    for label, (xs, ys) in series.items():
+        ax.plot(xs, ys, label=f"{label} ({ys[-1]:.2f})")
+    ax.set_xlabel(xlabel)
     ax.set_ylabel(key)
     ax.grid(True, alpha=0.3)
     ax.legend()
@@ -188,7 +253,8 @@ def main() -> None:
     ap.add_argument("--table", default="perplexity", choices=["perplexity", "method", "throughput", "history"])
     ap.add_argument("--key", default=None, help="metric key (default depends on the table)")
     ap.add_argument("--latex", action="store_true")
-    ap.add_argument("--plot", default=None, help="also write the curves of --key to this file (needs matplotlib)")
+    ap.add_argument("--plot", default=None, help="also write the curves of --key to this file (SVG without matplotlib)")
+    ap.add_argument("--plot-x", default="step", choices=["step", "comm_bytes"])
     a = ap.parse_args()
     runs = _labelled(a.runs)
     if a.table == "perplexity":
@@ -202,7 +268,7 @@ def main() -> None:
         tab = with_comm_cost(load_history(run_dir), load_config(run_dir))
     print(tab.to_latex(index=False) if a.latex else tab.to_markdown(index=False))
     if a.plot:
-        plot_curves(runs, a.plot, a.key or PERPLEXITY)
+        plot_curves(runs, a.plot, a.key or PERPLEXITY, a.plot_x)
 
 
 if __name__ == "__main__":

@@ -82,3 +82,19 @@ def test_cli_prints_a_table(tmp_path, capsys, monkeypatch):
     results.main()
     out = capsys.readouterr().out
     assert "baseline" in out and "Single GPU" in out and "6000" in out
+
+
+def test_figures_without_matplotlib(tmp_path):
+    """The notebook's two figures as SVG: perplexity against steps and against communication volume."""
+    import xml.dom.minidom
+    b = _fake_run(tmp_path, "swarm", 8, 2, 1, [80, 50, 35, 25.0], [1, 1, 1, 1.0])
+    c = _fake_run(tmp_path, "diloco", 8, 2, 2, [85, 55, 38, 26.5], [1, 1, 1, 1.0])
+    runs = {"SWARM": b, "DiLoCo-SWARM": c}
+    for x in ("step", "comm_bytes"):
+        out = tmp_path / f"fig_{x}.svg"
+        results.plot_curves(runs, str(out), x=x)
+        text = open(out if out.exists() else str(out) + ".svg").read()
+        xml.dom.minidom.parseString(text)                       # well-formed
+        assert text.count("<path ") == 2 and "SWARM (25)" in text and "DiLoCo-SWARM (26.5)" in text
+        assert ("Training steps" if x == "step" else "Communication cost (TB)") in text
+    assert results._nice_ticks(0, 10) == [0, 2, 4, 6, 8, 10] and results._nice_ticks(21, 100)[0] >= 21
