@@ -27,6 +27,8 @@ def recorded_launches(script, tmp_path, env=None):
     calls = [line.rstrip("\n").split("\x1f")[:-1] for line in open(log)]
     out = []
     for argv in calls:
+        if "diloco_swarm_b200.train" not in argv:
+            continue                              # e.g. the table command at the end of benchmark.sh
         i = argv.index("diloco_swarm_b200.train")
         nproc = int(argv[argv.index("--nproc-per-node") + 1])
         out.append((nproc, config_from_argv(argv[i + 1:])))
@@ -63,3 +65,14 @@ def test_experiment3_sweeps_the_model_size(tmp_path):
 def test_smoke_script_launch(tmp_path):
     (n, c), = recorded_launches("test.sh", tmp_path)
     assert n == 2 and c.swarm.num_stages == 1 and c.device == "cpu" and c.data.tokenize and c.train.max_steps == 40
+
+
+def test_benchmark_script_covers_the_four_kinds_of_parallelism(tmp_path):
+    from diloco_swarm_b200.utils.results import parallelism
+    runs = recorded_launches("benchmark.sh", tmp_path, {"GPUS": "4", "MBS": "16", "CAPS": "8", "OUT": str(tmp_path / "out")})
+    kinds = [parallelism(n, c.swarm.num_stages) for n, c in runs]
+    assert kinds == ["Single GPU", "Data Parallel", "Pipeline Parallel", "Pipeline Parallel", "SWARM"]
+    assert [c.logging.run_id for _, c in runs] == ["single-mbs16", "dp4-mbs16", "pp2-mbs16-cap8", "pp4-mbs16-cap8",
+                                                   "swarm4-mbs16-cap8"]
+    assert all(c.train.batch_size == 512 and c.train.micro_batch_size == 16 and c.train.max_steps == 5 and
+               c.model.n_embd == 768 and c.data.seq_length == 1024 for _, c in runs)
