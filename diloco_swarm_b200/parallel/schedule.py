@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 
@@ -107,3 +107,71 @@ def micro_batch_key(mb: int, first_stage_ranks: Sequence[int]) -> tuple:
     count their own from 1."""
     r0 = len(first_stage_ranks)
     return first_stage_ranks[mb % r0], mb // r0 + 1
+
+
+class PlanError(RuntimeError):
+    """The plans of a step are inconsistent: they would hang or compute something else than the step."""
+
+
+def check_plans(path: np.ndarray, plans: Dict[int, List[Op]], cap: int, forward_only: bool = False) -> None:
+    """Host-side check of one step's plans (the stand-in for a race detector on the pipeline): every
+    microbatch runs exactly once per stage on the rank the routing names, a backward follows its own
+    forward, no rank holds more than ``cap`` forwards in flight, neighbours agree on who sends what, and
+    a replay over in-order point-to-point channels lets every rank finish (no deadlock).  Raises
+    ``PlanError`` with the first violation.  The trainer runs it on every step with DSWARM_VERIFY_PLANS=1."""
+    M, S_ = path.shape
+    for r, ops in plans.items():
+        st, inflight, seen = r % S_, 0, set()
+        for op in ops:
+            if int(path[op.mb, st]) != r:
+                raise PlanError(f"rank {r} runs microbatch {op.mb}, which the routing gives to rank {int(path[op.mb, st])}")
+            want_prev = int(path[op.mb, st - 1]) if st > 0 else -1
+            want_next = int(path[op.mb, st + 1]) if st + 1 < S_ else -1
+            if (op.prev, op.next) != (want_prev, want_next):
+                raise PlanError(f"rank {r}, microbatch {op.mb}: neighbours {(op.prev, op.next)}, routing says {(want_prev, want_next)}")
+            if op.kind == FWD:
+                inflight += 1
+                seen.add(op.mb)
+                if inflight > cap and st != S_ - 1 and not forward_only:
+                    raise PlanError(f"rank {r} holds {inflight} forwards in flight, the limit is {cap}")
+            elif op.kind == BWD:
+                if op.mb not in seen:
+                    raise PlanError(f"rank {r} runs the backward of microbatch {op.mb} before its forward")
+                inflight -= 1
+            elif st != S_ - 1:
+                raise PlanError(f"rank {r} of stage {st} has a fused forward-backward, which only the last stage runs")
+    for mb in range(M):
+        for st in range(S_):
+            kinds = sorted(o.kind for o in plans.get(int(path[mb, st]), []) if o.mb == mb)
+            want = [FWD] if forward_only else ([FWD_BWD] if st == S_ - 1 else [FWD, BWD])
+            if kinds != want:
+                raise PlanError(f"microbatch {mb} at stage {st}: operations {kinds}, expected {want}")
+    # replay on in-order channels
+    pos = {r: 0 for r in plans}
+    queues: Dict[tuple, List[int]] = {}
+    progressed = True
+    while progressed:
+        progressed = False
+        for r, ops in plans.items():
+            while pos[r] < len(ops):
+                op = ops[pos[r]]
+                need = None
+                if op.kind in (FWD, FWD_BWD) and op.prev >= 0:
+                    need = (op.prev, r, "f")
+                elif op.kind == BWD and op.next >= 0:
+                    need = (op.next, r, "b")
+                if need is not None:
+                    q = queues.get(need, [])
+                    if not q or q[0] != op.mb:
+                        break
+                    q.pop(0)
+                if op.kind == FWD and op.next >= 0:
+                    queues.setdefault((r, op.next, "f"), []).append(op.mb)
+                if op.kind in (BWD, FWD_BWD) and op.prev >= 0 and not forward_only:
+                    queues.setdefault((r, op.prev, "b"), []).append(op.mb)
+                pos[r] += 1
+                progressed = True
+    stuck = {r: ops[pos[r]] for r, ops in plans.items() if pos[r] < len(ops)}
+    if stuck:
+        r, op = next(iter(stuck.items()))
+        raise PlanError(f"deadlock: {len(stuck)} ranks cannot go on, e.g. rank {r} waits at {op}")

@@ -122,6 +122,7 @@ class Trainer:
         if self.adaptive and config.elastic.enable:
             raise NotImplementedError("adaptive routing shares its measurements over the whole world and does "
                                       "not follow membership changes; use routing = weighted with elastic runs")
+        self._verify_plans = os.environ.get("DSWARM_VERIFY_PLANS", "0") == "1"
         self.timeline = None
         if config.logging.timeline_steps > 0:
             from .utils.timeline import StepTimeline
@@ -142,6 +143,11 @@ class Trainer:
         path = schedule.route(self.routing_seed + 7919 * phase, step, w.num_stages, w.world_size,
                               self.num_micro, self.alive, mode=mode, weights=self.route_weights)
         cap = self.config.train.max_micro_batches
+        if self._verify_plans:
+            # debugging aid: every rank derives all ranks' plans and replays them before it runs its own
+            every = {r: schedule.plan(path, w.world_size, r, cap, forward_only=forward_only)
+                     for r in range(w.world_size) if self.alive is None or self.alive[r]}
+            schedule.check_plans(path, every, cap, forward_only=forward_only)
         return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
 
     def _traced(self, name: str):

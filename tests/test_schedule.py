@@ -186,3 +186,37 @@ def test_weighted_routing_follows_the_weights():
     assert max(flat.values()) / min(flat.values()) < 1.15
     assert (S.route(3, 7, stages, world, M, mode="weighted", weights=w) ==
             S.route(3, 7, stages, world, M, mode="weighted", weights=w)).all()
+
+
+def test_check_plans_accepts_real_plans_and_names_what_is_wrong_with_broken_ones():
+    import dataclasses
+    for stages, world, M, cap, mode in ((1, 2, 6, 1, "uniform"), (2, 4, 16, 3, "uniform"), (3, 9, 27, 2, "balanced"),
+                                        (4, 8, 32, 4, "uniform")):
+        path = S.route(3, 5, stages, world, M, mode=mode)
+        plans = {r: S.plan(path, world, r, cap) for r in range(world)}
+        S.check_plans(path, plans, cap)
+        fplans = {r: S.plan(path, world, r, cap, forward_only=True) for r in range(world)}
+        S.check_plans(path, fplans, cap, forward_only=True)
+    path = S.route(3, 5, 2, 4, 16)
+    good = {r: S.plan(path, 4, r, 3) for r in range(4)}
+
+    def broken(change):
+        plans = {r: list(ops) for r, ops in good.items()}
+        change(plans)
+        with pytest.raises(S.PlanError) as e:
+            S.check_plans(path, plans, 3)
+        return str(e.value)
+
+    assert "expected" in broken(lambda p: p[0].pop())                                    # a backward is missing
+    first_bwd = next(i for i, o in enumerate(good[0]) if o.kind == S.BWD)
+    assert "before its forward" in broken(lambda p: p[0].insert(0, p[0].pop(first_bwd)))
+    assert "routing" in broken(lambda p: p[0].__setitem__(0, dataclasses.replace(p[0][0], next=0)))
+    assert "limit" in broken(lambda p: p[0].sort(key=lambda o: o.kind))                  # all forwards first: over the cap
+    # two last-stage ranks each wait for a tile that its sender has queued behind the other one's
+    last = [r for r in (1, 3)]
+    def swap_first_two(p):
+        for r in last:
+            if len(p[r]) >= 2:
+                p[r][0], p[r][1] = p[r][1], p[r][0]
+    msg = broken(swap_first_two)
+    assert "deadlock" in msg or "expected" in msg
