@@ -446,6 +446,12 @@ def test_loss_curve_of_the_reference_itself(ref, tmp_path, name, nproc, stages, 
     assert len(theirs) == len(ours) == steps // H, (theirs, ours)
     assert max(abs(a - b) for a, b in zip(theirs, ours)) < 2e-4, (theirs, ours)
     assert theirs[-1] < theirs[0]
+    # the rest of the step's global record: counters exactly, the gradient norm (of the master's stage,
+    # before clipping) to rounding, which says the gradients themselves agree
+    for key, tol in (("step", 0), ("tokens", 0), ("num_micro_batches", 0), ("learning_rate", 1e-12), ("norm", 1e-4)):
+        a = _global_losses(tmp_path / "ref" / "ref" / "master.log", f"train/global/{key}/current")
+        b = _global_losses(tmp_path / "ours" / "run" / "master.log", f"train/global/{key}/current")
+        assert len(a) == len(b) == steps // H and all(abs(x - y) <= tol * max(1.0, abs(x)) for x, y in zip(a, b)), (key, a, b)
     if eval_every:
         ev_t = _global_losses(tmp_path / "ref" / "ref" / "master.log", "eval/loss/average")
         ev_o = _global_losses(tmp_path / "ours" / "run" / "master.log", "eval/loss/average")
