@@ -225,7 +225,6 @@ def run_reference(args) -> dict:
 
 
 if __name__ == "__main__":
-    import argparse
     sys.path.insert(0, os.path.dirname(HERE))
     import bench
     print(json.dumps(run_reference(bench.parse_args())))

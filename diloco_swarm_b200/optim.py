@@ -8,10 +8,9 @@ in fused kernels (ops/optim.py); this file is also their oracle.
 from __future__ import annotations
 
 import math
-from typing import Iterable, List, Optional
+from typing import Iterable, Optional
 
 import torch
-import torch.distributed as dist
 
 
 def lr_factor(step_index: int, sched, num_steps: int) -> float:

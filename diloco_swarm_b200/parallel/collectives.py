@@ -12,14 +12,13 @@ against.
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 
 from ..ops._lib import Status, check, cuda_lib, stream_ptr
-from .symm import FLAG_WORDS, LocalPeerSet, SymmetricBuffer
+from .symm import FLAG_WORDS, SymmetricBuffer
 
 
 def shard_size(n: int, R: int, align: int) -> int:

@@ -18,7 +18,7 @@ from __future__ import annotations
 import datetime
 import time
 from collections import deque
-from typing import Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Deque, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

@@ -28,7 +28,7 @@ from __future__ import annotations
 
 import datetime
 import time
-from typing import List, Optional
+from typing import List
 
 import torch.distributed as dist
 

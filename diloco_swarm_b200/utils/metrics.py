@@ -9,8 +9,8 @@ perplexity "average" is the arithmetic mean of per-update exp(loss)
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, asdict
-from typing import Callable, Dict, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
 
 
 @dataclass

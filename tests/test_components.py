@@ -324,7 +324,6 @@ def test_wandb_run_per_rank_in_offline_mode(tmp_path, monkeypatch):
     """logging.wandb.enable (src/logger.py:50-58): one run per rank, grouped by the run id, fed by
     log_config / log_world / log_metrics; wandb's offline mode stands in for the service."""
     pytest.importorskip("wandb")
-    from types import SimpleNamespace
     from diloco_swarm_b200.config import LoggingConfig
     from diloco_swarm_b200.utils.logger import Logger
     monkeypatch.setenv("WANDB_MODE", "offline")

@@ -3,12 +3,9 @@
 Each script runs with a stand-in ``python`` on PATH that records its arguments instead of training;
 what follows ``-m diloco_swarm_b200.train`` must parse into a Config with the topology, optimisers and
 batch sizes of the reference's runs (experiments/experiment{1,2,3}.sh, experiments/test.sh)."""
-import json
 import os
 import stat
 import subprocess
-
-import pytest
 
 from diloco_swarm_b200.config import config_from_argv
 
