@@ -35,7 +35,8 @@ from .utils.ckpt import Checkpoint
 from .utils.logger import Level, Logger
 from .utils.metrics import Outputs, eval_metrics, train_metrics
 from .utils.timers import PhaseTimer
-from .utils.misc import format_float, format_int, get_device, get_train_pbar_description, seed_everything
+from .utils.misc import (format_float, format_int, get_device, get_eval_pbar_description,
+                         get_train_pbar_description, seed_everything)
 from .world import World
 
 
@@ -370,12 +371,18 @@ class Trainer:
     def eval_loop(self, eval_type: str, loader: D.BatchLoader, metrics) -> Dict[str, float]:
         metrics.reset()
         limit = self.config.eval.max_steps
+        total = min(limit, len(loader)) if limit > 0 else len(loader)
+        # second progress bar on the master's terminal, as in the reference (src/train.py:147)
+        bar = tqdm(total=total, position=1, leave=False, disable=not (self.world.is_master and sys.stderr.isatty()))
         for step, batch in enumerate(loader, start=1):
             if 0 < limit < step:
                 break
             _, stage = self.eval_step(step, eval_type, batch)
             if self.world.is_master:
                 metrics.update(stage)
+                bar.set_description(get_eval_pbar_description(metrics, f"[{eval_type.upper()}]"))
+            bar.update(1)
+        bar.close()
         return metrics.compute()
 
     # ------------------------------------------------------------------
