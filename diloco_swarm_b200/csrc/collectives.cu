@@ -26,6 +26,7 @@
 // while it waits for its counterpart.
 #include "ptx.cuh"
 #include "dswarm.h"
+#include "coll_index.h"
 
 namespace dsw {
 
@@ -190,26 +191,29 @@ grad_allreduce_f32_kernel(GradArgs a) {
   if (a.use_barrier) peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok);
 }
 
+// bf16 wire.  Three phases separated by the per-block barrier; all three walk the bucket with the
+// slice-wise map of coll_index.h, so the vectors block b reads after a barrier are exactly those block b
+// of the owning replica wrote before it (a plain grid-stride over the whole bucket would not give that:
+// with slices that are not a multiple of the grid's stride, block b would read what another block of
+// the peer wrote, and nobody waits for that block).
 __global__ void __launch_bounds__(512)
 grad_allreduce_bf16_kernel(GradArgs a) {
   __shared__ int sh_ok;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
   __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(a.pt.buf[a.rank]);
-  // phase 0: own fp32 gradient -> bf16 staging (peer-visible)
+  // phase 0: own fp32 gradient -> bf16 staging (peer-visible), every slice
   if (a.phase_mask & 1) {
-    for (long long i = a.offset + 8 * tid; i < a.offset + a.count; i += 8 * nth) {
+    dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
       const float4 x = ld_f4(a.grad + i), y = ld_f4(a.grad + i + 4);
       *reinterpret_cast<uint4*>(stage + i) =
           make_uint4(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w), pack_bf16(y.x, y.y), pack_bf16(y.z, y.w));
-    }
+    });
   }
   if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq, a.wait_limit, a.status, &sh_ok)) return;
   // phase 1: reduce my slice over all peers in fp32, scale, send back as bf16
   if (a.phase_mask & 2) {
-    const long long lo = a.offset + (long long)a.rank * a.shard;
-    const long long hi = min(a.offset + a.count, lo + a.shard);
-    for (long long i = lo + 8 * tid; i < hi; i += 8 * nth) {
+    dsw_for_each_owned(a.offset, a.count, a.shard, a.rank, a.rank + 1, tid, nth, 8, [&](long long i) {
       float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int j = 0; j < MAX_PEERS; ++j) {
@@ -225,17 +229,17 @@ grad_allreduce_bf16_kernel(GradArgs a) {
 #pragma unroll
       for (int j = 0; j < MAX_PEERS; ++j)
         if (j < a.R) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.pt.buf[j]) + i) = o;
-    }
+    });
   }
   if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok)) return;
-  // phase 2: widen the averaged bucket into the fp32 main gradient
+  // phase 2: widen the averaged bucket into the fp32 main gradient, every slice
   if (a.phase_mask & 4) {
-    for (long long i = a.offset + 8 * tid; i < a.offset + a.count; i += 8 * nth) {
+    dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
       const uint4 u = *reinterpret_cast<const uint4*>(stage + i);
       const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
       st_f4(a.grad + i, make_float4(f0.x, f0.y, f1.x, f1.y));
       st_f4(a.grad + i + 4, make_float4(f2.x, f2.y, f3.x, f3.y));
-    }
+    });
   }
 }
 

@@ -29,7 +29,13 @@ __device__ __forceinline__ long long gemm_gtimer() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// In-kernel timeline stamps exist only in the tracing build of the library (-DDSWARM_TRACE, used by
+// benchmarks/timelines.py); the shipped kernels carry none of it.
+#ifdef DSWARM_TRACE
 #define GEMM_TRACE(buf, slot) do { if ((buf) != nullptr && (slot) < 512) (buf)[(slot)++] = gemm_gtimer(); } while (0)
+#else
+#define GEMM_TRACE(buf, slot) do { } while (0)
+#endif
 
 constexpr int BM = 128;
 constexpr int BK = 64;          // one 128-byte swizzle row of bf16
@@ -59,215 +65,174 @@ struct GemmArgs {
   long long* trace;     // optional: CTA 0's MMA thread stores %globaltimer stamps per k-block (tuning aid)
 };
 
-// Epilogue for one row and 32 consecutive columns of the accumulator.
-__device__ __forceinline__ void epilogue_store(const GemmArgs& g, int row, int col0, float (&v)[32]) {
-    if (g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32) {
-      float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col0;
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        if (col0 + i < g.N) {
-          if (g.mode == EPI_ATOMIC_F32) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + i), "f"(v[i]), "f"(v[i + 1]),
-                         "f"(v[i + 2]), "f"(v[i + 3])
-                         : "memory");
-          } else {
-            *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-          }
-        }
-      }
-      return;
-    }
-    if (g.bias) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        if (col0 + i < g.N) {
-          const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
-          v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
-        }
-      }
-    }
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-      if (col0 + i >= g.N) break;
-      float* w = v + i;
-      if (g.mode == EPI_GELU) {
-        uint4 pre = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]),
-                               pack_bf16(w[6], w[7]));
-        *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col0 + i) = pre;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w[j] = gelu_erf(w[j]);
-      } else if (g.mode == EPI_RESID) {
-        const uint4 rr = *reinterpret_cast<const uint4*>(g.resid + (long long)row * g.ldr + col0 + i);
-        const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16(ru[j]);
-          w[2 * j] += f.x; w[2 * j + 1] += f.y;
-        }
-      } else if (g.mode == EPI_DGELU) {
-        const uint4 rr = *reinterpret_cast<const uint4*>(g.aux_in + (long long)row * g.ldaux + col0 + i);
-        const uint32_t ru[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16(ru[j]);
-          w[2 * j] *= gelu_erf_grad(f.x); w[2 * j + 1] *= gelu_erf_grad(f.y);
-        }
-      }
-      *reinterpret_cast<uint4*>(o + i) = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]),
-                                                    pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
-    }
-}
-
-// Drain NCH chunks of 32 accumulator columns for one row per thread.  The TMEM load of
-// chunk c+1 is in flight while chunk c is converted and stored.  `release` is called once,
-// right after the last load has landed, so the accumulator can be reused while the final
-// chunk is still being written out.
-template <int NCH, class Release>
-__device__ __forceinline__ void drain_accumulator(const GemmArgs& g, uint32_t t_addr, int row, bool row_ok, int col_base,
-                                                  bool has_k, Release release, long long* etr = nullptr,
-                                                  int* eslot = nullptr) {
-  uint32_t r[2][32];
-  tmem_ld_32x32(t_addr, r[0]);
-  tmem_ld_wait();
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    if (etr) GEMM_TRACE(etr, *eslot);
-    if (c + 1 < NCH) tmem_ld_32x32(t_addr + (c + 1) * 32, r[(c + 1) & 1]);
-    else release();
-    const int col0 = col_base + c * 32;
-    if (row_ok && col0 < g.N && has_k) {
-      float v[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[c & 1][i]);
-      epilogue_store(g, row, col0, v);
-    }
-    if (c + 1 < NCH) tmem_ld_wait();
-  }
-}
-
-// Staged epilogue.  A thread owns one accumulator row (that is how tcgen05.ld hands the data out),
-// but a store in which every lane writes 16 bytes of a different row touches 32 cache lines per
-// instruction.  So each warp passes its 32 x 128-byte slab through a private 4 KB tile of shared
-// memory (16-byte chunks XOR-swizzled by row, conflict-free both ways) and writes it out with
-// lane = (row within a group of 4, 16-byte chunk): every store, residual/aux load or fp32
+// ------------------------------------------------------------------ epilogue
+// A thread owns one accumulator row (that is how tcgen05.ld hands the data out), but a store in
+// which every lane writes 16 bytes of a different row touches 32 cache lines per instruction.  So
+// each warp passes its 32-row slab through a private 4 KB tile of shared memory (32 rows x 128
+// bytes, 16-byte chunks XOR-swizzled by row, conflict-free both ways) and writes it out with
+// lane = (row within a group of 4, 16-byte chunk): every store, residual / aux load or fp32
 // reduction instruction then covers 4 rows x 128 contiguous bytes.
+//
+// The accumulator is drained in chunks of 32 columns with the tcgen05.ld of chunk c+1 in flight
+// while chunk c is converted, so a thread holds 64 accumulator registers at most.  Two chunks fill
+// one bf16 slab (64 columns = 128 bytes per row); an fp32 chunk is a slab by itself.  Everything
+// the slab needs from global memory besides the accumulator (bias, residual, GELU pre-activation)
+// is requested at the top of the slab, before the wait for the accumulator, in one batch: issued
+// one by one between the stores of the write-out, each load would cost a full memory round trip.
 constexpr int EPI_STAGE_BYTES = 32 * 128;
 
-__device__ __forceinline__ void stage_row(uint8_t* stage, int lane, const uint32_t (&w)[32]) {
+// columns [16*q, 16*q + 16) of a 64-column bf16 slab (q = 0..3 -> 16-byte chunks 2q, 2q+1) ...
+// generic form: `w` holds NW 32-bit words of this thread's row, starting at 16-byte chunk `c0`.
+template <int NW>
+__device__ __forceinline__ void stage_words(uint8_t* stage, int lane, int c0, const uint32_t (&w)[NW]) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+  for (int c = 0; c < NW / 4; ++c)
+    *reinterpret_cast<uint4*>(stage + lane * 128 + (((c0 + c) ^ (lane & 7)) << 4)) =
         make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 
-// Write one staged slab: rows row_base..+31, `elems` columns of `esize` bytes starting at col0.
+// Visit the staged slab in write-out order: iteration i, this lane handles row i*4 + (lane >> 3),
+// 16-byte chunk lane & 7.
 template <class F>
 __device__ __forceinline__ void unstage_rows(const uint8_t* stage, int lane, F&& emit) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int rl = i * 4 + (lane >> 3), ch = lane & 7;
     const uint4 d = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((ch ^ (rl & 7)) << 4));
-    emit(rl, ch, d);
+    emit(i, rl, ch, d);
   }
 }
 
-template <int NCOLS, class Release>
-__device__ __forceinline__ void drain_accumulator_staged(const GemmArgs& g, uint32_t t_addr, int row_base, int lane,
-                                                         int col_base, bool has_k, uint8_t* stage, Release release) {
-  const bool f32 = g.mode == EPI_ATOMIC_F32 || g.mode == EPI_STORE_F32;
+// NCOLS accumulator columns (a multiple of 64) starting at TMEM address t_addr, rows row_base..+31
+// (one per lane), output columns col_base..+NCOLS-1.  `release` is called once, right after the last
+// TMEM load has landed, so the MMA thread can refill the accumulator while the last slab is written.
+template <int MODE, int NCOLS, class Release>
+__device__ __forceinline__ void epilogue_warp(const GemmArgs& g, uint32_t t_addr, int row_base, int lane, int col_base,
+                                              uint8_t* stage, Release&& release) {
+  constexpr bool F32 = MODE == EPI_ATOMIC_F32 || MODE == EPI_STORE_F32;
   constexpr int NCH = NCOLS / 32;
   uint32_t r[2][32];
   tmem_ld_32x32(t_addr, r[0]);
-  if (NCH > 1) tmem_ld_32x32(t_addr + 32, r[1]);
-  tmem_ld_wait();
+  if constexpr (F32) {
 #pragma unroll
-  for (int c = 0; c < NCH; c += 2) {
-    // r[0], r[1] hold columns [c*32, c*32+64) of this thread's row
-    float v[64];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) { v[i] = __uint_as_float(r[0][i]); v[32 + i] = __uint_as_float(r[1][i]); }
-    if (c + 2 < NCH) {                       // next 64 columns: in flight while this slab is written out
-      tmem_ld_32x32(t_addr + (c + 2) * 32, r[0]);
-      tmem_ld_32x32(t_addr + (c + 3) * 32, r[1]);
-    } else {
-      release();
+    for (int c = 0; c < NCH; ++c) {
+      tmem_ld_wait();
+      if (c + 1 < NCH) tmem_ld_32x32(t_addr + (c + 1) * 32, r[(c + 1) & 1]);
+      else release();
+      const int cb = col_base + c * 32;
+      if (cb >= g.N) continue;
+      __syncwarp();                                   // the previous slab has been read out
+      stage_words<32>(stage, lane, 0, r[c & 1]);
+      __syncwarp();
+      unstage_rows(stage, lane, [&](int, int rl, int ch, const uint4& d) {
+        const int row = row_base + rl, col = cb + ch * 4;
+        if (row < g.M && col < g.N) {
+          float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col;
+          if (MODE == EPI_ATOMIC_F32)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(__uint_as_float(d.x)),
+                         "f"(__uint_as_float(d.y)), "f"(__uint_as_float(d.z)), "f"(__uint_as_float(d.w))
+                         : "memory");
+          else
+            *reinterpret_cast<uint4*>(o) = d;
+        }
+      });
     }
-    const int col0 = col_base + c * 32;
-    if (has_k && col0 < g.N) {
-      if (f32) {
+  } else {
+    constexpr int NSLAB = NCOLS / 64;
+    constexpr bool EXTRA = MODE == EPI_RESID || MODE == EPI_DGELU;
+    const int my_ch = lane & 7, my_r = lane >> 3;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {      // fp32: 32 columns fill a 128-byte row
-          uint32_t w[32];
+    for (int s = 0; s < NSLAB; ++s) {
+      const int col0 = col_base + s * 64;
+      const bool slab_ok = col0 < g.N;
+      // ---- requests to global memory for this slab, all at once
+      uint4 x[EXTRA ? 8 : 1];
+      if constexpr (EXTRA) {
+        const __nv_bfloat16* src = MODE == EPI_RESID ? g.resid : g.aux_in;
+        const long long ld = MODE == EPI_RESID ? g.ldr : g.ldaux;
+        const int col = col0 + my_ch * 8;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(v[hh * 32 + i]);
-          __syncwarp();
-          stage_row(stage, lane, w);
-          __syncwarp();
-          const int cb = col0 + hh * 32;
-          unstage_rows(stage, lane, [&](int rl, int ch, const uint4& d) {
-            const int row = row_base + rl, col = cb + ch * 4;
-            if (row < g.M && col < g.N) {
-              float* o = reinterpret_cast<float*>(g.out) + (long long)row * g.ldo + col;
-              if (g.mode == EPI_ATOMIC_F32)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(__uint_as_float(d.x)),
-                             "f"(__uint_as_float(d.y)), "f"(__uint_as_float(d.z)), "f"(__uint_as_float(d.w))
-                             : "memory");
-              else
-                *reinterpret_cast<uint4*>(o) = d;
-            }
-          });
+        for (int i = 0; i < 8; ++i) {
+          const int row = row_base + i * 4 + my_r;
+          x[i] = (row < g.M && col < g.N) ? __ldg(reinterpret_cast<const uint4*>(src + (long long)row * ld + col))
+                                          : make_uint4(0, 0, 0, 0);
         }
-      } else {
-        if (g.bias) {
-#pragma unroll
-          for (int i = 0; i < 64; i += 4) {
-            if (col0 + i < g.N) {
-              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + i));
-              v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
-            }
-          }
-        }
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-        __syncwarp();
-        stage_row(stage, lane, w);
-        __syncwarp();
-        if (g.mode == EPI_GELU) {
-          // pre-activation goes out first, then the slab is re-staged with the activation
-          unstage_rows(stage, lane, [&](int rl, int ch, const uint4& d) {
-            const int row = row_base + rl, col = col0 + ch * 8;
-            if (row < g.M && col < g.N) *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col) = d;
-          });
-#pragma unroll
-          for (int i = 0; i < 32; ++i) w[i] = pack_bf16(gelu_erf(v[2 * i]), gelu_erf(v[2 * i + 1]));
-          __syncwarp();
-          stage_row(stage, lane, w);
-          __syncwarp();
-        }
-        unstage_rows(stage, lane, [&](int rl, int ch, uint4 d) {
-          const int row = row_base + rl, col = col0 + ch * 8;
-          if (row >= g.M || col >= g.N) return;
-          if (g.mode == EPI_RESID || g.mode == EPI_DGELU) {
-            const __nv_bfloat16* src = g.mode == EPI_RESID ? g.resid + (long long)row * g.ldr + col
-                                                           : g.aux_in + (long long)row * g.ldaux + col;
-            const uint4 x = *reinterpret_cast<const uint4*>(src);
-            uint32_t du[4] = {d.x, d.y, d.z, d.w};
-            const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float2 a = unpack_bf16(du[q]), b = unpack_bf16(xu[q]);
-              du[q] = g.mode == EPI_RESID ? pack_bf16(a.x + b.x, a.y + b.y)
-                                          : pack_bf16(a.x * gelu_erf_grad(b.x), a.y * gelu_erf_grad(b.y));
-            }
-            d = make_uint4(du[0], du[1], du[2], du[3]);
-          }
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col) = d;
-        });
       }
+      uint32_t post[MODE == EPI_GELU ? 32 : 1];      // gelu(acc + bias) of the slab, packed, until the pre-activation is out
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = 2 * s + h;
+        const int cb = col0 + h * 32;
+        tmem_ld_wait();
+        if (c + 1 < NCH) tmem_ld_32x32(t_addr + (c + 1) * 32, r[(c + 1) & 1]);
+        else release();
+        if (!slab_ok) continue;
+        // bias (an L1 hit after the first tile row), add, round; the GELU value is formed from the same
+        // fp32 sum and parked in registers until the pre-activation slab has been written out
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 bb = (g.bias != nullptr && cb + 4 * i < g.N) ? __ldg(reinterpret_cast<const float4*>(g.bias + cb) + i)
+                                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float v0 = __uint_as_float(r[c & 1][4 * i]) + bb.x, v1 = __uint_as_float(r[c & 1][4 * i + 1]) + bb.y;
+          const float v2 = __uint_as_float(r[c & 1][4 * i + 2]) + bb.z, v3 = __uint_as_float(r[c & 1][4 * i + 3]) + bb.w;
+          w[2 * i] = pack_bf16(v0, v1);
+          w[2 * i + 1] = pack_bf16(v2, v3);
+          if constexpr (MODE == EPI_GELU) {
+            post[16 * h + 2 * i] = pack_bf16(gelu_fast(v0), gelu_fast(v1));
+            post[16 * h + 2 * i + 1] = pack_bf16(gelu_fast(v2), gelu_fast(v3));
+          }
+        }
+        if (h == 0) __syncwarp();                     // the previous slab has been read out
+        stage_words<16>(stage, lane, 4 * h, w);
+      }
+      if (!slab_ok) continue;
+      __syncwarp();
+      if constexpr (MODE == EPI_GELU) {
+        unstage_rows(stage, lane, [&](int, int rl, int ch, const uint4& d) {
+          const int row = row_base + rl, col = col0 + ch * 8;
+          if (row < g.M && col < g.N) *reinterpret_cast<uint4*>(g.aux_out + (long long)row * g.ldaux + col) = d;
+        });
+        __syncwarp();
+        uint32_t w0[16], w1[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { w0[i] = post[i]; w1[i] = post[16 + i]; }
+        stage_words<16>(stage, lane, 0, w0);
+        stage_words<16>(stage, lane, 4, w1);
+        __syncwarp();
+      }
+      unstage_rows(stage, lane, [&](int i, int rl, int ch, uint4 d) {
+        const int row = row_base + rl, col = col0 + ch * 8;
+        if (row >= g.M || col >= g.N) return;
+        if constexpr (EXTRA) {
+          uint32_t du[4] = {d.x, d.y, d.z, d.w};
+          const uint32_t xu[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 a = unpack_bf16(du[q]), e = unpack_bf16(xu[q]);
+            du[q] = MODE == EPI_RESID ? pack_bf16(a.x + e.x, a.y + e.y)
+                                      : pack_bf16(a.x * gelu_grad_fast(e.x), a.y * gelu_grad_fast(e.y));
+          }
+          d = make_uint4(du[0], du[1], du[2], du[3]);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.out) + (long long)row * g.ldo + col) = d;
+      });
     }
-    if (c + 2 < NCH) tmem_ld_wait();
+  }
+}
+
+// One tile's worth of epilogue for this warp, dispatched on the mode once per tile.
+template <int NCOLS, class Release>
+__device__ __forceinline__ void drain_tile(const GemmArgs& g, uint32_t t_addr, int row_base, int lane, int col_base,
+                                           bool has_k, uint8_t* stage, Release&& release) {
+  if (!has_k) { release(); return; }
+  switch (g.mode) {
+    case EPI_GELU: epilogue_warp<EPI_GELU, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
+    case EPI_RESID: epilogue_warp<EPI_RESID, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
+    case EPI_DGELU: epilogue_warp<EPI_DGELU, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
+    case EPI_ATOMIC_F32: epilogue_warp<EPI_ATOMIC_F32, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
+    case EPI_STORE_F32: epilogue_warp<EPI_STORE_F32, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
+    default: epilogue_warp<EPI_STORE, NCOLS>(g, t_addr, row_base, lane, col_base, stage, release); break;
   }
 }
 
@@ -429,7 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
-      drain_accumulator_staged<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
+      drain_tile<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
                                        smem + L::EPI_OFFSET + (warp - 2) * EPI_STAGE_BYTES, [&] {
         tmem_ld_wait();
         tc_fence_before();
@@ -630,7 +595,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ab * BN + half * (BN / 2) + (uint32_t(q * 32) << 16);
-      drain_accumulator_staged<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
+      drain_tile<BN / 2>(g, t_addr, m0 + q * 32, lane, n0 + half * (BN / 2), has_k,
                                        smem + L::EPI_OFFSET + (warp - 2) * EPI_STAGE_BYTES, [&] {
         tmem_ld_wait();
         tc_fence_before();

@@ -43,7 +43,7 @@ def cuda_sources() -> List[str]:
 
 def build_host(force: bool = False, verbose: bool = False) -> str:
     srcs = host_sources()
-    if not force and _newer(HOST_LIB, srcs + [os.path.join(CSRC, "dswarm_host.h")]):
+    if not force and _newer(HOST_LIB, srcs + [os.path.join(CSRC, "dswarm_host.h"), os.path.join(CSRC, "coll_index.h")]):
         return HOST_LIB
     cxx = shutil.which("g++") or shutil.which("c++")
     if cxx is None:

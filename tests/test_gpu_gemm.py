@@ -88,6 +88,68 @@ def test_gemm_epilogues():
     _close(out32, a.float() @ b.float().t(), "fp32 store")
 
 
+@pytest.mark.parametrize("M,N,K", [(200, 264, 200), (129, 136, 72), (640, 1032, 136)])
+@pytest.mark.parametrize("bn", [128, 256, 512])
+def test_gemm_epilogues_tail_shapes(M, N, K, bn):
+    """Every fused epilogue on shapes whose last row and column tiles are partial, at every tile width."""
+    from diloco_swarm_b200.ops import kernels as Kn
+    from diloco_swarm_b200.ops._lib import Status
+    st = Status(torch.device("cuda"))
+    a, b = _mk((M, K), seed=21), _mk((N, K), 0.05, seed=22)
+    bias = torch.randn(N, device="cuda")
+    acc = a.float() @ b.float().t()
+    guard = 7.0          # rows past M / columns past N of padded outputs must stay untouched
+    def padded(dtype=torch.bfloat16):
+        return torch.full((M + 8, N + 8), guard, dtype=dtype, device="cuda")
+    def check_guard(t, what):
+        assert bool((t[M:, :] == guard).all()) and bool((t[:, N:] == guard).all()), f"{what}: wrote outside the matrix"
+    o = padded()
+    Kn.gemm(a, b, bias=bias, out=o[:M, :N], bn=bn, status=st)
+    _close(o[:M, :N], acc + bias, "bias"); check_guard(o, "bias")
+    o, pre = padded(), padded()
+    Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias, aux_out=pre[:M, :N], out=o[:M, :N], bn=bn, status=st)
+    _close(pre[:M, :N], acc + bias, "pre-activation"); check_guard(pre, "pre-activation")
+    _close(o[:M, :N], torch.nn.functional.gelu(acc + bias), "gelu"); check_guard(o, "gelu")
+    res = _mk((M, N), seed=23)
+    o = padded()
+    Kn.gemm(a, b, mode=Kn.EPI_RESID, bias=bias, resid=res, out=o[:M, :N], bn=bn, status=st)
+    _close(o[:M, :N], acc + bias + res.float(), "residual"); check_guard(o, "residual")
+    aux = _mk((M, N), 2.0, seed=24)
+    x = aux.float().requires_grad_(True)
+    torch.nn.functional.gelu(x).sum().backward()
+    o = padded()
+    Kn.gemm(a, b, mode=Kn.EPI_DGELU, aux_in=aux, out=o[:M, :N], bn=bn, status=st)
+    _close(o[:M, :N], acc * x.grad, "gelu backward"); check_guard(o, "gelu backward")
+    o32 = padded(torch.float32)
+    Kn.gemm(a, b, mode=Kn.EPI_STORE_F32, out=o32[:M, :N], bn=bn, status=st)
+    _close(o32[:M, :N], acc, "fp32 store"); check_guard(o32, "fp32 store")
+    torch.cuda.synchronize()
+    st.raise_if_set()
+
+
+def test_fast_gelu_matches_erf_form():
+    """The epilogues' erf approximation against torch's exact GELU and its derivative over the whole
+    range that matters, including the tails: the difference must be far below bf16 resolution."""
+    from diloco_swarm_b200.ops import kernels as Kn
+    n = 1 << 14
+    xs = torch.linspace(-12.0, 12.0, n, device="cuda")
+    # a GEMM whose accumulator is exactly x: one non-zero column of A (x, bf16) times ones
+    xb = xs.to(torch.bfloat16)
+    a = torch.zeros(n, 8, dtype=torch.bfloat16, device="cuda"); a[:, 0] = xb
+    b = torch.zeros(8, 8, dtype=torch.bfloat16, device="cuda"); b[:, 0] = 1.0      # every output column = x
+    pre = torch.empty(n, 8, dtype=torch.bfloat16, device="cuda")
+    g = Kn.gemm(a, b, mode=Kn.EPI_GELU, aux_out=pre)
+    ref = torch.nn.functional.gelu(xb.float())
+    assert torch.allclose(g[:, 0].float(), ref, atol=1e-6, rtol=2 ** -7)
+    assert torch.equal(pre[:, 0], xb)
+    x = xb.float().requires_grad_(True)
+    torch.nn.functional.gelu(x).sum().backward()
+    ones = torch.zeros(n, 8, dtype=torch.bfloat16, device="cuda"); ones[:, 0] = 1.0
+    aux = xb.unsqueeze(1).repeat(1, 8).contiguous()
+    dg = Kn.gemm(ones, b, mode=Kn.EPI_DGELU, aux_in=aux)              # 1 * gelu'(x)
+    assert torch.allclose(dg[:, 0].float(), x.grad, atol=1e-6, rtol=2 ** -7)
+
+
 def test_gemm_persistent_many_tiles():
     """More tiles than SMs, so CTAs loop over tiles and both accumulators are reused."""
     from diloco_swarm_b200.ops import kernels as Kn
