@@ -4,7 +4,7 @@
 
 ``kernel_cases --case gemm`` times the plain-store epilogue; inside a training
 step most GEMMs carry fused work (bias, exact GELU with a second output,
-residual add, GELU-derivative multiply, fp32 accumulation into the main
+residual add, multiply by the saved GELU derivative, fp32 accumulation into the main
 gradient under split-K).  This tool times each call exactly as
 ``models/engine_b200.py`` issues it (same operand layouts, same tile choice,
 same split) and, beside it, ``torch.matmul`` on the same operands: the library
@@ -35,11 +35,11 @@ def cases(M: int, d: int, V: int):
         ("qkv fwd (bias)", (M, 3 * d, d), lambda: K.gemm(x_d, w_qkv, bias=b_3d), lambda: x_d @ w_qkv.t()),
         ("out-proj fwd (bias+resid)", (M, d, d), lambda: K.gemm(x_d, w_o, mode=K.EPI_RESID, bias=b_d, resid=x_d),
          lambda: x_d @ w_o.t()),
-        ("fc fwd (bias+gelu, 2 outputs)", (M, 4 * d, d),
+        ("fc fwd (bias+gelu, gelu' saved)", (M, 4 * d, d),
          lambda: K.gemm(x_d, w_fc, mode=K.EPI_GELU, bias=b_4d, aux_out=h), lambda: x_d @ w_fc.t()),
         ("proj fwd (bias+resid)", (M, d, 4 * d), lambda: K.gemm(x_4d, w_pr, mode=K.EPI_RESID, bias=b_d, resid=x_d),
          lambda: x_4d @ w_pr.t()),
-        ("proj dgrad (dgelu)", (M, 4 * d, d), lambda: K.gemm(x_d, w_pr, b_t=False, mode=K.EPI_DGELU, aux_in=h),
+        ("proj dgrad (x saved gelu')", (M, 4 * d, d), lambda: K.gemm(x_d, w_pr, b_t=False, mode=K.EPI_MUL, aux_in=h),
          lambda: x_d @ w_pr),
         ("fc dgrad", (M, d, 4 * d), lambda: K.gemm(x_4d, w_fc, b_t=False), lambda: x_4d @ w_fc),
         ("out-proj dgrad", (M, d, d), lambda: K.gemm(x_d, w_o, b_t=False), lambda: x_d @ w_o),

@@ -23,7 +23,7 @@ os.environ["DSWARM_WGRAD_STREAM"] = "0"
 
 import torch  # noqa: E402
 
-MODES = {0: "store", 1: "gelu", 2: "resid", 3: "dgelu", 4: "atomic_f32", 5: "store_f32"}
+MODES = {0: "store", 1: "gelu", 2: "resid", 3: "mul", 4: "atomic_f32", 5: "store_f32"}
 
 
 def main():

@@ -15,7 +15,11 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import os
 import statistics
+
+# the stamps are compiled into the tracing build of the library only (ops/_build.py: variant "trace")
+os.environ.setdefault("DSWARM_LIB_VARIANT", "trace")
 
 import torch
 
@@ -35,33 +39,47 @@ def _setter(name):
     return fn
 
 
-def gemm_timeline(M, N, Kd, bn=256, ksub=2):
+def gemm_timeline(M, N, Kd, bn=256, mode="store"):
     set_trace = _setter("dsw_gemm_set_trace")
-    if bn == 512:
-        set_ksub = cuda_lib().dsw_gemm_set_pair_ksub
-        set_ksub.argtypes, set_ksub.restype = [ctypes.c_int], ctypes.c_int
-        set_ksub(ksub)
     a, b = _bf(M, Kd), _bf(N, Kd)
+    bias = torch.randn(N, device="cuda")
+    extra = _bf(M, N)
+    call = {"store": lambda: K.gemm(a, b, bn=bn),
+            "bias": lambda: K.gemm(a, b, bn=bn, bias=bias),
+            "gelu": lambda: K.gemm(a, b, bn=bn, bias=bias, mode=K.EPI_GELU, aux_out=extra),
+            "resid": lambda: K.gemm(a, b, bn=bn, bias=bias, mode=K.EPI_RESID, resid=extra),
+            "mul": lambda: K.gemm(a, b, bn=bn, mode=K.EPI_MUL, aux_in=extra)}[mode]
     for _ in range(3):
-        K.gemm(a, b, bn=bn)
+        call()
     torch.cuda.synchronize()
     tr = torch.zeros(512, dtype=torch.int64, device="cuda")
     set_trace(tr.data_ptr())
-    K.gemm(a, b, bn=bn)
+    call()
     torch.cuda.synchronize()
     set_trace(None)
-    t = [x for x in tr.cpu().tolist() if x]
+    raw = tr.cpu().tolist()
+    t = [x for x in raw[:256] if x]
     waits = [t[i + 1] - t[i] for i in range(0, len(t) - 3, 4)]
     mmas = [t[i + 2] - t[i + 1] for i in range(0, len(t) - 3, 4)]
     commits = [t[i + 3] - t[i + 2] for i in range(0, len(t) - 3, 4)]
     period = [t[i + 4] - t[i] for i in range(0, len(t) - 4, 4)]
-    kind = f"CTA-pair kernel, {ksub} k-block(s) per barrier" if bn == 512 else f"one-CTA kernel, bn={bn}"
-    n_mma = 4 * ksub if bn == 512 else 4
-    print(f"gemm {M}x{N}x{Kd} ({kind}): {len(waits)} barrier periods of CTA 0")
+    kind = "CTA-pair kernel, 2 k-blocks per barrier" if bn == 512 else f"one-CTA kernel, bn={bn}"
+    n_mma = 8 if bn == 512 else 4
+    print(f"gemm {M}x{N}x{Kd} {mode} ({kind}): {len(waits)} barrier periods of CTA 0")
     for name, v in (("full-barrier wait", waits), (f"{n_mma} x tcgen05.mma", mmas), ("tcgen05.commit", commits),
                     ("period", period)):
         print(f"  {name:18s} median {statistics.median(v):6.0f} ns   mean {statistics.mean(v):7.1f} ns   max {max(v)} ns")
     print("  first periods:", period[:28])
+    # CTA-pair kernel: the first epilogue warp's stamps per tile (start of the wait for the accumulator, got
+    # it, tile written out)
+    e = [x for x in raw[256:] if x]
+    if len(e) >= 3:
+        t0 = e[0]
+        tiles = [(e[i] - t0, e[i + 1] - e[i], e[i + 2] - e[i + 1]) for i in range(0, len(e) - 2, 3)]
+        print("  epilogue warp, per tile (start ns, wait for accumulator ns, drain + write-out ns):")
+        print("   ", tiles[:16])
+        print(f"  drain median {statistics.median(x[2] for x in tiles):.0f} ns, accumulator wait median "
+              f"{statistics.median(x[1] for x in tiles):.0f} ns, tiles {len(tiles)}, span {e[-1] - t0} ns")
 
 
 def attention_timeline(B, T, nh):
@@ -104,13 +122,13 @@ def main():
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=768)
     ap.add_argument("--bn", type=int, default=256, choices=[128, 256, 512], help="512 = the CTA-pair kernel")
-    ap.add_argument("--ksub", type=int, default=2, choices=[1, 2], help="CTA-pair kernel: k-blocks per barrier pair")
+    ap.add_argument("--mode", default="store", choices=["store", "bias", "gelu", "resid", "mul"], help="GEMM epilogue")
     ap.add_argument("--B", type=int, default=16)
     ap.add_argument("--T", type=int, default=1024)
     ap.add_argument("--heads", type=int, default=12)
     a = ap.parse_args()
     if a.kernel == "gemm":
-        gemm_timeline(a.M, a.N, a.K, a.bn, a.ksub)
+        gemm_timeline(a.M, a.N, a.K, a.bn, a.mode)
     else:
         attention_timeline(a.B, a.T, a.heads)
 

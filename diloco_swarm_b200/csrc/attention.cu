@@ -51,7 +51,12 @@ __device__ __forceinline__ long long gtimer() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// In-kernel timeline stamps exist only in the tracing build (-DDSWARM_TRACE, benchmarks/timelines.py).
+#ifdef DSWARM_TRACE
 #define ATT_TRACE(buf, base, slot) do { if ((buf) != nullptr && (slot) < 256) (buf)[(base) + (slot)++] = gtimer(); } while (0)
+#else
+#define ATT_TRACE(buf, base, slot) do { } while (0)
+#endif
 
 constexpr int ATT_BQ = 128;        // query rows per work item
 constexpr int ATT_BK = 128;        // kv rows per step

@@ -23,9 +23,9 @@
 
 // Epilogue modes of dsw_gemm_bf16.
 #define DSW_EPI_STORE 0       // out(bf16) = acc (+ bias)
-#define DSW_EPI_GELU 1        // aux_out(bf16) = acc + bias ; out(bf16) = gelu(aux_out), exact erf form
+#define DSW_EPI_GELU 1        // out(bf16) = gelu(acc + bias), exact erf form; aux_out (bf16, optional) = gelu'(acc + bias)
 #define DSW_EPI_RESID 2       // out(bf16) = acc + bias + resid
-#define DSW_EPI_DGELU 3       // out(bf16) = acc * gelu'(aux_in)
+#define DSW_EPI_MUL 3         // out(bf16) = acc * aux_in (with the aux_out of DSW_EPI_GELU: the GELU backward)
 #define DSW_EPI_ATOMIC_F32 4  // out(fp32) += acc, safe under split-K
 #define DSW_EPI_STORE_F32 5   // out(fp32) = acc
 
@@ -43,9 +43,8 @@ int dsw_gemm_bf16(const void* A, long long lda, int a_mn_major, const void* B, l
                   int M, int N, int K, int mode, int split_k, void* out, long long ldo, const float* bias,
                   const void* resid, long long ldr, void* aux_out, const void* aux_in, long long ldaux, int bn,
                   int max_ctas, int* status, cudaStream_t stream);
-// k-blocks per barrier pair in the CTA-pair kernel (1 or 2).
-int dsw_gemm_set_pair_ksub(int ksub);
-// Device buffer of 512 int64 that receives the MMA thread's timeline (null switches it off).
+// Tracing build of the library only (-DDSWARM_TRACE): device buffer of 512 int64 that receives the timeline
+// stamps of CTA 0's MMA thread and first epilogue warp (null switches it off).  A no-op in the shipped build.
 int dsw_gemm_set_trace(long long* buf);
 
 // ---------------------------------------------------------------- attention (attention.cu)

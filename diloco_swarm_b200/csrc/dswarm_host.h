@@ -33,9 +33,9 @@ int dsw_plan(int S, int world, int M, int cap, const int32_t* path, const float*
 
 // Thread-to-element map of the fused collectives (coll_index.h), for tests: out[v] = block that touches
 // vector v of the bucket in `phase` (0 cast-in, 1 reduce, 2 widen-out) on replica `rank`, -1 if none.
-// Returns the number of vectors touched, -1 on bad arguments.
-long long dsw_coll_touch_map(long long offset, long long count, long long shard, int R, int rank, int phase,
-                             int grid, int block, int vec, int32_t* out);
+// Returns 0, or -1 on bad arguments.
+int dsw_coll_touch_map(long long offset, long long count, long long shard, int R, int rank, int phase, int grid,
+                       int block, int vec, int32_t* out);
 
 #ifdef __cplusplus
 }

@@ -296,32 +296,85 @@ __device__ __forceinline__ float gelu_erf_grad(float x) {
   const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
   return cdf + x * pdf;
 }
-// The same two functions for the GEMM epilogues, where a tile's worth of them has to fit under the
-// next tile's main loop: erf by Abramowitz & Stegun 7.1.26 (absolute error below 1.5e-7, two
-// special-function-unit operations: a reciprocal and an exponential that is shared with the
-// density term), about 16 instructions instead of erff's 40.  The error is three orders of
-// magnitude below the resolution of the bf16 values these feed.
-__device__ __forceinline__ void gelu_cdf_pdf(float x, float& cdf, float& pdf) {
-  const float a = fabsf(x) * 0.70710678118654752f;
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, a, 1.0f));
-  float p = fmaf(t, 1.061405429f, -1.453152027f);
-  p = fmaf(t, p, 1.421413741f);
-  p = fmaf(t, p, -0.284496736f);
-  p = fmaf(t, p, 0.254829592f);
-  const float e = exp2f(-1.4426950408889634f * a * a);       // exp(-x^2 / 2)
-  const float half_erfc = 0.5f * p * t * e;                  // 0.5 * erfc(|x| / sqrt 2)
-  cdf = x >= 0.f ? 1.0f - half_erfc : half_erfc;
-  pdf = 0.3989422804014327f * e;
+// Packed fp32 pairs (one instruction works on two floats held in a 64-bit register pair).
+struct f2 { unsigned long long v; };
+__device__ __forceinline__ f2 f2_make(float lo, float hi) {
+  f2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi));
+  return r;
 }
-__device__ __forceinline__ float gelu_fast(float x) {
-  float cdf, pdf;
-  gelu_cdf_pdf(x, cdf, pdf);
-  return x * cdf;
+__device__ __forceinline__ f2 f2_bcast(float x) { return f2_make(x, x); }
+__device__ __forceinline__ void f2_split(f2 a, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v));
 }
-__device__ __forceinline__ float gelu_grad_fast(float x) {
-  float cdf, pdf;
-  gelu_cdf_pdf(x, cdf, pdf);
-  return fmaf(x, pdf, cdf);
+__device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) {
+  f2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return r;
+}
+__device__ __forceinline__ f2 f2_mul(f2 a, f2 b) {
+  f2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ f2 f2_add(f2 a, f2 b) {
+  f2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ f2 f2_sub(f2 a, f2 b) {
+  f2 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// GELU (exact erf form) and its derivative for two values at once, for the GEMM epilogues, where a
+// tile's worth of them has to fit under the next tile's main loop.  erf by Abramowitz & Stegun
+// 7.1.26 (absolute error below 1.5e-7, three orders of magnitude under the resolution of the bf16
+// values this feeds): erfc(z) = t (a1 + t (a2 + ... t a5)) exp(-z^2), t = 1 / (1 + p z), z = |x| / sqrt 2.
+// The exponential is shared with the density term of the derivative, so both functions cost four
+// special-function operations and about twenty packed instructions per pair:
+//   cdf = Phi(x), g = x cdf, dg = cdf + x phi(x).
+__device__ __forceinline__ void gelu_pair(float x0, float x1, f2& g, f2& dg) {
+  const f2 x = f2_make(x0, x1);
+  const f2 a = f2_make(fabsf(x0), fabsf(x1));
+  const f2 z = f2_mul(a, f2_bcast(0.70710678118654752f));
+  const f2 den = f2_fma(z, f2_bcast(0.3275911f), f2_bcast(1.0f));
+  float d0, d1;
+  f2_split(den, d0, d1);
+  const f2 t = f2_make(rcp_approx(d0), rcp_approx(d1));
+  // coefficients carry the factor 0.5 of 0.5 * erfc
+  f2 p = f2_fma(t, f2_bcast(0.5f * 1.061405429f), f2_bcast(0.5f * -1.453152027f));
+  p = f2_fma(t, p, f2_bcast(0.5f * 1.421413741f));
+  p = f2_fma(t, p, f2_bcast(0.5f * -0.284496736f));
+  p = f2_fma(t, p, f2_bcast(0.5f * 0.254829592f));
+  const f2 q = f2_mul(f2_mul(z, z), f2_bcast(-1.4426950408889634f));     // -z^2 log2(e)
+  float q0, q1;
+  f2_split(q, q0, q1);
+  const f2 e = f2_make(ex2_approx(q0), ex2_approx(q1));                    // exp(-x^2 / 2)
+  const f2 h = f2_mul(f2_mul(p, t), e);                                    // 0.5 erfc(|x| / sqrt 2)
+  // cdf = 0.5 + sign(x) (0.5 - h)
+  const f2 sgn = f2_make(copysignf(1.0f, x0), copysignf(1.0f, x1));
+  const f2 cdf = f2_fma(sgn, f2_sub(f2_bcast(0.5f), h), f2_bcast(0.5f));
+  const f2 pdf = f2_mul(e, f2_bcast(0.3989422804014327f));
+  g = f2_mul(x, cdf);
+  dg = f2_fma(x, pdf, cdf);
+}
+__device__ __forceinline__ uint32_t pack_bf16_f2(f2 a) {
+  float lo, hi;
+  f2_split(a, lo, hi);
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);

@@ -275,7 +275,8 @@ class B200Engine:
         att, actx = attention_fwd(qkv, B, T, self.cfg.n_head, need_ctx=keep)
         x1 = K.gemm(att, b.o_w, mode=K.EPI_RESID, bias=b.o_b, resid=x, status=st)
         ln2, mu2, rs2 = K.layernorm_fwd(x1, b.ln2_w, b.ln2_b)
-        h = torch.empty(x.shape[0], 4 * x.shape[1], dtype=BF16, device=x.device)
+        # the GELU epilogue also emits gelu'(pre-activation): the backward then only multiplies
+        h = torch.empty(x.shape[0], 4 * x.shape[1], dtype=BF16, device=x.device) if keep else None
         g = K.gemm(ln2, b.fc_w, mode=K.EPI_GELU, bias=b.fc_b, aux_out=h, status=st)
         x2 = K.gemm(g, b.pr_w, mode=K.EPI_RESID, bias=b.pr_b, resid=x1, status=st)
         saved = (x, ln1, mu1, rs1, actx, att, x1, ln2, mu2, rs2, h, g) if keep else None
@@ -286,7 +287,7 @@ class B200Engine:
         x, ln1, mu1, rs1, actx, att, x1, ln2, mu2, rs2, h, g = saved
         Mtok = x.shape[0]
         d = x.shape[1]
-        dh = K.gemm(dx2, b.pr_w, b_t=False, mode=K.EPI_DGELU, aux_in=h, status=st)
+        dh = K.gemm(dx2, b.pr_w, b_t=False, mode=K.EPI_MUL, aux_in=h, status=st)
         with self._fork(dx2, g, dh, ln2):
             K.gemm(dx2, g, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=b.dpr_w,
                    split_k=K.wgrad_split(d, 4 * d, Mtok), status=st)

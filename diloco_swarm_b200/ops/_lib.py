@@ -57,12 +57,13 @@ _SIGS = {
 
 
 def cuda_lib():
-    """The loaded kernel library (builds it if the sources are newer)."""
+    """The loaded kernel library.  It is rebuilt first when a source or header under csrc/ is newer than
+    it (a cheap time-stamp check; the build itself is serialised between processes by a file lock).
+    ``DSWARM_LIB_VARIANT=trace|bounds`` selects one of the debugging builds (ops/_build.py)."""
     global _cuda
     if _cuda is None:
-        path = _build.CUDA_LIB
-        if not os.path.exists(path) or os.environ.get("DSWARM_REBUILD", "0") == "1":
-            path = _build.build_cuda()
+        variant = os.environ.get("DSWARM_LIB_VARIANT", "")
+        path = _build.build_cuda(force=os.environ.get("DSWARM_REBUILD", "0") == "1", variant=variant)
         lib = ctypes.CDLL(path)
         for name, argtypes in _SIGS.items():
             fn = getattr(lib, name, None)

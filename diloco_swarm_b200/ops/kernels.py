@@ -17,7 +17,7 @@ from ._lib import Status, check, cuda_lib, ptr, stream_ptr
 
 BF16, F32 = torch.bfloat16, torch.float32
 
-EPI_STORE, EPI_GELU, EPI_RESID, EPI_DGELU, EPI_ATOMIC_F32, EPI_STORE_F32 = range(6)
+EPI_STORE, EPI_GELU, EPI_RESID, EPI_MUL, EPI_ATOMIC_F32, EPI_STORE_F32 = range(6)
 
 _NUM_SMS = 148
 
@@ -60,6 +60,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Tru
 
     ``a`` is [M,K] (or [K,M] with ``a_t``), ``b`` is [N,K] with ``b_t`` (the
     nn.Linear weight layout) or [K,N] without.  bf16 in, fp32 accumulate.
+    Epilogues: EPI_GELU returns gelu(acc + bias) (exact erf form) and, when
+    ``aux_out`` is given, also stores gelu'(acc + bias) there; EPI_MUL returns
+    acc * ``aux_in``, which with that saved derivative is the GELU backward.
     """
     assert a.dtype == BF16 and b.dtype == BF16 and a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1
@@ -77,9 +80,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Tru
         assert mode != EPI_ATOMIC_F32
         out = torch.empty(M, N, dtype=F32 if f32_out else BF16, device=a.device)
     assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype == (F32 if f32_out else BF16)
-    if mode == EPI_GELU:
-        assert aux_out is not None and aux_out.shape == (M, N) and aux_out.dtype == BF16
-    if mode == EPI_DGELU:
+    if mode == EPI_GELU and aux_out is not None:      # aux_out receives gelu'(a @ b + bias) for the backward
+        assert aux_out.shape == (M, N) and aux_out.dtype == BF16
+    if mode == EPI_MUL:
         assert aux_in is not None and aux_in.shape == (M, N) and aux_in.dtype == BF16
     if mode == EPI_RESID:
         assert resid is not None and resid.shape == (M, N) and resid.dtype == BF16

@@ -21,6 +21,25 @@ from ..ops._lib import Status, check, cuda_lib, stream_ptr
 from .symm import FLAG_WORDS, SymmetricBuffer
 
 
+def touch_map(offset: int, count: int, shard: int, R: int, rank: int, phase: int, grid: int, block: int,
+              vec: int = 8):
+    """Which block of the bf16-wire gradient all-reduce touches which vector of a bucket in a phase
+    (0 cast-in, 1 reduce, 2 widen-out) on replica ``rank``; -1 where the phase touches nothing.
+    Evaluated by the host library from the same header the kernel walks its indices with
+    (csrc/coll_index.h), so a CPU test can check what the per-block barrier relies on."""
+    import ctypes
+
+    import numpy as np
+
+    from .schedule import _host
+    out = np.empty(count // vec, dtype=np.int32)
+    rc = _host().dsw_coll_touch_map(offset, count, shard, R, rank, phase, grid, block, vec,
+                                    out.ctypes.data_as(ctypes.c_void_p))
+    if rc != 0:
+        raise ValueError("bad arguments for the touch map")
+    return out
+
+
 def shard_size(n: int, R: int, align: int) -> int:
     per = (n + R - 1) // R
     return (per + align - 1) // align * align

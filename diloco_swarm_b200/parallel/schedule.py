@@ -33,6 +33,10 @@ def _host():
         lib.dsw_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+        lib.dsw_coll_touch_map.restype = ctypes.c_int
+        lib.dsw_coll_touch_map.argtypes = [ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int,
+                                           ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.c_void_p]
         _lib = lib
     return _lib
 

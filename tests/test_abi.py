@@ -60,7 +60,7 @@ def test_cuda_bindings_match_the_header():
 def test_host_bindings_match_the_header():
     decl = _declarations("dswarm_host.h")
     lib = schedule._host()
-    assert set(decl) == {"dsw_route", "dsw_route_weighted", "dsw_plan"}
+    assert set(decl) == {"dsw_route", "dsw_route_weighted", "dsw_plan", "dsw_coll_touch_map"}
     for name, want in decl.items():
         got = list(getattr(lib, name).argtypes)
         assert len(got) == len(want), name
@@ -82,9 +82,7 @@ def test_every_definition_is_declared():
 
 
 def test_built_libraries_export_the_declared_symbols():
-    if not os.path.exists(_build.CUDA_LIB):
-        pytest.skip("libdswarm_cuda.so is not built")
-    cuda = ctypes.CDLL(_build.CUDA_LIB)
+    cuda = ctypes.CDLL(_build.build_cuda())      # nvcc cross-compiles without a GPU
     for name in {**_declarations("dswarm.h"), **_declarations("dswarm_noalloc.h")}:
         assert hasattr(cuda, name), f"{name} is declared but not exported by libdswarm_cuda.so"
     host = ctypes.CDLL(_build.build_host())

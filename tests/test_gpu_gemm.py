@@ -72,18 +72,19 @@ def test_gemm_epilogues():
     acc = a.float() @ b.float().t() + bias
     out = Kn.gemm(a, b, bias=bias)
     _close(out, acc, "bias")
-    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    out = Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias, aux_out=pre)
-    _close(pre, acc, "gelu pre-activation")
+    dg = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    out = Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias, aux_out=dg)
+    xg = acc.clone().requires_grad_(True)
+    torch.nn.functional.gelu(xg).sum().backward()
+    _close(dg, xg.grad, "gelu derivative")
     _close(out, torch.nn.functional.gelu(acc), "gelu")
+    _close(Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias), torch.nn.functional.gelu(acc), "gelu without the derivative")
     res = _mk((M, N), seed=9)
     out = Kn.gemm(a, b, mode=Kn.EPI_RESID, bias=bias, resid=res)
     _close(out, acc + res.float(), "residual")
     aux = _mk((M, N), seed=10)
-    x = aux.float().requires_grad_(True)
-    torch.nn.functional.gelu(x).sum().backward()
-    out = Kn.gemm(a, b, mode=Kn.EPI_DGELU, aux_in=aux)
-    _close(out, (a.float() @ b.float().t()) * x.grad, "gelu backward")
+    out = Kn.gemm(a, b, mode=Kn.EPI_MUL, aux_in=aux)
+    _close(out, (a.float() @ b.float().t()) * aux.float(), "multiply by the saved derivative")
     out32 = Kn.gemm(a, b, mode=Kn.EPI_STORE_F32)
     _close(out32, a.float() @ b.float().t(), "fp32 store")
 
@@ -108,18 +109,18 @@ def test_gemm_epilogues_tail_shapes(M, N, K, bn):
     _close(o[:M, :N], acc + bias, "bias"); check_guard(o, "bias")
     o, pre = padded(), padded()
     Kn.gemm(a, b, mode=Kn.EPI_GELU, bias=bias, aux_out=pre[:M, :N], out=o[:M, :N], bn=bn, status=st)
-    _close(pre[:M, :N], acc + bias, "pre-activation"); check_guard(pre, "pre-activation")
+    xg = (acc + bias).clone().requires_grad_(True)
+    torch.nn.functional.gelu(xg).sum().backward()
+    _close(pre[:M, :N], xg.grad, "gelu derivative"); check_guard(pre, "gelu derivative")
     _close(o[:M, :N], torch.nn.functional.gelu(acc + bias), "gelu"); check_guard(o, "gelu")
     res = _mk((M, N), seed=23)
     o = padded()
     Kn.gemm(a, b, mode=Kn.EPI_RESID, bias=bias, resid=res, out=o[:M, :N], bn=bn, status=st)
     _close(o[:M, :N], acc + bias + res.float(), "residual"); check_guard(o, "residual")
     aux = _mk((M, N), 2.0, seed=24)
-    x = aux.float().requires_grad_(True)
-    torch.nn.functional.gelu(x).sum().backward()
     o = padded()
-    Kn.gemm(a, b, mode=Kn.EPI_DGELU, aux_in=aux, out=o[:M, :N], bn=bn, status=st)
-    _close(o[:M, :N], acc * x.grad, "gelu backward"); check_guard(o, "gelu backward")
+    Kn.gemm(a, b, mode=Kn.EPI_MUL, aux_in=aux, out=o[:M, :N], bn=bn, status=st)
+    _close(o[:M, :N], acc * aux.float(), "multiply"); check_guard(o, "multiply")
     o32 = padded(torch.float32)
     Kn.gemm(a, b, mode=Kn.EPI_STORE_F32, out=o32[:M, :N], bn=bn, status=st)
     _close(o32[:M, :N], acc, "fp32 store"); check_guard(o32, "fp32 store")
@@ -137,16 +138,12 @@ def test_fast_gelu_matches_erf_form():
     xb = xs.to(torch.bfloat16)
     a = torch.zeros(n, 8, dtype=torch.bfloat16, device="cuda"); a[:, 0] = xb
     b = torch.zeros(8, 8, dtype=torch.bfloat16, device="cuda"); b[:, 0] = 1.0      # every output column = x
-    pre = torch.empty(n, 8, dtype=torch.bfloat16, device="cuda")
-    g = Kn.gemm(a, b, mode=Kn.EPI_GELU, aux_out=pre)
+    dg = torch.empty(n, 8, dtype=torch.bfloat16, device="cuda")
+    g = Kn.gemm(a, b, mode=Kn.EPI_GELU, aux_out=dg)
     ref = torch.nn.functional.gelu(xb.float())
     assert torch.allclose(g[:, 0].float(), ref, atol=1e-6, rtol=2 ** -7)
-    assert torch.equal(pre[:, 0], xb)
     x = xb.float().requires_grad_(True)
     torch.nn.functional.gelu(x).sum().backward()
-    ones = torch.zeros(n, 8, dtype=torch.bfloat16, device="cuda"); ones[:, 0] = 1.0
-    aux = xb.unsqueeze(1).repeat(1, 8).contiguous()
-    dg = Kn.gemm(ones, b, mode=Kn.EPI_DGELU, aux_in=aux)              # 1 * gelu'(x)
     assert torch.allclose(dg[:, 0].float(), x.grad, atol=1e-6, rtol=2 ** -7)
 
 

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 
 def _lib():
     from diloco_swarm_b200.ops import _build
-    lib = ctypes.CDLL(_build.CUDA_LIB)
+    lib = ctypes.CDLL(_build.build_cuda())      # rebuilt first when a source is newer
     vp, ci = ctypes.c_void_p, ctypes.c_int
     lib.dsw_layernorm_bwd_noalloc.restype = ci
     lib.dsw_layernorm_bwd_noalloc.argtypes = [vp] * 10 + [ci, ci, vp]
