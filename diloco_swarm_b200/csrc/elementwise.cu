@@ -43,54 +43,93 @@ __device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
 }
 
 // ------------------------------------------------------------------ LayerNorm
-// One warp per row; the row stays in registers (d <= 8 * 256 = 2048).
+// One warp per row, rows stay in the packed bf16 form they were loaded in (d <= 8 * 256 = 2048).
+// A warp walks many rows: gamma and beta are read into registers once per warp (read per row they
+// were 12 of the 18 memory instructions of a 768-wide row), and the next row's loads are issued
+// before the current row is reduced, so a warp always has a row in flight.
 constexpr int LN_MAX_CHUNKS_ALL = 8;
 
-template <int LN_MAX_CHUNKS>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16(w[j]);
+    f[2 * j] = t.x; f[2 * j + 1] = t.y;
+  }
+}
+
+template <int NCH>
+__device__ __forceinline__ void ln_load_row(uint4 (&o)[NCH], const __nv_bfloat16* __restrict__ x, int row, int d, int lane) {
+  const __nv_bfloat16* xr = x + (long long)row * d;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    o[c] = col < d ? *reinterpret_cast<const uint4*>(xr + col) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <int NCH>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
                      float* __restrict__ rstd_out, int M, int d, float eps) {
   const int lane = threadIdx.x & 31;
-  const int wpb = blockDim.x >> 5;
-  const int nch = (d + 255) / 256;
-  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < M; row += gridDim.x * wpb) {
-    const __nv_bfloat16* xr = x + (long long)row * d;
-    float v[LN_MAX_CHUNKS][8];
+  const int stride = gridDim.x * (blockDim.x >> 5);
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  float g[NCH][8], b[NCH][8];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { g[c][j] = 0.f; b[c][j] = 0.f; }
+    if (col < d) {
+      load8f(gamma + col, g[c]);
+      if (beta) load8f(beta + col, b[c]);
+    }
+  }
+  const float inv_d = 1.f / d;
+  uint4 cur[NCH], nxt[NCH];
+  ln_load_row<NCH>(cur, x, row, d, lane);
+  for (; row < M; row += stride) {
+    const bool more = row + stride < M;
+    if (more) ln_load_row<NCH>(nxt, x, row + stride, d, lane);
     float s = 0.f;
 #pragma unroll
-    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
-      const int col = c * 256 + lane * 8;
-      if (c < nch && col < d) {
-        load8(xr + col, v[c]);
+    for (int c = 0; c < NCH; ++c) {
+      float v[8];
+      unpack8(cur[c], v);                          // columns past d were loaded as zeros
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += v[c][j];
-      }
+      for (int j = 0; j < 8; ++j) s += v[j];
     }
-    const float mean = warp_sum(s) / d;
+    const float mean = warp_sum(s) * inv_d;
     float q = 0.f;
 #pragma unroll
-    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
-      const int col = c * 256 + lane * 8;
-      if (c < nch && col < d) {
+    for (int c = 0; c < NCH; ++c) {
+      if (c * 256 + lane * 8 < d) {
+        float v[8];
+        unpack8(cur[c], v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { const float t = v[c][j] - mean; q += t * t; }
+        for (int j = 0; j < 8; ++j) { const float t = v[j] - mean; q += t * t; }
       }
     }
-    const float rstd = rsqrtf(warp_sum(q) / d + eps);
+    const float rstd = rsqrtf(warp_sum(q) * inv_d + eps);
     if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
     __nv_bfloat16* yr = y + (long long)row * d;
 #pragma unroll
-    for (int c = 0; c < LN_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < NCH; ++c) {
       const int col = c * 256 + lane * 8;
-      if (c < nch && col < d) {
-        float g[8], b[8], o[8];
-        load8f(gamma + col, g);
-        if (beta) load8f(beta + col, b);
+      if (col < d) {
+        float v[8], o[8];
+        unpack8(cur[c], v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = (v[c][j] - mean) * rstd * g[j] + (beta ? b[j] : 0.f);
+        for (int j = 0; j < 8; ++j) o[j] = fmaf((v[j] - mean) * rstd, g[c][j], b[c][j]);
         store8(yr + col, o);
       }
+    }
+    if (more) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) cur[c] = nxt[c];
     }
   }
 }
@@ -104,15 +143,6 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
 // atomics).  At the end the block folds its warps' strips and writes partial[block][3][d]; a small
 // finish kernel adds the per-block partials into the fp32 gradients in a fixed order.
 constexpr int LN_BWD_WARPS = 8;
-
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 t = unpack_bf16(w[j]);
-    f[2 * j] = t.x; f[2 * j + 1] = t.y;
-  }
-}
 
 // One row's operands as loaded (bf16, 8 per lane per 256-column chunk) plus its statistics.
 template <int NCH>
@@ -140,8 +170,12 @@ __device__ __forceinline__ void ln_bwd_load(LnBwdRow<NCH>& o, const __nv_bfloat1
   o.rstd = rstd_in[row];
 }
 
+// Blocks per SM: rows up to 768 columns keep the column sums, gamma and two rows (the current one and the
+// prefetched next one) in registers, about 200 per thread, so one block; wider rows use the strips, two blocks.
+constexpr int ln_bwd_blocks_per_sm(int nch) { return nch <= 3 ? 1 : 2; }
+
 template <int LN_MAX_CHUNKS>
-__global__ void __launch_bounds__(32 * LN_BWD_WARPS, 2)
+__global__ void __launch_bounds__(32 * LN_BWD_WARPS, ln_bwd_blocks_per_sm(LN_MAX_CHUNKS))
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
@@ -158,13 +192,16 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   // cycles than the whole row costs in DRAM time.  Wider rows add into the strips row by row; up to 1024
   // columns the next row's loads are issued before the current row is worked on.
   constexpr bool REG_ACC = LN_MAX_CHUNKS <= 3;
-  constexpr bool PREFETCH = !REG_ACC && LN_MAX_CHUNKS <= 4;
+  constexpr bool PREFETCH = LN_MAX_CHUNKS <= 4;
   constexpr int NACC = REG_ACC ? LN_MAX_CHUNKS : 1;
-  float acc_g[NACC][8], acc_b[NACC][8], acc_r[NACC][8];
+  float acc_g[NACC][8], acc_b[NACC][8], acc_r[NACC][8], gm[NACC][8];
 #pragma unroll
-  for (int c = 0; c < NACC; ++c)
+  for (int c = 0; c < NACC; ++c) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { acc_g[c][j] = 0.f; acc_b[c][j] = 0.f; acc_r[c][j] = 0.f; }
+    for (int j = 0; j < 8; ++j) { acc_g[c][j] = 0.f; acc_b[c][j] = 0.f; acc_r[c][j] = 0.f; gm[c][j] = 0.f; }
+    // gamma lives in registers next to the sums (read per row it was 12 of a 768-wide row's 24 memory instructions)
+    if (REG_ACC && c * 256 + lane * 8 < d) load8f(gamma + c * 256 + lane * 8, gm[c]);
+  }
   const int stride = gridDim.x * LN_BWD_WARPS;
   int row = blockIdx.x * LN_BWD_WARPS + warp;
   LnBwdRow<LN_MAX_CHUNKS> cur, nxt;
@@ -185,12 +222,12 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
         float g[8], dv[8], xh[8];
         unpack8(cur.x[c], xh);
         unpack8(cur.dy[c], dv);
-        load8f(gamma + col, g);
+        if constexpr (!REG_ACC) load8f(gamma + col, g);
         if constexpr (REG_ACC) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float xhat = (xh[j] - mean) * rstd;
-            const float gy = dv[j] * g[j];
+            const float gy = dv[j] * gm[c][j];
             s1 += gy;
             s2 += gy * xhat;
             acc_g[c][j] += dv[j] * xhat;
@@ -223,7 +260,12 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
         float g[8], dv[8], xh[8], o[8], r[8];
         unpack8(cur.x[c], xh);
         unpack8(cur.dy[c], dv);
-        load8f(gamma + col, g);
+        if constexpr (REG_ACC) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = gm[c][j];
+        } else {
+          load8f(gamma + col, g);
+        }
         if (dres) {
           unpack8(cur.r[c], r);
           if constexpr (REG_ACC) {
@@ -522,7 +564,8 @@ typedef __nv_bfloat16 bf16;
 extern "C" int dsw_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean,
                                  float* rstd, int M, int d, float eps, cudaStream_t st) {
   if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
-  const int grid = grid_for(M, 8);
+  // two blocks per SM, several rows per warp when there are enough rows: gamma and beta are paid once per warp
+  const int grid = grid_for(M, 16, 148 * 2);
 #define LN_FWD(NCH) layernorm_fwd_kernel<NCH><<<grid, 256, 0, st>>>((const bf16*)x, gamma, beta, (bf16*)y, mean, rstd, M, d, eps)
   switch ((d + 255) / 256) {
     case 1: LN_FWD(1); break; case 2: LN_FWD(2); break; case 3: LN_FWD(3); break; case 4: LN_FWD(4); break;
@@ -544,15 +587,20 @@ extern "C" int dsw_layernorm_bwd(const void* dy, const void* x, const float* gam
                                  const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
                                  float* dres_sum, float* scratch, int M, int d, cudaStream_t st) {
   if (d % 8 || d > 256 * LN_MAX_CHUNKS_ALL) return -10;
-  const int grid = dsw_layernorm_bwd_blocks(M);
+  int grid = dsw_layernorm_bwd_blocks(M);
+  if ((d + 255) / 256 <= 3 && grid > 148) grid = 148;          // the register-resident variant runs one block per SM
   const int want = dres_sum != nullptr && dres != nullptr;
   const size_t shmem = sizeof(float) * LN_BWD_WARPS * 3 * d;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -2;
 #define LN_BWD(NCH)                                                                                              \
   do {                                                                                                           \
-    static bool attr = false;                                                                                    \
-    if (!attr) {                                                                                                 \
-      cudaFuncSetAttribute(layernorm_bwd_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 256 * NCH * 4); \
-      attr = true;                                                                                               \
+    static bool attr[64] = {false};          /* the attribute is per device */                                 \
+    if (!attr[dev]) {                                                                                            \
+      if (cudaFuncSetAttribute(layernorm_bwd_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                               8 * 3 * 256 * NCH * 4) != cudaSuccess)                                            \
+        return -2;                                                                                               \
+      attr[dev] = true;                                                                                          \
     }                                                                                                            \
     layernorm_bwd_kernel<NCH><<<grid, 32 * LN_BWD_WARPS, shmem, st>>>((const bf16*)dy, (const bf16*)x, gamma, mean, rstd, \
                                                                      (const bf16*)dres, (bf16*)dx, scratch, M, d); \

@@ -212,6 +212,28 @@ __device__ __forceinline__ void epilogue_warp(const GemmArgs& g, uint32_t t_addr
   }
 }
 
+// The residual / saved-derivative operand of a tile, asked into L2 one tile ahead: the epilogue's loads of it
+// then cost an L2 round trip instead of a DRAM one, which otherwise sits exposed once per chunk.
+// Same lane-to-address map as the loads in epilogue_warp; one request per 32-byte sector.
+template <int MODE, int NCOLS>
+__device__ __forceinline__ void prefetch_extra(const GemmArgs& g, int row_base, int lane, int col_base) {
+  if constexpr (MODE == EPI_RESID || MODE == EPI_MUL) {
+    const __nv_bfloat16* src = MODE == EPI_RESID ? g.resid : g.aux_in;
+    const long long ld = MODE == EPI_RESID ? g.ldr : g.ldaux;
+    if (lane & 1) return;
+#pragma unroll
+    for (int c = 0; c < NCOLS / 32; ++c) {
+      const int col = col_base + c * 32 + (lane & 3) * 8;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = row_base + i * 8 + (lane >> 2);
+        if (row < g.M && col < g.N)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (long long)row * ld + col));
+      }
+    }
+  }
+}
+
 // One tile's worth of epilogue for this warp.  MODE is the kernel's compile-time epilogue class: a kernel
 // that switched on the mode at run time carried the registers of every epilogue at once and spilled.
 template <int MODE, int NCOLS, class Release>
@@ -368,6 +390,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int part = (warp - EPI_WARP0) >> 2;   // which quarter of the tile's columns
     uint32_t tcount = 0;
     bool ok = true;
+    auto prefetch_tile = [&](int tile) {
+      if (tile >= num_tiles) return;
+      const int rem = tile % (tiles_m * tiles_n);
+      prefetch_extra<MODE, BN / 4>(g, (rem % tiles_m) * BM + q * 32, lane, (rem / tiles_m) * BN + part * (BN / 4));
+    };
+    prefetch_tile(blockIdx.x);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
       const int ks = tile / (tiles_m * tiles_n);
       const int rem = tile - ks * tiles_m * tiles_n;
@@ -376,6 +404,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int ab = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       const bool has_k = ks * kb_per_split < kb_total;
+      prefetch_tile(tile + gridDim.x);
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ab * BN + part * (BN / 4) + (uint32_t(q * 32) << 16);
@@ -577,6 +606,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     long long* etr = (blockIdx.x == 0 && warp == EPI_WARP0 && lane == 0 && g.trace != nullptr) ? g.trace + 256 : nullptr;
     int eslot = 0;
     (void)etr; (void)eslot;
+    auto prefetch_tile = [&](int tile) {
+      if (tile >= num_tiles) return;
+      const int rem = tile % (tiles_m * tiles_n);
+      prefetch_extra<MODE, BN / 4>(g, (rem % tiles_m) * 256 + int(rank) * 128 + q * 32, lane,
+                                   (rem / tiles_m) * BN + part * (BN / 4));
+    };
+    prefetch_tile(pair);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
       const int ks = tile / (tiles_m * tiles_n);
       const int rem = tile - ks * tiles_m * tiles_n;
@@ -585,6 +621,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int ab = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       const bool has_k = ks * kb_per_split < kb_total;
+      prefetch_tile(tile + num_pairs);
       GEMM_TRACE2(etr, eslot);
       if (!mbar_wait(&acc_full[ab], aph, abort_flag, g.status)) { ok = false; break; }
       GEMM_TRACE2(etr, eslot);
