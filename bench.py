@@ -12,6 +12,12 @@ Topology per N: 1 -> 1 stage x 1, 2 -> 2 x 1, 4 -> 2 x 2, 8 -> 2 x 4.
 The global batch is fixed, so this is strong scaling.  The outer sync runs
 once inside the timed region (H = min(50, K)).
 
+After the two headline regions the same process runs a few steps of plain SWARM
+(per-step fused gradient all-reduce instead of DiLoCo) on a second trainer and
+reports its tokens/s and the exposed part of the gradient sync, and, outside any
+timed region, checks the fused collectives against NCCL on buffers of the
+stage's real size (``collective_check``; a mismatch makes the run fail).
+
 Two timed regions of K steps each, both on the device with CUDA events between
 a barrier + synchronize on both sides, max over ranks:
   value  batches already resident on the device;
@@ -36,6 +42,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 TOPOLOGY = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
+# The unmodified reference (gloo + host staging) on this pool's B200s, same config, tokens/s as measured by an
+# earlier driver run of `bench.py --impl reference`; the reference publishes no throughput (so vs_baseline is null).
+REFERENCE_TOKENS_PER_S = {1: 483165.0, 2: 136634.0, 4: 200694.0, 8: 300112.0}
 SMI_QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -66,6 +75,9 @@ def parse_args():
                          "<log-dir>/bench<pid>/timeline (utils/timeline.py); adds events to the timed region")
     ap.add_argument("--log-dir", default=os.path.join(tempfile.gettempdir(), "dswarm_bench"))
     ap.add_argument("--recv-prefetch", type=int, default=2, help="pipeline receives posted this many operations ahead")
+    ap.add_argument("--swarm-steps", type=int, default=-1,
+                    help="timed steps of the plain-SWARM side measurement (default min(steps, 8); 0 skips it)")
+    ap.add_argument("--no-collective-check", action="store_true")
     return ap.parse_args()
 
 
@@ -121,11 +133,12 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def build_config(args, S: int):
+def build_config(args, S: int, no_outer=None, run_suffix: str = ""):
     from diloco_swarm_b200.config import Config, load_toml
     model = load_toml(os.path.join(ROOT, "configs", "model", f"gpt2-{args.model}.toml"))
     H = args.H if args.H > 0 else max(1, min(50, args.steps))
-    outer = {"type": "None", "lr": 0.0} if args.no_outer else {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
+    no_outer = args.no_outer if no_outer is None else no_outer
+    outer = {"type": "None", "lr": 0.0} if no_outer else {"type": "SGD", "lr": 0.7, "momentum": 0.9, "nesterov": True}
     return Config(
         model=model,
         data={"path": "synthetic:zipf", "seq_length": args.seq, "num_examples": args.batch * 2, "pin_memory": True},
@@ -134,10 +147,11 @@ def build_config(args, S: int):
                "inner_optimizer": {"type": "AdamW", "lr": 6e-4},
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
-        swarm={"num_stages": S, "sync_every_n_steps": 1 if args.no_outer else H, "layer_split": args.layer_split,
+        swarm={"num_stages": S, "sync_every_n_steps": 1 if no_outer else H, "layer_split": args.layer_split,
                "collective": args.collective, "routing": args.routing, "recv_prefetch": args.recv_prefetch},
         eval={"enable": False}, sample={"enable": False},
-        logging={"log_dir": args.log_dir, "run_id": f"bench{os.getpid()}" if args.timeline_steps == 0 else "bench",
+        logging={"log_dir": args.log_dir,
+                 "run_id": (f"bench{os.getpid()}" if args.timeline_steps == 0 else "bench") + run_suffix,
                  "console": {"log_level": "ERROR"}, "file": {"log_level": "ERROR"},
                  "timeline_steps": args.timeline_steps, "timeline_start": args.warmup + 1},
         engine=args.engine), H
@@ -174,9 +188,16 @@ def run_ours(args) -> dict:
         h2d += (host[0]["target_ids"].numel() + host[0]["attention_mask"].numel()) * 8
     step_no = [0]
 
+    active = [tr]
+    sync_phases = []          # device phases of every step that synchronised, in order
+
     def one(batches):
         step_no[0] += 1
-        local, _ = tr.train_step(step_no[0], batches[step_no[0] % 2])
+        t = active[0]
+        before = t.last_sync_phase_ms
+        local, _ = t.train_step(step_no[0], batches[step_no[0] % 2])
+        if t.last_sync_phase_ms is not before:
+            sync_phases.append(t.last_sync_phase_ms)
         return local
 
     windows, per_step, mallocs = [], [], []
@@ -218,13 +239,60 @@ def run_ours(args) -> dict:
     if world_size > 1:
         dist.all_reduce(loss_t, op=dist.ReduceOp.SUM)
         loss_t /= len(tr.world.last_stage_ranks)
-    # device time of the last outer sync (fused all-reduce + Nesterov + write-back + bf16 refresh), max over
-    # ranks; the kernel's entry barrier waits for the slowest replica, so replica skew is part of it
-    osync = torch.tensor([tr.last_phase_ms.get("outer_sync", 0.0)], dtype=torch.float64, device=dev)
-    if world_size > 1:
-        dist.all_reduce(osync, op=dist.ReduceOp.MAX)
+    # Device time of the outer sync (fused all-reduce + Nesterov + write-back + bf16 refresh of the weights) in the
+    # steps that ran one, max over ranks, mean over those steps; the wait for the slowest replica before it is
+    # reported separately.  Roofline: replica r reads its 1/R slice from R - 1 peers and writes it to R - 1
+    # peers, 2 (R-1)/R 4n bytes per direction, over the slower of the two figures below.
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world_size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n_sync = max_over_ranks(float(len(sync_phases)))
+    outer_ms = max_over_ranks(statistics.mean(p.get("outer_sync", 0.0) for p in sync_phases) if sync_phases else 0.0)
+    outer_wait_ms = max_over_ranks(statistics.mean(p.get("outer_wait", 0.0) for p in sync_phases) if sync_phases else 0.0)
+    stage_elems = int(max_over_ranks(float(getattr(tr.engine, "n", 0))))
+    outer_info = {"ms": outer_ms if n_sync else None, "wait_for_slowest_replica_ms": outer_wait_ms if n_sync else None,
+                  "steps_with_a_sync": int(n_sync), "stage_elements": stage_elems, "replicas": R}
+    if R > 1 and n_sync and outer_ms > 0:
+        link_bytes = 2.0 * (R - 1) / R * 4.0 * stage_elems
+        outer_info["nvlink_bytes_per_direction"] = link_bytes
+        outer_info["includes"] = "fused kernel + bf16 refresh of the stage's weights (one pass over local memory)"
+        outer_info["frac_of_770_GBs_measured_peer_copy"] = link_bytes / (outer_ms * 1e-3) / 770e9
+        outer_info["frac_of_900_GBs_nominal"] = link_bytes / (outer_ms * 1e-3) / 900e9
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
+
+    # ---- plain SWARM in the same process: per-step fused gradient all-reduce, bucket-wise under the last backward
+    swarm = None
+    k2 = min(args.steps, 8) if args.swarm_steps < 0 else args.swarm_steps
+    if k2 > 0 and not args.no_outer and args.timeline_steps == 0:
+        cfg2, _ = build_config(args, S, no_outer=True, run_suffix="_swarm")
+        tr2 = Trainer(cfg2, world=tr.world)
+        tr2.num_train_steps = 10 ** 6
+        active[0] = tr2
+        first = len(sync_phases)
+        for _ in range(3):
+            one(resident)
+        ms_sw, _, _ = timed(resident, k2)
+        exposed = [p.get("grad_sync", 0.0) for p in sync_phases[first + 3:]]
+        swarm = {"swarm_tokens_per_s": args.batch * args.seq * k2 / (ms_sw / 1e3), "swarm_ms_per_step": ms_sw / k2,
+                 "steps": k2, "warmup": 3,
+                 "grad_sync_exposed_ms": max_over_ranks(statistics.mean(exposed) if exposed else 0.0),
+                 "grad_wire_dtype": cfg2.swarm.grad_wire_dtype}
+        tr2.logger.close()
+        active[0] = tr
+
+    # ---- the fused collectives against NCCL on this box, outside the timed regions
+    check = {"status": "skipped"}
+    if not args.no_collective_check and args.engine == "b200" and args.collective == "fused":
+        from diloco_swarm_b200.parallel.collectives import check_against_nccl
+        grp = tr.world.curr_stage_group if R > 1 else None
+        check = check_against_nccl(grp, dev, tr.engine.n, tr.engine.buckets)
+        bad = max_over_ranks(1.0 if check["status"] == "mismatch" else 0.0)
+        if bad:
+            check["status"] = "mismatch"
     out = {
         "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -241,7 +309,11 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
-        "outer_sync_ms_incl_peer_wait": float(osync.item()),
+        "outer_sync": outer_info,
+        "outer_sync_ms": outer_info["ms"],
+        **(swarm or {}),
+        "collective_check": check["status"], "collective_check_detail": check,
+        "vs_reference_measured_earlier": (value / REFERENCE_TOKENS_PER_S[N]) if N in REFERENCE_TOKENS_PER_S else None,
         "loss": float(loss_t.item()),
         "step_ms_rank0": {"device_resident_inputs": per_step[0], "e2e": per_step[1]},
         "cuda_mallocs_in_timed_regions_rank0": mallocs,
@@ -251,6 +323,10 @@ def run_ours(args) -> dict:
     tr.world.barrier()
     tr.logger.close()
     tr.world.destroy()
+    if check["status"] == "mismatch":
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        raise SystemExit("collective_check failed: the fused collectives disagree with NCCL: " + json.dumps(check))
     return out if rank == 0 else {}
 
 

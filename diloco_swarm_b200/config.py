@@ -67,6 +67,9 @@ class SwarmConfig(BaseConfig):
     # (added) pipeline receives posted this many operations ahead of their use (a posted NCCL receive is a
     # resident kernel that waits for its sender, so more look-ahead hides latency but holds SM resources)
     recv_prefetch: int = 2
+    # (added) bound of the fused collectives' waits for a peer GPU, in seconds (the kernels count clock cycles at
+    # a nominal 2 GHz); a wait that runs out ends the kernel with a status that the host raises as an error
+    peer_wait_s: float = 2.0
 
 
 class ModelConfig(BaseConfig):

@@ -29,7 +29,7 @@ from .gpt2 import GPT2Config, init_tensor, split_layers, stage_param_specs
 from ..ops import kernels as K
 from ..ops._lib import Status, load_all_kernels
 from ..ops.attention import attention_bwd, attention_fwd
-from ..parallel.collectives import GradSync, OuterSync
+from ..parallel.collectives import GradSync, OuterSync, StageRendezvous, wait_cycles_for
 from ..parallel.symm import SymmetricBuffer
 
 BF16, F32 = torch.bfloat16, torch.float32
@@ -59,6 +59,10 @@ class B200Engine:
         d = cfg.n_embd
         assert d % 8 == 0 and cfg.vocab_size % 8 == 0, "n_embd and vocab_size must be multiples of 8"
         assert cfg.bias, "the b200 engine implements the reference's bias=True model"
+        if cfg.dropout != 0.0:
+            raise NotImplementedError(
+                "model.dropout > 0 is implemented by the autograd engine only (--engine torch); the sm_100a "
+                "kernels train without dropout, as every configuration and experiment of the reference does")
         K.set_deterministic(bool(getattr(config.train, "deterministic", False)))
 
         # ---- flat layout ------------------------------------------------
@@ -93,9 +97,12 @@ class B200Engine:
         self.outer: Optional[OuterSync] = None
         if self.has_outer:
             assert oc.type == "SGD", "the outer optimiser is SGD (optionally Nesterov) as in the reference"
-            self.outer = OuterSync(self.theta_buf, self.n, device, oc.lr, oc.momentum, oc.nesterov, group, self.status)
+            self.outer = OuterSync(self.theta_buf, self.n, device, oc.lr, oc.momentum, oc.nesterov, group, self.status,
+                                   wait_cycles=wait_cycles_for(config.swarm.peer_wait_s))
         self.grad_sync = GradSync(self.grad_buf, self.n, device, group,
-                                  wire_bf16=config.swarm.grad_wire_dtype == "bfloat16", status=self.status)
+                                  wire_bf16=config.swarm.grad_wire_dtype == "bfloat16", status=self.status,
+                                  wait_cycles=wait_cycles_for(config.swarm.peer_wait_s))
+        self.rendezvous = StageRendezvous(group, device)
         self.stash: Dict[int, dict] = {}
         self.training = True
         self._build_views()
@@ -232,6 +239,11 @@ class B200Engine:
         self.comm_stream.wait_stream(torch.cuda.current_stream())
         if self.side is not None:
             self.comm_stream.wait_stream(self.side)
+        if self._buckets_sent == 0:
+            # replicas reach their last backward at different times (routing gives them different loads):
+            # meet on the communication stream first, so the kernels' bounded peer waits only see the
+            # microseconds between the replicas leaving that meeting, not the skew of the step
+            self.rendezvous.meet(self.comm_stream)
         self.grad_sync.bucket(off, cnt, stream=self.comm_stream)
         self._buckets_sent += 1
 
@@ -272,7 +284,7 @@ class B200Engine:
         st = self.status
         ln1, mu1, rs1 = K.layernorm_fwd(x, b.ln1_w, b.ln1_b)
         qkv = K.gemm(ln1, b.qkv_w, bias=b.qkv_b, status=st)
-        att, actx = attention_fwd(qkv, B, T, self.cfg.n_head, need_ctx=keep)
+        att, actx = attention_fwd(qkv, B, T, self.cfg.n_head, need_ctx=keep, status=st)
         x1 = K.gemm(att, b.o_w, mode=K.EPI_RESID, bias=b.o_b, resid=x, status=st)
         ln2, mu2, rs2 = K.layernorm_fwd(x1, b.ln2_w, b.ln2_b)
         # the GELU epilogue also emits gelu'(pre-activation): the backward then only multiplies
@@ -425,7 +437,18 @@ class B200Engine:
                        ic.nesterov, self.stats, zero_grad=True)
         return self.stats[1]
 
-    def outer_step(self) -> None:
+    def outer_step(self, timer=None) -> None:
+        """``timer`` (utils/timers.PhaseTimer): the wait for the slowest replica is recorded as phase
+        "outer_wait", the synchronisation itself (fused kernel or library twin, plus the bf16 refresh of the
+        weights) as "outer_sync", so that the second is the cost of the operation and not of the skew."""
+        import contextlib
+        phase = timer.phase if timer is not None else (lambda name: contextlib.nullcontext())
+        with phase("outer_wait"):
+            self.rendezvous.meet()        # absorbs the skew that H steps without contact have built up
+        with phase("outer_sync"):
+            self._outer_update()
+
+    def _outer_update(self) -> None:
         o = self.outer
         if self.fused or o.R == 1:
             o.step()

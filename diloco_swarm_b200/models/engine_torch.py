@@ -139,9 +139,12 @@ class TorchEngine:
         self.inner.step()
         return float(norm)
 
-    def outer_step(self) -> None:
+    def outer_step(self, timer=None) -> None:
         """pseudo-gradient = outer - inner, averaged over the stage, outer
         optimiser step, inner <- outer (src/utils.py:218-226, src/train.py:261-269)."""
+        if timer is not None:
+            with timer.phase("outer_sync"):
+                return self.outer_step()
         R = self.world.num_replicas
         with torch.no_grad():
             for po, pi in zip(self.outer_params, self.model.parameters()):

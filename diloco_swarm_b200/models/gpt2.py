@@ -139,9 +139,13 @@ class _LayerNorm(nn.Module):
 
 
 class _Attention(nn.Module):
-    def __init__(self, d: int, n_head: int, bias: bool):
+    """Dropout sits where the reference has it: on the attention probabilities and on the projected
+    output (src/model.py:48-49,67,77)."""
+
+    def __init__(self, d: int, n_head: int, bias: bool, dropout: float = 0.0):
         super().__init__()
         self.n_head = n_head
+        self.dropout = dropout
         self.c_attn = nn.Linear(d, 3 * d, bias=bias)
         self.c_proj = nn.Linear(d, d, bias=bias)
 
@@ -149,27 +153,29 @@ class _Attention(nn.Module):
         B, T, C = x.shape
         hs = C // self.n_head
         q, k, v = (t.view(B, T, self.n_head, hs).transpose(1, 2) for t in self.c_attn(x).split(C, dim=2))
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        return self.c_proj(y.transpose(1, 2).reshape(B, T, C))
+        p = self.dropout if self.training else 0.0
+        y = F.scaled_dot_product_attention(q, k, v, dropout_p=p, is_causal=True)
+        return F.dropout(self.c_proj(y.transpose(1, 2).reshape(B, T, C)), p, self.training)
 
 
 class _MLP(nn.Module):
-    def __init__(self, d: int, bias: bool):
+    def __init__(self, d: int, bias: bool, dropout: float = 0.0):
         super().__init__()
+        self.dropout = dropout
         self.c_fc = nn.Linear(d, 4 * d, bias=bias)
         self.c_proj = nn.Linear(4 * d, d, bias=bias)
 
     def forward(self, x):
-        return self.c_proj(F.gelu(self.c_fc(x)))
+        return F.dropout(self.c_proj(F.gelu(self.c_fc(x))), self.dropout, self.training)    # src/model.py:86,89
 
 
 class _Block(nn.Module):
-    def __init__(self, d: int, n_head: int, bias: bool):
+    def __init__(self, d: int, n_head: int, bias: bool, dropout: float = 0.0):
         super().__init__()
         self.ln_1 = _LayerNorm(d, bias)
-        self.attn = _Attention(d, n_head, bias)
+        self.attn = _Attention(d, n_head, bias, dropout)
         self.ln_2 = _LayerNorm(d, bias)
-        self.mlp = _MLP(d, bias)
+        self.mlp = _MLP(d, bias, dropout)
 
     def forward(self, x):
         x = x + self.attn(self.ln_1(x))
@@ -196,7 +202,7 @@ class TorchStage(nn.Module):
         if self.is_first:
             t.wte = nn.Embedding(cfg.vocab_size, d)
             t.wpe = nn.Embedding(cfg.block_size, d)
-        t.h = nn.ModuleList([_Block(d, cfg.n_head, cfg.bias) for _ in self.layers])
+        t.h = nn.ModuleList([_Block(d, cfg.n_head, cfg.bias, cfg.dropout) for _ in self.layers])
         if self.is_last:
             t.ln_f = _LayerNorm(d, cfg.bias)
         self.transformer = t
@@ -213,7 +219,8 @@ class TorchStage(nn.Module):
     # -- pieces (reference: encode_tokens / forward_layers / forward_logits) --
     def encode_tokens(self, input_ids: torch.Tensor) -> torch.Tensor:
         pos = torch.arange(input_ids.size(1), device=input_ids.device)
-        return self.transformer.wte(input_ids) + self.transformer.wpe(pos)
+        x = self.transformer.wte(input_ids) + self.transformer.wpe(pos)
+        return F.dropout(x, self.config.dropout, self.training)                               # src/model.py:114,139
 
     def forward(self, input_ids: Optional[torch.Tensor] = None,
                 hidden_states: Optional[torch.Tensor] = None) -> torch.Tensor:

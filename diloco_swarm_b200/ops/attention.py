@@ -20,7 +20,7 @@ from typing import Optional, Tuple
 import torch
 import torch.nn.functional as F
 
-from ._lib import check, cuda_lib, stream_ptr
+from ._lib import Status, check, cuda_lib, stream_ptr
 
 BF16 = torch.bfloat16
 
@@ -36,10 +36,13 @@ def _native_available(hs: int, T: int) -> bool:
 
 
 class AttnCtx:
-    __slots__ = ("qkv", "out", "lse", "B", "T", "nh", "native", "q", "k", "v", "o")
+    __slots__ = ("qkv", "out", "lse", "B", "T", "nh", "native", "q", "k", "v", "o", "status")
 
 
-def attention_fwd(qkv: torch.Tensor, B: int, T: int, nh: int, need_ctx: bool = True) -> Tuple[torch.Tensor, Optional[AttnCtx]]:
+def attention_fwd(qkv: torch.Tensor, B: int, T: int, nh: int, need_ctx: bool = True,
+                  status: Optional[Status] = None) -> Tuple[torch.Tensor, Optional[AttnCtx]]:
+    """``status``: the engine's status word; an mbarrier wait that runs out inside the kernel (forward
+    or the backward that uses the returned context) is reported there instead of passing silently."""
     M, d3 = qkv.shape
     d = d3 // 3
     hs = d // nh
@@ -48,16 +51,18 @@ def attention_fwd(qkv: torch.Tensor, B: int, T: int, nh: int, need_ctx: bool = T
         out = torch.empty(M, d, dtype=BF16, device=qkv.device)
         lse = torch.empty(B * nh * T, dtype=torch.float32, device=qkv.device)
         check(cuda_lib().dsw_attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, nh, hs,
-                                           1.0 / math.sqrt(hs), None, stream_ptr()), "dsw_attention_fwd")
+                                           1.0 / math.sqrt(hs), status.ptr if status is not None else None,
+                                           stream_ptr()), "dsw_attention_fwd")
         if ctx is not None:
             ctx.native, ctx.qkv, ctx.out, ctx.lse, ctx.B, ctx.T, ctx.nh = True, qkv, out, lse, B, T, nh
+            ctx.status = status
         return out, ctx
     q, k, v = (qkv[:, i * d:(i + 1) * d].view(B, T, nh, hs).transpose(1, 2) for i in range(3))
     if ctx is not None:
         q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
         with torch.enable_grad():
             o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        ctx.native, ctx.q, ctx.k, ctx.v, ctx.o = False, q, k, v, o
+        ctx.native, ctx.q, ctx.k, ctx.v, ctx.o, ctx.status = False, q, k, v, o, None
     else:
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
     return o.detach().transpose(1, 2).reshape(M, d), ctx
@@ -75,7 +80,8 @@ def attention_bwd(dout: torch.Tensor, ctx: AttnCtx) -> torch.Tensor:
         dout = dout.contiguous()
         check(cuda_lib().dsw_attention_bwd(ctx.qkv.data_ptr(), ctx.out.data_ptr(), dout.data_ptr(), ctx.lse.data_ptr(),
                                            dqkv.data_ptr(), dq_acc.data_ptr(), dvec.data_ptr(), B, T, nh, hs,
-                                           1.0 / math.sqrt(hs), None, stream_ptr()), "dsw_attention_bwd")
+                                           1.0 / math.sqrt(hs), ctx.status.ptr if ctx.status is not None else None,
+                                           stream_ptr()), "dsw_attention_bwd")
         return dqkv
     q, k, v, o = ctx.q, ctx.k, ctx.v, ctx.o
     B, nh, T, hs = q.shape

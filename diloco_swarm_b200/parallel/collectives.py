@@ -40,6 +40,38 @@ def touch_map(offset: int, count: int, shard: int, R: int, rank: int, phase: int
     return out
 
 
+class StageRendezvous:
+    """Brings the replicas of a stage together, on the device, before a fused collective is queued.
+
+    The fused kernels bound their waits for a peer (``swarm.peer_wait_s``), which is right for telling a
+    dead peer from a live one but wrong for absorbing skew: DiLoCo replicas of a one-stage world share
+    nothing for H steps, and a few per cent of clock difference under the power cap adds up to seconds.
+    (The reference meets at a ``dist.barrier()`` every step, src/train.py:246.)  One tiny all-reduce on the
+    stage group, queued on the stream the fused kernel will run on, makes every replica's stream wait
+    until all have arrived; the kernel's own bounded wait then only sees the microseconds between the
+    replicas leaving that all-reduce."""
+
+    def __init__(self, group, device: torch.device):
+        self.group, self.device = group, device
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.count = 0
+
+    def meet(self, stream: Optional["torch.cuda.Stream"] = None) -> None:
+        if self.group is None or dist.get_world_size(self.group) == 1:
+            return
+        self.count += 1
+        if stream is not None and self.device.type == "cuda":
+            with torch.cuda.stream(stream):
+                dist.all_reduce(self.token, group=self.group)
+        else:
+            dist.all_reduce(self.token, group=self.group)
+
+
+def wait_cycles_for(seconds: float) -> int:
+    """Cycle budget of a peer wait (the kernels read clock64; 2 GHz nominal)."""
+    return max(1, int(seconds * 2.0e9))
+
+
 def shard_size(n: int, R: int, align: int) -> int:
     per = (n + R - 1) // R
     return (per + align - 1) // align * align
@@ -135,3 +167,71 @@ class GradSync:
 
     def all(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         self.bucket(0, self.n, stream)
+
+
+def check_against_nccl(group, device: torch.device, n: int, buckets, lr: float = 0.7, momentum: float = 0.9,
+                       seed: int = 1234) -> dict:
+    """Run the fused collectives once on fresh buffers of a stage's real size and bucket list and compare
+    them with the library route (NCCL all-reduce + separate update) on the same values.
+
+    Returns ``{"status": "ok" | "mismatch" | "n/a", ...}`` with the largest absolute differences; every rank
+    of ``group`` must call it (it allocates symmetric buffers collectively).  Meant for places where the
+    multi-GPU path has to prove itself on the box it runs on, e.g. the benchmark outside its timed regions."""
+    R = dist.get_world_size(group) if group is not None else 1
+    if R == 1:
+        return {"status": "n/a", "why": "one replica per stage: no stage-wide collective runs"}
+    rank = dist.get_rank(group)
+    status = Status(device)
+    g = torch.Generator(device=device).manual_seed(seed + rank)
+    out = {"status": "ok", "replicas": R, "elements": n, "buckets": len(buckets)}
+
+    def worst(x: torch.Tensor) -> float:
+        t = x.abs().max().reshape(1).to(torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.item())
+
+    # ---- per-step gradient all-reduce, fp32 and bf16 wire, bucket by bucket as the engine sends them
+    for wire in (False, True):
+        buf = SymmetricBuffer(n * 4, device, group)
+        grad = buf.view(torch.float32, n)
+        grad.copy_(torch.randn(n, device=device, generator=g) * 1e-2)
+        ref = grad.clone()
+        dist.all_reduce(ref, group=group)
+        ref.div_(R)
+        gs = GradSync(buf, n, device, group, wire_bf16=wire, status=status)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group, device_ids=[device.index])
+        for off, cnt in buckets:
+            gs.bucket(off, cnt)
+        torch.cuda.synchronize(device)
+        err = worst(grad - ref)
+        tol = 5e-4 if wire else 1e-6        # bf16 wire: two roundings of values up to about 6e-2
+        out["grad_allreduce_bf16_wire_max_err" if wire else "grad_allreduce_f32_max_err"] = err
+        if not err <= tol:
+            out["status"] = "mismatch"
+        dist.barrier(group=group, device_ids=[device.index])
+    # ---- DiLoCo outer sync
+    theta_buf = SymmetricBuffer(n * 4, device, group)
+    theta = theta_buf.view(torch.float32, n)
+    common = torch.Generator(device=device).manual_seed(seed)
+    theta_g = torch.randn(n, device=device, generator=common)
+    theta.copy_(theta_g)                                   # OuterSync takes its shard of the global weights from here
+    sync = OuterSync(theta_buf, n, device, lr, momentum, True, group, status)
+    theta.add_(torch.randn(n, device=device, generator=g) * 1e-2)       # H inner steps' worth of drift, per replica
+    delta = theta_g - theta
+    dist.all_reduce(delta, group=group)
+    delta.div_(R)
+    ref = theta_g - lr * (delta + momentum * delta)        # first Nesterov step: buffer = delta
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group, device_ids=[device.index])
+    sync.step()
+    torch.cuda.synchronize(device)
+    err = worst(theta - ref)
+    out["outer_sync_max_err"] = err
+    if not err <= 1e-5:
+        out["status"] = "mismatch"
+    code = status.read()
+    if code != 0:
+        out["status"], out["kernel_status"] = "mismatch", code
+    dist.barrier(group=group, device_ids=[device.index])
+    return out

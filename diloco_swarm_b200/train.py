@@ -135,6 +135,9 @@ class Trainer:
         self.last_enqueue_s: float = 0.0
         self.timer = PhaseTimer(self.device, nvtx=os.environ.get("DSWARM_NVTX", "0") == "1")
         self.last_phase_ms: Dict[str, float] = {}
+        self.last_sync_phase_ms: Dict[str, float] = {}
+        self.step_timed_out = False  # the last step ran past train.step_timeout (NCCL: warned, then drained)
+        self.timeouts_seen = 0
 
     # ------------------------------------------------------------------
     def _plan(self, step: int, phase: int, forward_only: bool):
@@ -161,7 +164,10 @@ class Trainer:
         """Brackets one forward / backward of the step: a span on the timeline, and the compute time per
         microbatch when routing adapts to measured speeds (device time on GPUs, events on the compute
         stream after the wait for the op's input; wall time on CPU)."""
-        return self._both(self._traced(name), self._measured()) if self.adaptive else self._traced(name)
+        sw = self.config.swarm
+        if self.adaptive or (sw.straggler_rank == self.world.rank and sw.straggler_ms > 0):
+            return self._both(self._traced(name), self._measured())
+        return self._traced(name)
 
     def _measured(self):
         sw = self.config.swarm
@@ -259,6 +265,27 @@ class Trainer:
                     comm.send_backward(dx, op.prev)
         comm.end_step()
 
+    def _watch_step_deadline(self, step: int, deadline: float) -> None:
+        """Step timeout on NCCL.  The reference warns and leaves its event loop when a step takes longer than
+        ``train.step_timeout`` and still reaches the barrier (src/train.py:186,245).  Here the whole step is
+        already queued on the device when the host gets here, and a posted NCCL transfer cannot be withdrawn, so
+        the host watches an event at the end of the step's work: past the deadline it logs the reference's
+        warning once and then keeps waiting until everything posted has drained (the slow peer does arrive, or
+        the process group's own timeout ends the job), so that no leftover of this step can meet the next one.
+        The step's update is applied: unlike the reference's abandoned loop, every microbatch did finish."""
+        done = torch.cuda.Event()
+        done.record()
+        self.step_timed_out = False
+        while not done.query():
+            if time.time() > deadline:
+                self.step_timed_out = True
+                self.timeouts_seen += 1
+                self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
+                self.logger.log_message(f"Step {step}: waiting for the transfers already posted to drain",
+                                        master=False, level=Level.WARNING)
+                break
+            time.sleep(0.0005)
+
     def train_step(self, step: int, batch: Dict[str, torch.Tensor]) -> Tuple[Outputs, Optional[Outputs]]:
         cfg, w, eng, comm = self.config, self.world, self.engine, self.comm
         start = time.time()
@@ -317,14 +344,18 @@ class Trainer:
                 norm = eng.optimizer_step(lr, cfg.train.max_norm)
             self.opt_steps += 1
             if do_sync and eng.has_outer:
-                with self.timer.phase("outer_sync"), self._traced("outer_sync"):
-                    eng.outer_step()
+                with self._traced("outer_sync"):
+                    eng.outer_step(timer=self.timer)     # phases "outer_wait" (replica skew) and "outer_sync"
         self.last_enqueue_s = time.time() - start   # host time to queue the whole step
+        if comm.is_nccl and w.world_size > 1 and not failed:
+            self._watch_step_deadline(step, start + cfg.train.step_timeout)
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         eng.check_status()
         self.last_phase_ms = self.timer.collect()
+        if do_sync and applied:
+            self.last_sync_phase_ms = dict(self.last_phase_ms)     # phases of the latest step that synchronised
         if self.timeline is not None:
             self.timeline.end_step()
         if self.adaptive and w.world_size > 1:

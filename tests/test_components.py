@@ -343,3 +343,28 @@ def test_wandb_run_per_rank_in_offline_mode(tmp_path, monkeypatch):
     lg.close()
     assert lg.wandb_run is None
     assert any(d.startswith("offline-run") for d in os.listdir(tmp_path / "w" / "wandb"))
+
+
+def test_dropout_is_applied_by_the_autograd_stage_in_training_only():
+    """model.dropout (reference: src/model.py:48-49,67,86,114): active in training mode, off in evaluation,
+    and a model built with dropout = 0 is unaffected."""
+    import torch
+    from diloco_swarm_b200.models.gpt2 import GPT2Config, TorchStage
+    cfg = dict(block_size=32, vocab_size=64, n_layer=2, n_head=2, n_embd=32)
+    ids = torch.randint(0, 64, (2, 16))
+    plain, drop = TorchStage(GPT2Config(**cfg)), TorchStage(GPT2Config(**cfg, dropout=0.5))
+    drop.eval(); plain.eval()
+    assert torch.equal(drop(input_ids=ids), plain(input_ids=ids))          # same seeded weights, dropout off
+    drop.train(); plain.train()
+    a, b = drop(input_ids=ids), drop(input_ids=ids)
+    assert not torch.equal(a, b)                                             # fresh masks per call
+    assert torch.equal(plain(input_ids=ids), plain(input_ids=ids))
+
+
+def test_stage_rendezvous_is_a_no_op_without_replicas():
+    import torch
+    from diloco_swarm_b200.parallel.collectives import StageRendezvous, wait_cycles_for
+    r = StageRendezvous(None, torch.device("cpu"))
+    r.meet()
+    assert r.count == 0
+    assert wait_cycles_for(2.0) == 4_000_000_000 and wait_cycles_for(0.0) == 1

@@ -21,12 +21,12 @@ LOG = "/tmp/dsw_tests/gpu_multi"
 _port = [29700]
 
 
-def _run(run_id, nproc, stages, extra=()):
+def _run(run_id, nproc, stages, extra=(), engine="b200", timeout=300):
     shutil.rmtree(f"{LOG}/{run_id}", ignore_errors=True)
     _port[0] += 3
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_port[0]), "-m", "diloco_swarm_b200.train",
-           "--swarm.num_stages", str(stages), "--engine", "b200", "--model", "@configs/model/gpt2-tiny.toml",
+           "--swarm.num_stages", str(stages), "--engine", engine, "--model", "@configs/model/gpt2-tiny.toml",
            "--model.n_head", "2",                      # head size 64: the tcgen05 attention kernels
            "--data", "@configs/data/synthetic-zipf.toml", "--data.num_examples", "256", "--data.seq_length", "128",
            "--train.inner_optimizer", "@configs/optimizer/adamw.toml", "--train.inner_optimizer.lr", "0.003",
@@ -35,7 +35,7 @@ def _run(run_id, nproc, stages, extra=()):
            "--train.step_timeout", "30", "--eval.enable", "false", "--sample.enable", "false",
            "--logging.log_dir", LOG, "--logging.run_id", run_id, "--logging.console.log_level", "ERROR"] + list(extra)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    p = subprocess.run(cmd, cwd=ROOT, env=env, timeout=300, capture_output=True, text=True)
+    p = subprocess.run(cmd, cwd=ROOT, env=env, timeout=timeout, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr[-3000:]
     text = open(f"{LOG}/{run_id}/master.log").read()
     return [float(x) for x in re.findall(r"\[TRAIN\] Step: \d+ - Time: [\d.]+s - Loss: ([\d.]+)", text)]
@@ -71,3 +71,32 @@ def test_swarm_2x2_matches_pipeline_2x1():
     pipe = _run("pp2", 2, 2)
     swarm = _run("sw4", 4, 2)
     assert max(abs(a - b) for a, b in zip(pipe, swarm)) < 5e-3, (pipe, swarm)
+
+
+def test_step_timeout_on_nccl_warns_then_drains():
+    """A host-side straggler (a finite sleep per microbatch on rank 0, far below the process-group timeout)
+    makes rank 1 wait longer than train.step_timeout: it must log the reference's warning, let everything
+    posted drain, and the run must finish with the same losses as the undisturbed pipeline."""
+    _need(2)
+    calm = _run("pp2_calm", 2, 2, ["--train.max_steps", "3"])
+    slow = _run("pp2_slow", 2, 2, ["--train.max_steps", "3", "--train.step_timeout", "1",
+                                   "--swarm.straggler_rank", "0", "--swarm.straggler_ms", "200"])
+    assert len(calm) == len(slow) == 3
+    assert max(abs(a - b) for a, b in zip(calm, slow)) < 5e-3, (calm, slow)
+    log1 = open(f"{LOG}/pp2_slow/1.log").read()
+    assert "Train step 1 timed out" in log1 and "to drain" in log1
+    assert "timed out" not in open(f"{LOG}/pp2_calm/1.log").read()
+
+
+def test_replica_leaves_between_steps_on_gpus():
+    """Membership change in the form that is safe on shared GPUs: a replica announces its leave, finishes its
+    step and exits with nothing in flight; the others learn of it on the host before their next launch and
+    re-route (autograd engine on NCCL groups, NVLS off, no multimem)."""
+    _need(4)
+    losses = _run("leave_gpu", 4, 2, ["--elastic.enable", "true", "--elastic.timeout", "30", "--elastic.leave_rank", "2",
+                                      "--elastic.leave_after_step", "2", "--train.max_steps", "5",
+                                      "--train.step_timeout", "5"], engine="torch", timeout=180)
+    assert len(losses) == 5 and all(l == l for l in losses)
+    text = open(f"{LOG}/leave_gpu/master.log").read() + open(f"{LOG}/leave_gpu/0.log").read()
+    assert "ranks [2] are gone" in text
+    assert "Rank 2 leaves after step 2" in open(f"{LOG}/leave_gpu/2.log").read()
