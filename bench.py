@@ -301,7 +301,9 @@ def run_ours(args) -> dict:
         "config": {"model": f"gpt2-{args.model}", "global_batch": args.batch, "seq_len": args.seq,
                    "micro_batch": args.micro_batch, "parallelism": f"{S} stages x {R} replicas",
                    "algorithm": "swarm" if args.no_outer else f"diloco-swarm H={H}",
-                   "max_micro_batches": args.cap, "layer_split": args.layer_split, "engine": args.engine,
+                   "max_micro_batches": args.cap, "layer_split": args.layer_split,
+                   "layers_per_stage": tr.config.swarm.layer_split if S > 1 else str(tr.config.model.n_layer),
+                   "engine": args.engine,
                    "collective": args.collective,
                    "routing": args.routing, **({"timeline_steps": args.timeline_steps} if args.timeline_steps else {}),
                    "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},

@@ -104,7 +104,7 @@ outer_sync_kernel(OuterArgs a) {
     float4 s[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      if (idx[u] < hi) {
+      if (idx[u] < hi && DSW_OK(idx[u] >= 0 && idx[u] + 4 <= a.n)) {
 #pragma unroll
         for (int j = 0; j < MAX_PEERS; ++j) {
           if (j < a.R) {
@@ -169,7 +169,7 @@ grad_allreduce_f32_kernel(GradArgs a) {
     float4 s[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      if (idx[u] < hi) {
+      if (idx[u] < hi && DSW_OK(idx[u] >= 0 && idx[u] + 4 <= a.offset + a.count)) {
 #pragma unroll
         for (int j = 0; j < MAX_PEERS; ++j) {
           if (j < a.R) {
@@ -205,6 +205,7 @@ grad_allreduce_bf16_kernel(GradArgs a) {
   // phase 0: own fp32 gradient -> bf16 staging (peer-visible), every slice
   if (a.phase_mask & 1) {
     dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
+      if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
       const float4 x = ld_f4(a.grad + i), y = ld_f4(a.grad + i + 4);
       *reinterpret_cast<uint4*>(stage + i) =
           make_uint4(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w), pack_bf16(y.x, y.y), pack_bf16(y.z, y.w));
@@ -214,6 +215,7 @@ grad_allreduce_bf16_kernel(GradArgs a) {
   // phase 1: reduce my slice over all peers in fp32, scale, send back as bf16
   if (a.phase_mask & 2) {
     dsw_for_each_owned(a.offset, a.count, a.shard, a.rank, a.rank + 1, tid, nth, 8, [&](long long i) {
+      if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
       float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int j = 0; j < MAX_PEERS; ++j) {
@@ -235,6 +237,7 @@ grad_allreduce_bf16_kernel(GradArgs a) {
   // phase 2: widen the averaged bucket into the fp32 main gradient, every slice
   if (a.phase_mask & 4) {
     dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
+      if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
       const uint4 u = *reinterpret_cast<const uint4*>(stage + i);
       const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
       st_f4(a.grad + i, make_float4(f0.x, f0.y, f1.x, f1.y));
@@ -312,6 +315,8 @@ extern "C" int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* 
   else           grad_allreduce_f32_kernel<<<blocks, 512, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+DSW_BOUNDS_TU(dsw_bounds_collectives)
 
 extern "C" int dsw_load_collectives() {
   cudaFuncAttributes a;

@@ -129,6 +129,20 @@ int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* grad, long 
                        long long shard, int rank, int R, int wire_bf16, unsigned seq, long long wait_limit,
                        int use_barrier, int phase_mask, int blocks, int* status, cudaStream_t st);
 
+// ---------------------------------------------------------------- bounds-checking build (-DDSWARM_BOUNDS)
+// First failed bounds check since the last call: 0 = none, else 100000 * unit + source line (units: 1
+// elementwise.cu, 2 optim.cu, 3 collectives.cu, 4 gemm_one_cta.cu, 5 gemm_pair.cu).  The shipped build has no
+// checks and returns 0.  The per-unit readers return that unit's line.
+int dsw_bounds_status();
+int dsw_bounds_elementwise();
+int dsw_bounds_optim();
+int dsw_bounds_collectives();
+int dsw_bounds_gemm_one_cta();
+int dsw_bounds_gemm_pair();
+// Bounds build: one check fails on purpose, without touching memory, so that the report path can be tested
+// (returns 1); shipped build: nothing happens (returns 0).
+int dsw_bounds_selftest(cudaStream_t st);
+
 // ---------------------------------------------------------------- module loading
 // Load every kernel of a source file on the current device now, so that no first launch has to wait for
 // the device to go idle while a pipeline receive is spinning on it.

@@ -59,12 +59,14 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 }
 
 template <int NCH>
-__device__ __forceinline__ void ln_load_row(uint4 (&o)[NCH], const __nv_bfloat16* __restrict__ x, int row, int d, int lane) {
+__device__ __forceinline__ void ln_load_row(uint4 (&o)[NCH], const __nv_bfloat16* __restrict__ x, int row, int d, int lane,
+                                            int M) {
   const __nv_bfloat16* xr = x + (long long)row * d;
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int col = c * 256 + lane * 8;
-    o[c] = col < d ? *reinterpret_cast<const uint4*>(xr + col) : make_uint4(0, 0, 0, 0);
+    o[c] = (col < d && DSW_OK(row >= 0 && row < M && col + 8 <= d)) ? *reinterpret_cast<const uint4*>(xr + col)
+                                                                   : make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -90,10 +92,10 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
   }
   const float inv_d = 1.f / d;
   uint4 cur[NCH], nxt[NCH];
-  ln_load_row<NCH>(cur, x, row, d, lane);
+  ln_load_row<NCH>(cur, x, row, d, lane, M);
   for (; row < M; row += stride) {
     const bool more = row + stride < M;
-    if (more) ln_load_row<NCH>(nxt, x, row + stride, d, lane);
+    if (more) ln_load_row<NCH>(nxt, x, row + stride, d, lane, M);
     float s = 0.f;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
@@ -119,7 +121,7 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int col = c * 256 + lane * 8;
-      if (col < d) {
+      if (col < d && DSW_OK(row < M && col + 8 <= d)) {
         float v[8], o[8];
         unpack8(cur[c], v);
 #pragma unroll
@@ -160,7 +162,7 @@ __device__ __forceinline__ void ln_bwd_load(LnBwdRow<NCH>& o, const __nv_bfloat1
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int col = c * 256 + lane * 8;
-    if (c < nch && col < d) {
+    if (c < nch && col < d && DSW_OK(row >= 0 && col + 8 <= d)) {
       o.x[c] = *reinterpret_cast<const uint4*>(x + off + col);
       o.dy[c] = *reinterpret_cast<const uint4*>(dy + off + col);
       if (dres) o.r[c] = *reinterpret_cast<const uint4*>(dres + off + col);
@@ -282,7 +284,7 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           o[j] = rstd * (dv[j] * g[j] - s1 - (xh[j] - mean) * rstd * s2) + (dres ? r[j] : 0.f);
-        store8(dx + off + col, o);
+        if (DSW_OK(row < M && col + 8 <= d)) store8(dx + off + col, o);
       }
     }
     if (PREFETCH) cur = nxt;
@@ -344,6 +346,7 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restri
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < N) {
     for (int row = blockIdx.y * 8 + rl; row < M; row += gridDim.y * 8) {
+      if (!DSW_OK(col + 8 <= N && col + 8 <= ld)) continue;
       float v[8];
       load8(x + (long long)row * ld + col, v);
 #pragma unroll
@@ -374,6 +377,7 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const float* __restrict_
     const int row = int(i / per_row), col = int(i % per_row) * 8;
     long long id = ids[row];
     if (id < 0 || id >= V) { if (status) atomicCAS(status, 0, ST_BAD_ARG); id = 0; }
+    if (!DSW_OK(row < BT && col + 8 <= d && id >= 0 && id < V)) continue;
     float a[8], b[8], o[8];
     load8f(wte + id * d + col, a);
     load8f(wpe + (long long)(row % T) * d + col, b);
@@ -490,6 +494,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lon
   }
   float mx = -INFINITY, sm = 0.f;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    if (!DSW_OK(i * 8 + 8 <= V && V <= ld)) continue;
     float v[8];
     load8(lr + i * 8, v);
     float m8 = v[0];
@@ -540,6 +545,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lon
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
   const long long n8 = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    if (!DSW_OK(i * 8 + 8 <= n)) continue;
     float v[8];
     load8f(src + i * 8, v);
     store8(dst + i * 8, v);
@@ -674,6 +680,43 @@ extern "C" int dsw_cast_f32_bf16(const float* src, void* dst, long long n, cudaS
 extern "C" int dsw_cast_bf16_f32(const void* src, float* dst, long long n, cudaStream_t st) {
   cast_bf16_f32_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)src, dst, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+DSW_BOUNDS_TU(dsw_bounds_elementwise)
+
+// First failed bounds check since the last call: 0 = none, else 100000 * unit + source line (unit 1 =
+// elementwise.cu, 2 = optim.cu, 3 = collectives.cu, 4 = gemm_one_cta.cu, 5 = gemm_pair.cu); -1 if a word
+// could not be read.  Always 0 in the shipped build; synchronises the device in the bounds build.
+extern "C" int dsw_bounds_status() {
+  int (*units[])() = {dsw_bounds_elementwise, dsw_bounds_optim, dsw_bounds_collectives, dsw_bounds_gemm_one_cta,
+                      dsw_bounds_gemm_pair};
+  int first = 0;
+  for (int u = 0; u < 5; ++u) {
+    const int v = units[u]();
+    if (v < 0) return -1;
+    if (v > 0 && first == 0) first = 100000 * (u + 1) + v;
+  }
+  return first;
+}
+
+#ifdef DSWARM_BOUNDS
+namespace dsw {
+__global__ void bounds_selftest_kernel(int n) {
+  // no memory is touched: the check itself is what is exercised
+  if (DSW_OK(n < 0)) return;
+}
+}  // namespace dsw
+#endif
+// Bounds build: makes one check fail on purpose (without touching memory) so that a test can see the report path
+// work; returns 1 if a kernel was launched.  Shipped build: does nothing and returns 0.
+extern "C" int dsw_bounds_selftest(cudaStream_t st) {
+#ifdef DSWARM_BOUNDS
+  dsw::bounds_selftest_kernel<<<1, 32, 0, st>>>(1);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+#else
+  (void)st;
+  return 0;
+#endif
 }
 
 extern "C" int dsw_load_elementwise() {

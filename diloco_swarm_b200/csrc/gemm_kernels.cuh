@@ -185,6 +185,7 @@ __device__ __forceinline__ void epilogue_warp(const GemmArgs& g, uint32_t t_addr
       unstage_rows64(stage, lane, [&](int i, int rl, int ch, uint4 d) {
         const int row = row_base + rl, col = cb + ch * 8;
         if (row >= g.M || col >= g.N) return;
+        if (!DSW_OK(col + 8 <= g.N && col + 8 <= g.ldo && rl >= 0 && rl < 32)) return;
         if constexpr (EXTRA) {
           uint32_t du[4] = {d.x, d.y, d.z, d.w};
           const uint32_t xu[4] = {x[i].x, x[i].y, x[i].z, x[i].w};

@@ -1,6 +1,7 @@
 // Instantiations and launcher of the one-CTA tcgen05 GEMM kernel (gemm_kernels.cuh): 128 x 128 and
 // 128 x 256 tiles, one instantiation per epilogue class.
 #include "gemm_kernels.cuh"
+#include "dswarm.h"
 
 namespace dsw {
 
@@ -58,6 +59,10 @@ int launch_one_cta(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const G
   if (bn == 256) return launch_bn<256, 4>(ta, tb, g, num_sms, max_ctas, st);
   return launch_bn<128, 6>(ta, tb, g, num_sms, max_ctas, st);
 }
+
+}  // namespace dsw
+DSW_BOUNDS_TU(dsw_bounds_gemm_one_cta)
+namespace dsw {
 
 int load_one_cta_kernels() { return (load_bn<256, 4>() | load_bn<128, 6>()) ? -1 : 0; }
 

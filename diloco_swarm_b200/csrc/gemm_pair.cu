@@ -1,6 +1,7 @@
 // Instantiations and launcher of the CTA-pair tcgen05 GEMM kernel (gemm_kernels.cuh): 256 x 256 tiles on
 // two CTAs of a cluster (cta_group::2), one instantiation per epilogue class.
 #include "gemm_kernels.cuh"
+#include "dswarm.h"
 
 namespace dsw {
 
@@ -39,6 +40,10 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g,
     default: return -13;
   }
 }
+
+}  // namespace dsw
+DSW_BOUNDS_TU(dsw_bounds_gemm_pair)
+namespace dsw {
 
 int load_pair_kernels() {
   cudaFuncAttributes a;

@@ -18,6 +18,7 @@ sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) 
   const long long n4 = n / 4;
   const float4* g4 = reinterpret_cast<const float4*>(g);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    if (!DSW_OK(4 * i + 4 <= n)) continue;
     const float4 v = g4[i];
     acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
@@ -51,6 +52,7 @@ adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m
   const float decay = 1.f - lr * wd;
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    if (!DSW_OK(4 * i + 4 <= n)) continue;
     float4 pp = reinterpret_cast<float4*>(p)[i];
     float4 gg = reinterpret_cast<float4*>(g)[i];
     float4 mm = reinterpret_cast<float4*>(m)[i];
@@ -89,6 +91,7 @@ sgd_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ buf
            long long n, float lr, float mu, int nesterov, const float* __restrict__ coef_ptr, int zero_grad) {
   const float coef = coef_ptr ? coef_ptr[0] : 1.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    if (!DSW_OK(i >= 0 && i < n)) continue;
     const float gr = g[i] * coef;
     float upd = gr;
     if (mu != 0.f) {
@@ -134,6 +137,8 @@ extern "C" int dsw_sgd(float* p, float* g, float* buf, void* p16, long long n, f
   sgd_kernel<<<148 * 4, 512, 0, st>>>(p, g, buf, (__nv_bfloat16*)p16, n, lr, mu, nesterov, coef, zero_grad);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+DSW_BOUNDS_TU(dsw_bounds_optim)
 
 extern "C" int dsw_load_optim() {
   cudaFuncAttributes a;

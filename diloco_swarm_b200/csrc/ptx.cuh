@@ -18,6 +18,28 @@ enum : int {
   ST_BAD_ARG = 3,
 };
 
+// ---------------------------------------------------------------- bounds-checking build
+// The stand-in for a memory sanitizer: with -DDSWARM_BOUNDS every global access of the memory-bound
+// kernels, the optimiser kernels, the fused collectives and the GEMM epilogue is preceded by a check of
+// the element offset it is about to use against the extent the launcher was given.  An access that
+// fails the check is skipped (nothing faults) and the source line of the first failure in this
+// translation unit is kept in a device word that dsw_bounds_status() reads and clears.  In the
+// shipped build DSW_OK(cond) is the constant true and costs nothing.
+#ifdef DSWARM_BOUNDS
+static __device__ int dsw_bounds_word = 0;
+#define DSW_OK(cond) ((cond) ? true : (atomicCAS(&dsw_bounds_word, 0, __LINE__), false))
+#define DSW_BOUNDS_TU(name)                                                                   \
+  extern "C" int name() {                                                                     \
+    int v = 0, z = 0;                                                                         \
+    if (cudaMemcpyFromSymbol(&v, dsw::dsw_bounds_word, sizeof(int)) != cudaSuccess) return -1;     \
+    if (cudaMemcpyToSymbol(dsw::dsw_bounds_word, &z, sizeof(int)) != cudaSuccess) return -1;       \
+    return v;                                                                                 \
+  }
+#else
+#define DSW_OK(cond) (true)
+#define DSW_BOUNDS_TU(name) extern "C" int name() { return 0; }
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

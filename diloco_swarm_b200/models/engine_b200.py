@@ -120,6 +120,7 @@ class B200Engine:
         self.buckets = self._make_buckets()
         self._buckets_sent = 0
         self._overlap = os.environ.get("DSWARM_GRAD_OVERLAP", "1") != "0"
+        self._canary_every_step = os.environ.get("DSWARM_CANARY_CHECK", "0") == "1"
 
     # ------------------------------------------------------------------ views
     def _slice(self, buf: torch.Tensor, key: str) -> torch.Tensor:
@@ -179,6 +180,19 @@ class B200Engine:
 
     def check_status(self) -> None:
         self.status.raise_if_set()
+        if self._canary_every_step:
+            for buf in self.symmetric_buffers():
+                buf.check_canaries()
+
+    def symmetric_buffers(self):
+        """Every peer-mapped buffer of this stage (weights, gradient, the collectives' flags and staging)."""
+        out = [self.theta_buf, self.grad_buf]
+        for obj in (self.outer, self.grad_sync):
+            for name in ("flags", "stage_buf"):
+                b = getattr(obj, name, None) if obj is not None else None
+                if b is not None:
+                    out.append(b)
+        return out
 
     def warmup(self, B: int, T: int) -> None:
         """Run every code path of a step once on dummy data of the real shape, then

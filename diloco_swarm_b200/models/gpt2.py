@@ -35,33 +35,74 @@ class GPT2Config:
     parameter_sharing: bool = False
 
 
+# Cost of the non-block parts of a stage in units of one transformer block, as measured on B200 for a
+# 16k-token GPT-2 small microbatch (block 1.21 ms; final LayerNorm + LM head + loss 3.9 ms, which by FLOPs
+# alone would be V / (12 d) = 5.5 blocks: a block also carries attention, LayerNorms and bias work;
+# embedding forward + backward 0.2 ms).
+HEAD_COST_PER_FLOP_BLOCK = 0.59
+EMBED_COST_BLOCKS = 0.15
+FWD_SHARE = 0.32          # forward part of a block's (and the head's) forward + backward time
+
+
+def stage_cost_blocks(n_blocks: int, first: bool, last: bool, n_embd: int, vocab_size: int) -> float:
+    """Forward + backward time of a stage per microbatch, in units of one transformer block."""
+    c = float(n_blocks)
+    if first:
+        c += EMBED_COST_BLOCKS
+    if last:
+        c += HEAD_COST_PER_FLOP_BLOCK * vocab_size / (12.0 * n_embd)
+    return c
+
+
+def balanced_split(n_layer: int, num_stages: int, n_embd: int, vocab_size: int,
+                   loads: Optional[Sequence[float]] = None) -> List[int]:
+    """Blocks per stage (each at least one) that minimise the busiest stage's time per step,
+    max over stages of load_s * cost_s.  ``loads`` = microbatches the busiest replica of each stage serves
+    per step (all equal when omitted): under uniform stochastic wiring the later stages' busiest replicas
+    get more than their even share, so they should carry less work per microbatch."""
+    S = num_stages
+    if S > n_layer:
+        raise ValueError(f"{S} stages need at least {S} layers")
+    w = [1.0] * S if loads is None else [float(x) for x in loads]
+    INF = float("inf")
+    # dp[s][i]: best bottleneck with stages 0..s covering blocks 0..i-1; second key = sum of squares (evenness)
+    dp = [[(INF, INF)] * (n_layer + 1) for _ in range(S)]
+    cut = [[0] * (n_layer + 1) for _ in range(S)]
+    for i in range(1, n_layer + 1):
+        c = w[0] * stage_cost_blocks(i, True, S == 1, n_embd, vocab_size)
+        dp[0][i] = (c, c * c)
+    for s in range(1, S):
+        for i in range(s + 1, n_layer + 1):
+            for j in range(s, i):
+                if dp[s - 1][j][0] == INF:
+                    continue
+                c = w[s] * stage_cost_blocks(i - j, False, s == S - 1, n_embd, vocab_size)
+                cand = (max(dp[s - 1][j][0], c), dp[s - 1][j][1] + c * c)
+                if cand < dp[s][i]:
+                    dp[s][i], cut[s][i] = cand, j
+    counts, i = [0] * S, n_layer
+    for s in range(S - 1, 0, -1):
+        j = cut[s][i]
+        counts[s], i = i - j, j
+    counts[0] = i
+    return counts
+
+
 def split_layers(n_layer: int, num_stages: int, mode: str = "even",
                  n_embd: int = 768, vocab_size: int = 50304) -> List[List[int]]:
     """Block indices per stage.
 
     "even": n_layer // S each, remainder to the first stages (src/model.py:195-198).
-    "balanced": gives the last stage fewer blocks to make room for the LM head and
-    the loss.  By FLOPs the head equals V/(12 d) blocks; measured on B200 (GPT-2
-    small: block 1.4 ms, head + loss 5.2 ms per 16k-token microbatch) it costs about
-    0.68 of that, because a block also carries attention, LayerNorms and bias work.
+    "balanced": fewer blocks on the last stage to make room for the LM head and the loss
+    (``balanced_split`` with equal loads; the trainer replaces "balanced" by the explicit counts it gets
+    with the loads of the run's routing before it builds the stage).
     "a,b,c": explicit counts.
     """
     S = num_stages
     if mode == "even":
         counts = [n_layer // S + (1 if i < n_layer % S else 0) for i in range(S)]
     elif mode == "balanced":
-        head_blocks = 0.68 * vocab_size / (12.0 * n_embd)
-        per = (n_layer + head_blocks) / S
-        counts = [0] * S
-        left = n_layer
-        for s in range(S - 1, -1, -1):
-            want = per - (head_blocks if s == S - 1 else 0.0)
-            c = int(round(want)) if s > 0 else left
-            c = max(1 if left - (s) >= 1 else 0, min(c, left - s))
-            counts[s] = c
-            left -= c
-        if sum(counts) != n_layer:
-            counts[0] += n_layer - sum(counts)
+        counts = balanced_split(n_layer, S, n_embd, vocab_size)
     else:
         counts = [int(x) for x in mode.split(",")]
         if len(counts) != S or sum(counts) != n_layer:

@@ -87,6 +87,20 @@ def route(seed: int, step: int, num_stages: int, world_size: int, num_micro_batc
     return path
 
 
+def busiest_replica_loads(seed: int, num_stages: int, world_size: int, num_micro_batches: int, mode: str = "uniform",
+                          weights: Optional[Sequence[float]] = None, steps: int = 64) -> List[float]:
+    """Microbatches per step that the busiest replica of each stage serves, averaged over the first ``steps``
+    steps of the run's own routing.  Under uniform stochastic wiring the first stage is even (roots are dealt
+    round-robin) and every later stage's busiest replica gets clearly more than M / R (about 10.5 of 32
+    with four replicas); the step time follows the busiest replica, so the layer split weighs stages by this."""
+    out = [0.0] * num_stages
+    for step in range(1, steps + 1):
+        path = route(seed, step, num_stages, world_size, num_micro_batches, None, mode=mode, weights=weights)
+        for s in range(num_stages):
+            out[s] += float(np.bincount(path[:, s], minlength=world_size).max())
+    return [x / steps for x in out]
+
+
 def plan(path: np.ndarray, world_size: int, rank: int, cap: int, forward_only: bool = False,
          cost_f: Optional[Sequence[float]] = None, cost_b: Optional[Sequence[float]] = None) -> List[Op]:
     """Ordered forward/backward ops of ``rank`` for one step."""

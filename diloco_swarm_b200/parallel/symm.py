@@ -20,6 +20,12 @@ from ..ops._lib import check, cuda_lib
 MAX_PEERS = 8
 FLAG_BLOCKS = 148          # csrc/dswarm.h: DSW_MAX_COLL_BLOCKS
 FLAG_WORDS = FLAG_BLOCKS * MAX_PEERS
+GUARD_BYTES = 256          # canary zone in front of and behind every symmetric buffer
+CANARY = 0xC5
+
+
+class CanaryError(RuntimeError):
+    """Something wrote outside a symmetric buffer (into the guard zone in front of or behind it)."""
 
 
 class _CudaArray:
@@ -38,12 +44,19 @@ class SymmetricBuffer:
         lib = cuda_lib()
         self.device = device
         self.nbytes = (nbytes + 255) // 256 * 256
+        # Peers store into these buffers with plain pointers, and the sanitizer tools are closed on shared GPUs,
+        # so every buffer sits between two guard zones filled with a fixed byte; check_canaries() (called when
+        # the buffer is closed, and per step with DSWARM_CANARY_CHECK=1) tells whether a store went astray.
         p = ctypes.c_void_p()
         with torch.cuda.device(device):
-            check(lib.dsw_symm_alloc(self.nbytes, ctypes.byref(p)), "dsw_symm_alloc")
-        self.ptr = p.value
+            check(lib.dsw_symm_alloc(self.nbytes + 2 * GUARD_BYTES, ctypes.byref(p)), "dsw_symm_alloc")
+        self._base = p.value
+        self.ptr = self._base + GUARD_BYTES
         self._imported: List[int] = []
-        self.local = torch.as_tensor(_CudaArray(self.ptr, self.nbytes, self), device=device)
+        self._whole = torch.as_tensor(_CudaArray(self._base, self.nbytes + 2 * GUARD_BYTES, self), device=device)
+        self._whole[:GUARD_BYTES].fill_(CANARY)
+        self._whole[GUARD_BYTES + self.nbytes:].fill_(CANARY)
+        self.local = self._whole[GUARD_BYTES:GUARD_BYTES + self.nbytes]
         R = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
         self.rank_in_group = dist.get_rank(group) if R > 1 else 0
         self.peer_ptrs: List[int] = [self.ptr]
@@ -51,7 +64,7 @@ class SymmetricBuffer:
             if R > MAX_PEERS:
                 raise ValueError(f"at most {MAX_PEERS} replicas per stage")
             handle = (ctypes.c_char * 64)()
-            check(lib.dsw_symm_export(self.ptr, handle), "dsw_symm_export")
+            check(lib.dsw_symm_export(self._base, handle), "dsw_symm_export")
             mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(device)
             gathered = [torch.empty_like(mine) for _ in range(R)]
             dist.all_gather(gathered, mine, group=group)
@@ -65,7 +78,7 @@ class SymmetricBuffer:
                 with torch.cuda.device(device):
                     check(lib.dsw_symm_import(raw, ctypes.byref(q)), "dsw_symm_import")
                 self._imported.append(q.value)
-                self.peer_ptrs.append(q.value)
+                self.peer_ptrs.append(q.value + GUARD_BYTES)        # the peer's payload starts behind its front guard
         self.R = R
         self._table = (ctypes.c_void_p * MAX_PEERS)(*[ctypes.c_void_p(x) for x in self.peer_ptrs])
 
@@ -78,15 +91,30 @@ class SymmetricBuffer:
         t = self.local[byte_offset:].view(dtype)
         return t if numel is None else t[:numel]
 
+    def check_canaries(self) -> None:
+        """Raise ``CanaryError`` if a guard zone of this rank's buffer no longer holds the canary byte
+        (one small device-to-host read; synchronises the current stream)."""
+        if not self._base:
+            return
+        front = self._whole[:GUARD_BYTES]
+        back = self._whole[GUARD_BYTES + self.nbytes:]
+        bad = [name for name, z in (("in front of", front), ("behind", back)) if not bool((z == CANARY).all())]
+        if bad:
+            raise CanaryError(f"the guard zone {' and '.join(bad)} a symmetric buffer of {self.nbytes} bytes was "
+                              "overwritten: a kernel stored outside the buffer")
+
     def close(self) -> None:
         lib = cuda_lib()
         for q in self._imported:
             lib.dsw_symm_unimport(q)
         self._imported = []
-        if self.ptr:
-            self.local = None
-            lib.dsw_symm_free(self.ptr)
-            self.ptr = 0
+        if self._base:
+            try:
+                self.check_canaries()
+            finally:
+                self.local = self._whole = None
+                lib.dsw_symm_free(self._base)
+                self._base = self.ptr = 0
 
 
 class LocalPeerSet:

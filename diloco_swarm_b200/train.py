@@ -92,7 +92,6 @@ class Trainer:
         self.logger = logger or Logger(w, config.logging)
         seed_everything(config.train.seed)
         torch.set_float32_matmul_precision(config.amp.precision)
-        self.engine = make_engine(config, w, self.device)
         tc = config.train
         self.seq = config.data.seq_length
         self.mbs = tc.micro_batch_size
@@ -101,6 +100,8 @@ class Trainer:
         self.micro_per_device = max(1, self.num_micro // len(w.last_stage_ranks))
         self.loss_scale = 1.0 / self.micro_per_device
         self.routing_seed = config.swarm.routing_seed if config.swarm.routing_seed is not None else tc.seed
+        self._resolve_layer_split()
+        self.engine = make_engine(config, w, self.device)
         self.comm = PipelineComm(w, (self.mbs, self.seq, config.model.n_embd), self.engine.act_dtype,
                                  self.device, prefetch=max(1, config.swarm.recv_prefetch))
         if hasattr(self.engine, "warmup"):
@@ -140,6 +141,27 @@ class Trainer:
         self.timeouts_seen = 0
 
     # ------------------------------------------------------------------
+    def _resolve_layer_split(self) -> None:
+        """``layer_split = balanced`` becomes explicit block counts before the stage is built: the cut that
+        minimises the busiest stage's time per step under this run's routing (the busiest replica of a later
+        stage serves more than its even share of the microbatches when the wiring is uniformly random).
+        Also fixes the per-stage forward / backward costs that order each rank's operations in the plan:
+        with the nominal 1 : 2 of every stage the simulated arrival order differs from the real one wherever
+        stages are uneven, and a rank then waits for a tensor while another one is already there."""
+        from .models.gpt2 import FWD_SHARE, balanced_split, split_layers, stage_cost_blocks
+        sw, mc, w = self.config.swarm, self.config.model, self.world
+        S = w.num_stages
+        if sw.layer_split == "balanced" and S > 1:
+            mode = "weighted" if sw.routing == "adaptive" else sw.routing
+            weights = list(sw.routing_weights) or None
+            loads = schedule.busiest_replica_loads(self.routing_seed, S, w.world_size, self.num_micro, mode, weights)
+            counts = balanced_split(mc.n_layer, S, mc.n_embd, mc.vocab_size, loads)
+            sw.layer_split = ",".join(str(c) for c in counts)
+        layers = split_layers(mc.n_layer, S, sw.layer_split, mc.n_embd, mc.vocab_size)
+        cost = [stage_cost_blocks(len(layers[s]), s == 0, s == S - 1, mc.n_embd, mc.vocab_size) for s in range(S)]
+        self.cost_f = [FWD_SHARE * c for c in cost]
+        self.cost_b = [(1.0 - FWD_SHARE) * c for c in cost]
+
     def _plan(self, step: int, phase: int, forward_only: bool):
         w = self.world
         # phase separates the routing streams of train / eval / test steps
@@ -149,10 +171,12 @@ class Trainer:
         cap = self.config.train.max_micro_batches
         if self._verify_plans:
             # debugging aid: every rank derives all ranks' plans and replays them before it runs its own
-            every = {r: schedule.plan(path, w.world_size, r, cap, forward_only=forward_only)
+            every = {r: schedule.plan(path, w.world_size, r, cap, forward_only=forward_only,
+                                      cost_f=self.cost_f, cost_b=self.cost_b)
                      for r in range(w.world_size) if self.alive is None or self.alive[r]}
             schedule.check_plans(path, every, cap, forward_only=forward_only)
-        return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only)
+        return path, schedule.plan(path, w.world_size, w.rank, cap, forward_only=forward_only,
+                                   cost_f=self.cost_f, cost_b=self.cost_b)
 
     def _traced(self, name: str):
         """A named span on this rank's lane of the timeline, when one is being recorded."""

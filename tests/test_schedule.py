@@ -220,3 +220,31 @@ def test_check_plans_accepts_real_plans_and_names_what_is_wrong_with_broken_ones
                 p[r][0], p[r][1] = p[r][1], p[r][0]
     msg = broken(swap_first_two)
     assert "deadlock" in msg or "expected" in msg
+
+
+def test_busiest_replica_loads_and_the_split_that_follows_them():
+    """Uniform wiring: the first stage's replicas serve M / R each (roots are dealt round-robin), a later
+    stage's busiest replica clearly more; the balanced split then moves a block from the last stage to the
+    first when there are four replicas per stage, and not when there is one."""
+    from diloco_swarm_b200.models.gpt2 import balanced_split
+    loads = S.busiest_replica_loads(42, 2, 8, 32, "uniform")
+    assert loads[0] == 8.0 and 9.5 < loads[1] < 11.5
+    assert S.busiest_replica_loads(42, 2, 8, 32, "balanced") == [8.0, 8.0]
+    assert S.busiest_replica_loads(42, 2, 2, 32, "uniform") == [32.0, 32.0]
+    assert balanced_split(12, 2, 768, 50304) == [8, 4]
+    assert balanced_split(12, 2, 768, 50304, loads) == [9, 3]
+    assert balanced_split(12, 1, 768, 50304) == [12]
+    for n, st, d in ((24, 4, 1024), (36, 8, 1280), (48, 3, 1600), (4, 2, 128)):
+        c = balanced_split(n, st, d, 50304)
+        assert sum(c) == n and len(c) == st and min(c) >= 1
+
+
+def test_plans_with_stage_costs_stay_consistent():
+    """Per-stage costs change the order of a rank's operations, never their set; the plans of all ranks
+    still pass the consistency check."""
+    path = S.route(7, 3, 2, 8, 32)
+    for costs in (None, ([0.3, 1.2], [0.7, 2.4]), ([2.9, 2.4], [6.1, 5.1])):
+        kw = {} if costs is None else {"cost_f": costs[0], "cost_b": costs[1]}
+        plans = {r: S.plan(path, 8, r, 8, **kw) for r in range(8)}
+        S.check_plans(path, plans, 8)
+        assert sorted((o.kind, o.mb) for o in plans[1]) == sorted((o.kind, o.mb) for o in S.plan(path, 8, 1, 8))
