@@ -74,7 +74,8 @@ def parse_args():
                     help="diagnosis: record every rank's forwards and backwards of this many timed steps into "
                          "<log-dir>/bench<pid>/timeline (utils/timeline.py); adds events to the timed region")
     ap.add_argument("--log-dir", default=os.path.join(tempfile.gettempdir(), "dswarm_bench"))
-    ap.add_argument("--recv-prefetch", type=int, default=2, help="pipeline receives posted this many operations ahead")
+    ap.add_argument("--recv-prefetch", type=int, default=1, help="pipeline receives posted this many operations ahead")
+    ap.add_argument("--p2p", default="auto", choices=["auto", "nccl", "copy"], help="pipeline transport")
     ap.add_argument("--swarm-steps", type=int, default=-1,
                     help="timed steps of the plain-SWARM side measurement (default min(steps, 8); 0 skips it)")
     ap.add_argument("--no-collective-check", action="store_true")
@@ -148,7 +149,8 @@ def build_config(args, S: int, no_outer=None, run_suffix: str = ""):
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
         swarm={"num_stages": S, "sync_every_n_steps": 1 if no_outer else H, "layer_split": args.layer_split,
-               "collective": args.collective, "routing": args.routing, "recv_prefetch": args.recv_prefetch},
+               "collective": args.collective, "routing": args.routing, "recv_prefetch": args.recv_prefetch,
+               "p2p": args.p2p},
         eval={"enable": False}, sample={"enable": False},
         logging={"log_dir": args.log_dir,
                  "run_id": (f"bench{os.getpid()}" if args.timeline_steps == 0 else "bench") + run_suffix,
@@ -304,7 +306,7 @@ def run_ours(args) -> dict:
                    "max_micro_batches": args.cap, "layer_split": args.layer_split,
                    "layers_per_stage": tr.config.swarm.layer_split if S > 1 else str(tr.config.model.n_layer),
                    "engine": args.engine,
-                   "collective": args.collective,
+                   "collective": args.collective, "p2p": type(tr.comm).__name__,
                    "routing": args.routing, **({"timeline_steps": args.timeline_steps} if args.timeline_steps else {}),
                    "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,

@@ -64,9 +64,16 @@ class SwarmConfig(BaseConfig):
     collective: Literal["fused", "nccl"] = "fused"
     # (added) wire dtype of the per-step gradient all-reduce
     grad_wire_dtype: Literal["float32", "bfloat16"] = "float32"
-    # (added) pipeline receives posted this many operations ahead of their use (a posted NCCL receive is a
-    # resident kernel that waits for its sender, so more look-ahead hides latency but holds SM resources)
-    recv_prefetch: int = 2
+    # (added) a pipeline receive is posted this many operations of the rank's plan before the operation that
+    # consumes it (a posted NCCL receive is a resident kernel that waits for its sender, so more look-ahead
+    # hides latency but holds SMs that the persistent GEMMs want)
+    recv_prefetch: int = 1
+    # (added) pipeline transport between stages: "nccl" = isend / irecv (a waiting transfer is a resident kernel),
+    # "copy" = copy engines + stream-ordered flags into peer-mapped inboxes (no kernel at all; one node, up to 8
+    # ranks); "auto" = "copy" where that applies (CUDA, one node), else "nccl"
+    p2p: Literal["auto", "nccl", "copy"] = "auto"
+    # (added) message slots per (sender, receiver) ring of the copy transport
+    p2p_slots: int = 4
     # (added) bound of the fused collectives' waits for a peer GPU, in seconds (the kernels count clock cycles at
     # a nominal 2 GHz); a wait that runs out ends the kernel with a status that the host raises as an error
     peer_wait_s: float = 2.0

@@ -24,6 +24,8 @@
 // ST_PEER_TIMEOUT to the status word and the kernel returns; nothing traps.
 // Grids are at most one wave, so every block of every replica is resident
 // while it waits for its counterpart.
+#include <cuda.h>
+#include <mutex>
 #include "ptx.cuh"
 #include "dswarm.h"
 #include "coll_index.h"
@@ -278,6 +280,59 @@ extern "C" int dsw_symm_import(const void* handle64, void** ptr) {
 }
 extern "C" int dsw_symm_unimport(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
 extern "C" int dsw_max_peers() { return MAX_PEERS; }
+
+// ------------------------------------------------------------------ stream-ordered flags and copies
+// What the copy-engine pipeline transport (parallel/ce_comm.py) is made of: a stream waits until a 32-bit
+// word in device memory reaches a value, a stream writes such a word (also into a peer's memory), and a
+// stream copies between two device pointers of which one may be a peer's.  None of the three runs a kernel,
+// so a transfer that waits for its peer holds no SM (a posted NCCL receive is a resident kernel, and one
+// blocked SM is enough to stretch a persistent GEMM with static tile assignment to two waves).
+namespace {
+typedef CUresult (*WaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+typedef CUresult (*WriteValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+WaitValue32Fn g_wait32 = nullptr;
+WriteValue32Fn g_write32 = nullptr;
+std::once_flag g_memops_once;
+void load_memops() {
+  std::call_once(g_memops_once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_wait32 = reinterpret_cast<WaitValue32Fn>(p);
+    p = nullptr;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_write32 = reinterpret_cast<WriteValue32Fn>(p);
+  });
+}
+}  // namespace
+
+// The stream waits until *addr >= value (unsigned, wrap-aware as the driver defines it).  addr: device memory
+// of the current device, 4-byte aligned.
+extern "C" int dsw_stream_wait_geq32(void* addr, unsigned value, cudaStream_t st) {
+  load_memops();
+  if (!g_wait32) return -1;
+  if (reinterpret_cast<uintptr_t>(addr) & 3) return -11;
+  const CUresult r = g_wait32(reinterpret_cast<CUstream>(st), reinterpret_cast<CUdeviceptr>(addr), value,
+                              CU_STREAM_WAIT_VALUE_GEQ);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+// The stream stores value into *addr once everything queued before it is done.  addr may point into a peer's
+// memory that this process has mapped.
+extern "C" int dsw_stream_write32(void* addr, unsigned value, cudaStream_t st) {
+  load_memops();
+  if (!g_write32) return -1;
+  if (reinterpret_cast<uintptr_t>(addr) & 3) return -11;
+  const CUresult r = g_write32(reinterpret_cast<CUstream>(st), reinterpret_cast<CUdeviceptr>(addr), value,
+                               CU_STREAM_WRITE_VALUE_DEFAULT);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+// Device-to-device copy on the stream (copy engines); either pointer may be a mapped peer buffer.
+extern "C" int dsw_copy_async(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  const cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st);
+  return e == cudaSuccess ? 0 : -(int)e - 100;
+}
 
 // ------------------------------------------------------------------ launchers
 // bufs / flags: host arrays of R device pointers (replica order).  flags may be

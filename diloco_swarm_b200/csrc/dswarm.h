@@ -113,6 +113,13 @@ int dsw_symm_export(void* ptr, void* handle64);
 int dsw_symm_import(const void* handle64, void** ptr);
 int dsw_symm_unimport(void* ptr);
 int dsw_max_peers();
+// Stream-ordered flags and copies without kernels (the copy-engine pipeline transport): the stream waits
+// until the 32-bit word at addr (this device's memory) is >= value; the stream writes value to addr (own or
+// mapped peer memory) after all earlier work on it; the stream copies bytes between device pointers (either
+// may be a mapped peer buffer).  -1: the driver lacks stream memory operations.
+int dsw_stream_wait_geq32(void* addr, unsigned value, cudaStream_t st);
+int dsw_stream_write32(void* addr, unsigned value, cudaStream_t st);
+int dsw_copy_async(void* dst, const void* src, size_t bytes, cudaStream_t st);
 // bufs / flags: host arrays of R device pointers in replica order (this replica's own buffer at index
 // `rank`).  seq: a number that grows by 2 per call, the same on every replica.  wait_limit <= 0 picks the
 // default bound of the peer waits; use_barrier = 0 (single-GPU arithmetic checks) skips them; blocks <= 0

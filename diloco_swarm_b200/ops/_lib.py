@@ -46,6 +46,9 @@ _SIGS = {
     "dsw_symm_import": [c_void_p, ctypes.POINTER(c_void_p)],
     "dsw_symm_unimport": [c_void_p],
     "dsw_max_peers": [],
+    "dsw_stream_wait_geq32": [c_void_p, c_uint, c_void_p],
+    "dsw_stream_write32": [c_void_p, c_uint, c_void_p],
+    "dsw_copy_async": [c_void_p, c_void_p, c_size_t, c_void_p],
     "dsw_outer_sync": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_float, c_float, c_int,
                        c_uint, c_ll, c_int, c_int, c_void_p, c_void_p],
     "dsw_grad_allreduce": [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_uint, c_ll, c_int,

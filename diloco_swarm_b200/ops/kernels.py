@@ -23,6 +23,9 @@ _NUM_SMS = 148
 
 
 _USE_PAIR = os.environ.get("DSWARM_GEMM_PAIR", "1") != "0"
+# Cap on the CTAs of every GEMM launch (0 = all SMs): leaves SMs to kernels that sit on the device while
+# the GEMMs run, such as a pipeline transfer waiting for its peer.
+_MAX_CTAS = int(os.environ.get("DSWARM_GEMM_MAX_CTAS", "0"))
 
 
 def _efficiency(M: int, N: int, splits: int, bm: int, bn: int, units: int) -> float:
@@ -96,6 +99,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Tru
         split_k = math.ceil(kb_total / per)       # no empty split
     if bn == 0:
         bn = _pick_bn(M, N, split_k)
+    if max_ctas == 0:
+        max_ctas = _MAX_CTAS
     aux = aux_out if aux_out is not None else aux_in
     rc = cuda_lib().dsw_gemm_bf16(
         a.data_ptr(), a.stride(0), 1 if a_t else 0, b.data_ptr(), b.stride(0), 0 if b_t else 1, M, N, K, mode,

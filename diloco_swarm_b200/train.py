@@ -102,8 +102,7 @@ class Trainer:
         self.routing_seed = config.swarm.routing_seed if config.swarm.routing_seed is not None else tc.seed
         self._resolve_layer_split()
         self.engine = make_engine(config, w, self.device)
-        self.comm = PipelineComm(w, (self.mbs, self.seq, config.model.n_embd), self.engine.act_dtype,
-                                 self.device, prefetch=max(1, config.swarm.recv_prefetch))
+        self.comm = self._make_comm()
         if hasattr(self.engine, "warmup"):
             self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
@@ -141,6 +140,23 @@ class Trainer:
         self.timeouts_seen = 0
 
     # ------------------------------------------------------------------
+    def _make_comm(self):
+        """Pipeline transport: copy engines with stream-ordered flags where every rank can map every other
+        rank's inbox (CUDA, one node, at most 8 ranks, no membership changes), NCCL / gloo point-to-point else."""
+        cfg, w = self.config, self.world
+        shape = (self.mbs, self.seq, cfg.model.n_embd)
+        kind = cfg.swarm.p2p
+        one_node = w.local_world_size == w.world_size
+        fits = self.device.type == "cuda" and one_node and 1 < w.world_size <= 8 and not cfg.elastic.enable
+        if kind == "auto":
+            kind = "copy" if fits and w.num_stages > 1 else "nccl"
+        if kind == "copy":
+            if not fits:
+                raise ValueError("swarm.p2p = copy needs CUDA ranks of one node (at most 8) and a static membership")
+            from .parallel.ce_comm import CopyEngineComm
+            return CopyEngineComm(w, shape, self.engine.act_dtype, self.device, slots=cfg.swarm.p2p_slots)
+        return PipelineComm(w, shape, self.engine.act_dtype, self.device, prefetch=max(0, cfg.swarm.recv_prefetch))
+
     def _resolve_layer_split(self) -> None:
         """``layer_split = balanced`` becomes explicit block counts before the stage is built: the cut that
         minimises the busiest stage's time per step under this run's routing (the busiest replica of a later
@@ -265,6 +281,7 @@ class Trainer:
         comm.begin_step(ops, timeout_s=self.config.train.step_timeout)
         for i, op in enumerate(ops):
             rows = D.micro_batch_rows(op.mb, self.mbs)
+            comm.tick(i)
             if op.kind == BWD:
                 dy = comm.recv(i)
                 with self._compute(f"B{op.mb}"):
@@ -371,7 +388,7 @@ class Trainer:
                 with self._traced("outer_sync"):
                     eng.outer_step(timer=self.timer)     # phases "outer_wait" (replica skew) and "outer_sync"
         self.last_enqueue_s = time.time() - start   # host time to queue the whole step
-        if comm.is_nccl and w.world_size > 1 and not failed:
+        if comm.device_async and w.world_size > 1 and not failed:
             self._watch_step_deadline(step, start + cfg.train.step_timeout)
         loss_val = float(loss_acc.item())      # the step's one device-to-host read
         if self.device.type == "cuda":
@@ -407,6 +424,7 @@ class Trainer:
         comm.begin_step(ops)
         for i, op in enumerate(ops):
             rows = D.micro_batch_rows(op.mb, self.mbs)
+            comm.tick(i)
             n_local += 1
             ids = dev["input_ids"][rows] if eng.is_first else None
             hidden = comm.recv(i) if op.prev >= 0 else None

@@ -76,6 +76,7 @@ def test_every_definition_is_declared():
     for src in _build.cuda_sources() + _build.host_sources():
         text = open(src).read()
         defined |= set(re.findall(r'extern "C" int (dsw_\w+)\s*\(', text))
+        defined |= set(re.findall(r"^DSW_BOUNDS_TU\((dsw_\w+)\)", text, flags=re.M))     # macro-made readers
         for block in re.findall(r'extern "C" \{(.*?)\n\}  // extern "C"', text, flags=re.S):
             defined |= set(re.findall(r"^int (dsw_\w+)\s*\(", block, flags=re.M))
     assert defined == set(decl), (sorted(defined - set(decl)), sorted(set(decl) - defined))
