@@ -288,10 +288,10 @@ def run_ours(args) -> dict:
 
     # ---- the fused collectives against NCCL on this box, outside the timed regions
     check = {"status": "skipped"}
-    if not args.no_collective_check and args.engine == "b200" and args.collective == "fused":
+    if not args.no_collective_check and args.engine == "b200" and args.collective in ("fused", "nvls"):
         from diloco_swarm_b200.parallel.collectives import check_against_nccl
         grp = tr.world.curr_stage_group if R > 1 else None
-        check = check_against_nccl(grp, dev, tr.engine.n, tr.engine.buckets)
+        check = check_against_nccl(grp, dev, tr.engine.n, tr.engine.buckets, multicast=args.collective == "nvls")
         bad = max_over_ranks(1.0 if check["status"] == "mismatch" else 0.0)
         if bad:
             check["status"] = "mismatch"

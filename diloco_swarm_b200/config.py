@@ -59,9 +59,11 @@ class SwarmConfig(BaseConfig):
     # stages); "balanced" = weigh embedding / LM head when splitting blocks;
     # or an explicit comma list such as "7,5".
     layer_split: str = "even"
-    # (added) fused collectives: "fused" = hand-written NVLink kernels,
+    # (added) stage-wide synchronisations: "fused" = hand-written kernels over peer loads / stores,
+    # "nvls" = the same kernels with the reduction and the broadcast done inside the NVSwitch (multimem
+    # instructions on multicast-bound buffers; falls back to "fused" where the box has no NVLS),
     # "nccl" = library all-reduce followed by separate update kernels.
-    collective: Literal["fused", "nccl"] = "fused"
+    collective: Literal["fused", "nvls", "nccl"] = "fused"
     # (added) wire dtype of the per-step gradient all-reduce
     grad_wire_dtype: Literal["float32", "bfloat16"] = "float32"
     # (added) a pipeline receive is posted this many operations of the rank's plan before the operation that

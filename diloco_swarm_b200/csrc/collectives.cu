@@ -248,6 +248,123 @@ grad_allreduce_bf16_kernel(GradArgs a) {
   }
 }
 
+// ------------------------------------------------------------------ NVLS variants
+// The same two synchronisations with the reduction done inside the NVSwitch: the buffers are bound to a
+// multicast object, `multimem.ld_reduce` on the multicast address returns the sum over all replicas of one
+// 16-byte vector (one load crosses this GPU's links instead of R - 1), and `multimem.st` stores a vector into
+// every replica at once (one store instead of R).  Per GPU and direction the links then carry 1/R of the
+// buffer in and 1/R out, against (R - 1)/R each way for the peer-load kernels.  Slice ownership, the flag
+// barrier (plain peer stores / loads on the flag words) and the bounded waits are unchanged.
+__device__ __forceinline__ float4 mm_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// eight bf16 values: summed over the replicas with fp32 accumulation inside the switch
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const __nv_bfloat16* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_bf16x8(__nv_bfloat16* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__global__ void __launch_bounds__(512)
+outer_sync_nvls_kernel(OuterArgs a, float* mc) {
+  __shared__ int sh_ok;
+  if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq, a.wait_limit, a.status, &sh_ok)) return;
+  const long long lo = (long long)a.rank * a.shard;
+  const long long hi = min(a.n, lo + a.shard);
+  const float invR = 1.f / a.R;
+  const long long stride = 4LL * gridDim.x * blockDim.x;
+  for (long long i0 = lo + 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i0 < hi; i0 += 2 * stride) {
+    const long long idx[2] = {i0, i0 + stride};
+    float4 s[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (idx[u] < hi && DSW_OK(idx[u] >= 0 && idx[u] + 4 <= a.n)) s[u] = mm_ld_reduce_f4(mc + idx[u]);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] >= hi) continue;
+      const long long k = idx[u] - lo;
+      float4 tg = ld_f4(a.theta_g + k);
+      float4 mb = ld_f4(a.mom + k);
+      float* S = &s[u].x; float* T = &tg.x; float* B = &mb.x;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float delta = T[c] - S[c] * invR;
+        float upd = delta;
+        if (a.mu != 0.f) {
+          B[c] = a.mu * B[c] + delta;
+          upd = a.nesterov ? delta + a.mu * B[c] : B[c];
+        }
+        T[c] = T[c] - a.lr * upd;
+      }
+      st_f4(a.theta_g + k, tg);
+      st_f4(a.mom + k, mb);
+      mm_st_f4(mc + idx[u], tg);
+    }
+  }
+  if (a.use_barrier) peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok);
+}
+
+__global__ void __launch_bounds__(512)
+grad_allreduce_nvls_f32_kernel(GradArgs a, float* mc) {
+  __shared__ int sh_ok;
+  if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq, a.wait_limit, a.status, &sh_ok)) return;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  dsw_for_each_owned(a.offset, a.count, a.shard, a.rank, a.rank + 1, tid, nth, 4, [&](long long i) {
+    if (!DSW_OK(i >= a.offset && i + 4 <= a.offset + a.count)) return;
+    float4 s = mm_ld_reduce_f4(mc + i);
+    s.x *= a.scale; s.y *= a.scale; s.z *= a.scale; s.w *= a.scale;
+    mm_st_f4(mc + i, s);
+  });
+  if (a.use_barrier) peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok);
+}
+
+// bf16 wire through the switch: cast into the (multicast-bound) staging buffer, reduce the own slice with
+// fp32 accumulation in the switch, scale, store to every replica's staging at once, widen.
+__global__ void __launch_bounds__(512)
+grad_allreduce_nvls_bf16_kernel(GradArgs a, __nv_bfloat16* mc) {
+  __shared__ int sh_ok;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(a.pt.buf[a.rank]);
+  dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
+    if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
+    const float4 x = ld_f4(a.grad + i), y = ld_f4(a.grad + i + 4);
+    *reinterpret_cast<uint4*>(stage + i) =
+        make_uint4(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w), pack_bf16(y.x, y.y), pack_bf16(y.z, y.w));
+  });
+  if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq, a.wait_limit, a.status, &sh_ok)) return;
+  dsw_for_each_owned(a.offset, a.count, a.shard, a.rank, a.rank + 1, tid, nth, 8, [&](long long i) {
+    if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
+    const uint4 u = mm_ld_reduce_bf16x8(mc + i);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) { const float2 f = unpack_bf16(w[c]); o[c] = pack_bf16(f.x * a.scale, f.y * a.scale); }
+    mm_st_bf16x8(mc + i, make_uint4(o[0], o[1], o[2], o[3]));
+  });
+  if (a.use_barrier && !peer_barrier(a.pt, a.rank, a.R, a.seq + 1, a.wait_limit, a.status, &sh_ok)) return;
+  dsw_for_each_owned(a.offset, a.count, a.shard, 0, a.R, tid, nth, 8, [&](long long i) {
+    if (!DSW_OK(i >= a.offset && i + 8 <= a.offset + a.count)) return;
+    const uint4 u = *reinterpret_cast<const uint4*>(stage + i);
+    const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
+    st_f4(a.grad + i, make_float4(f0.x, f0.y, f1.x, f1.y));
+    st_f4(a.grad + i + 4, make_float4(f2.x, f2.y, f3.x, f3.y));
+  });
+}
+
 static void fill_table(PeerTable& pt, void* const* bufs, void* const* flags, int R) {
   for (int j = 0; j < MAX_PEERS; ++j) {
     pt.buf[j] = j < R ? bufs[j] : nullptr;
@@ -371,6 +488,39 @@ extern "C" int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// NVLS variants: mc = the multicast address of the same buffer that bufs[rank] is this replica's unicast view
+// of (the fp32 weights / gradient, or the bf16 staging buffer when wire_bf16 is set).  R >= 2.
+extern "C" int dsw_outer_sync_nvls(void* const* bufs, void* mc, void* const* flags, float* theta_g, float* mom,
+                                   long long n, long long shard, int rank, int R, float lr, float mu, int nesterov,
+                                   unsigned seq, long long wait_limit, int blocks, int* status, cudaStream_t st) {
+  if (R < 2 || R > MAX_PEERS || n % 4 || shard % 4 || mc == nullptr) return -10;
+  OuterArgs a;
+  fill_table(a.pt, bufs, flags, R);
+  a.theta_g = theta_g; a.mom = mom; a.n = n; a.shard = shard; a.rank = rank; a.R = R;
+  a.lr = lr; a.mu = mu; a.nesterov = nesterov; a.seq = seq;
+  a.wait_limit = wait_limit > 0 ? wait_limit : WAIT_CYCLES_LIMIT;
+  a.use_barrier = 1; a.status = status;
+  if (blocks <= 0 || blocks > DSW_MAX_COLL_BLOCKS) blocks = DSW_MAX_COLL_BLOCKS;
+  outer_sync_nvls_kernel<<<blocks, 512, 0, st>>>(a, reinterpret_cast<float*>(mc));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int dsw_grad_allreduce_nvls(void* const* bufs, void* mc, void* const* flags, float* grad, long long offset,
+                                       long long count, long long shard, int rank, int R, int wire_bf16, unsigned seq,
+                                       long long wait_limit, int blocks, int* status, cudaStream_t st) {
+  if (R < 2 || R > MAX_PEERS || offset % 8 || count % 8 || shard % 8 || mc == nullptr) return -10;
+  GradArgs a;
+  fill_table(a.pt, bufs, flags, R);
+  a.grad = grad; a.offset = offset; a.count = count; a.shard = shard; a.rank = rank; a.R = R;
+  a.scale = 1.f / R; a.seq = seq;
+  a.wait_limit = wait_limit > 0 ? wait_limit : WAIT_CYCLES_LIMIT;
+  a.use_barrier = 1; a.phase_mask = 7; a.status = status;
+  if (blocks <= 0 || blocks > DSW_MAX_COLL_BLOCKS) blocks = DSW_MAX_COLL_BLOCKS;
+  if (wire_bf16) grad_allreduce_nvls_bf16_kernel<<<blocks, 512, 0, st>>>(a, reinterpret_cast<__nv_bfloat16*>(mc));
+  else           grad_allreduce_nvls_f32_kernel<<<blocks, 512, 0, st>>>(a, reinterpret_cast<float*>(mc));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 DSW_BOUNDS_TU(dsw_bounds_collectives)
 
 extern "C" int dsw_load_collectives() {
@@ -379,5 +529,8 @@ extern "C" int dsw_load_collectives() {
   bad |= cudaFuncGetAttributes(&a, outer_sync_kernel) != cudaSuccess;
   bad |= cudaFuncGetAttributes(&a, grad_allreduce_f32_kernel) != cudaSuccess;
   bad |= cudaFuncGetAttributes(&a, grad_allreduce_bf16_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, outer_sync_nvls_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, grad_allreduce_nvls_f32_kernel) != cudaSuccess;
+  bad |= cudaFuncGetAttributes(&a, grad_allreduce_nvls_bf16_kernel) != cudaSuccess;
   return bad ? -1 : 0;
 }

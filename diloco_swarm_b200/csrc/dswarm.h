@@ -136,6 +136,15 @@ int dsw_grad_allreduce(void* const* bufs, void* const* flags, float* grad, long 
                        long long shard, int rank, int R, int wire_bf16, unsigned seq, long long wait_limit,
                        int use_barrier, int phase_mask, int blocks, int* status, cudaStream_t st);
 
+// The same two with the reduction inside the NVSwitch (multimem.ld_reduce / multimem.st): mc is the multicast
+// address of the buffer whose unicast views are bufs[0..R-1] (for wire_bf16 the bf16 staging buffers).  R >= 2.
+int dsw_outer_sync_nvls(void* const* bufs, void* mc, void* const* flags, float* theta_g, float* mom, long long n,
+                        long long shard, int rank, int R, float lr, float mu, int nesterov, unsigned seq,
+                        long long wait_limit, int blocks, int* status, cudaStream_t st);
+int dsw_grad_allreduce_nvls(void* const* bufs, void* mc, void* const* flags, float* grad, long long offset,
+                            long long count, long long shard, int rank, int R, int wire_bf16, unsigned seq,
+                            long long wait_limit, int blocks, int* status, cudaStream_t st);
+
 // ---------------------------------------------------------------- bounds-checking build (-DDSWARM_BOUNDS)
 // First failed bounds check since the last call: 0 = none, else 100000 * unit + source line (units: 1
 // elementwise.cu, 2 optim.cu, 3 collectives.cu, 4 gemm_one_cta.cu, 5 gemm_pair.cu).  The shipped build has no

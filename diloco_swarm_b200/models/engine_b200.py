@@ -73,8 +73,9 @@ class B200Engine:
             off += _align(math.prod(shape))
         self.n = _align(off, 8 * 8)          # divisible into 8-element-aligned shards for up to 8 replicas
         group = world.curr_stage_group if world.num_replicas > 1 else None
-        self.theta_buf = SymmetricBuffer(self.n * 4, device, group)
-        self.grad_buf = SymmetricBuffer(self.n * 4, device, group)
+        nvls = config.swarm.collective == "nvls"
+        self.theta_buf = SymmetricBuffer(self.n * 4, device, group, multicast=nvls)
+        self.grad_buf = SymmetricBuffer(self.n * 4, device, group, multicast=nvls)
         self.theta = self.theta_buf.view(F32, self.n)
         self.grad = self.grad_buf.view(F32, self.n)
         self.w16 = torch.zeros(self.n, dtype=BF16, device=device)
@@ -93,7 +94,7 @@ class B200Engine:
         self.opt_step = 0
         oc = config.train.outer_optimizer
         self.has_outer = oc.type != "None"
-        self.fused = config.swarm.collective == "fused"
+        self.fused = config.swarm.collective in ("fused", "nvls")
         self.outer: Optional[OuterSync] = None
         if self.has_outer:
             assert oc.type == "SGD", "the outer optimiser is SGD (optionally Nesterov) as in the reference"

@@ -53,6 +53,10 @@ _SIGS = {
                        c_uint, c_ll, c_int, c_int, c_void_p, c_void_p],
     "dsw_grad_allreduce": [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_uint, c_ll, c_int,
                            c_int, c_int, c_void_p, c_void_p],
+    "dsw_outer_sync_nvls": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_float,
+                            c_float, c_int, c_uint, c_ll, c_int, c_void_p, c_void_p],
+    "dsw_grad_allreduce_nvls": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_uint,
+                                c_ll, c_int, c_void_p, c_void_p],
     "dsw_attention_fwd": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "dsw_attention_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_float, c_void_p, c_void_p],

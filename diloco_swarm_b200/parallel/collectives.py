@@ -102,6 +102,15 @@ class OuterSync:
             dist.barrier(group=group, device_ids=[device.index])
 
     def step(self) -> None:
+        if self.R > 1 and self.theta.mc_ptr:
+            # the weights are bound to a multicast object: reduce and broadcast inside the NVSwitch
+            check(cuda_lib().dsw_outer_sync_nvls(
+                self.theta.table, self.theta.mc_ptr, self.flags.table, self.theta_g.data_ptr(), self.mom.data_ptr(),
+                self.n, self.shard, self.rank, self.R, self.lr, self.mu, 1 if self.nesterov else 0, self.seq,
+                self.wait_cycles, self.blocks, self.status.ptr if self.status else None, stream_ptr()),
+                "dsw_outer_sync_nvls")
+            self.seq += 2
+            return
         check(cuda_lib().dsw_outer_sync(
             self.theta.table, self.flags.table if self.flags else None, self.theta_g.data_ptr(), self.mom.data_ptr(),
             self.n, self.shard, self.rank, self.R, self.lr, self.mu, 1 if self.nesterov else 0, self.seq,
@@ -143,7 +152,8 @@ class GradSync:
         self.grad, self.n, self.device, self.group = grad, n, device, group
         self.R, self.rank = grad.R, grad.rank_in_group
         self.wire_bf16 = wire_bf16
-        self.stage_buf = SymmetricBuffer(n * 2, device, group) if (wire_bf16 and self.R > 1) else None
+        self.nvls = bool(grad.mc_ptr)
+        self.stage_buf = SymmetricBuffer(n * 2, device, group, multicast=self.nvls) if (wire_bf16 and self.R > 1) else None
         self.flags = SymmetricBuffer(FLAG_WORDS * 4, device, group) if self.R > 1 else None
         self.seq = 1
         self.status = status
@@ -159,6 +169,14 @@ class GradSync:
         assert offset % 8 == 0 and count % 8 == 0
         shard = shard_size(count, self.R, 8)
         table = self.stage_buf.table if self.wire_bf16 else self.grad.table
+        if self.nvls:
+            mc = self.stage_buf.mc_ptr if self.wire_bf16 else self.grad.mc_ptr
+            check(cuda_lib().dsw_grad_allreduce_nvls(
+                table, mc, self.flags.table, self.grad.ptr, offset, count, shard, self.rank, self.R,
+                1 if self.wire_bf16 else 0, self.seq, self.wait_cycles, self.blocks,
+                self.status.ptr if self.status else None, stream_ptr(stream)), "dsw_grad_allreduce_nvls")
+            self.seq += 2
+            return
         check(cuda_lib().dsw_grad_allreduce(
             table, self.flags.table, self.grad.ptr, offset, count, shard, self.rank, self.R,
             1 if self.wire_bf16 else 0, self.seq, self.wait_cycles, 1, 7, self.blocks,
@@ -170,7 +188,7 @@ class GradSync:
 
 
 def check_against_nccl(group, device: torch.device, n: int, buckets, lr: float = 0.7, momentum: float = 0.9,
-                       seed: int = 1234) -> dict:
+                       seed: int = 1234, multicast: bool = False) -> dict:
     """Run the fused collectives once on fresh buffers of a stage's real size and bucket list and compare
     them with the library route (NCCL all-reduce + separate update) on the same values.
 
@@ -183,7 +201,7 @@ def check_against_nccl(group, device: torch.device, n: int, buckets, lr: float =
     rank = dist.get_rank(group)
     status = Status(device)
     g = torch.Generator(device=device).manual_seed(seed + rank)
-    out = {"status": "ok", "replicas": R, "elements": n, "buckets": len(buckets)}
+    out = {"status": "ok", "replicas": R, "elements": n, "buckets": len(buckets), "nvls": False}
 
     def worst(x: torch.Tensor) -> float:
         t = x.abs().max().reshape(1).to(torch.float64)
@@ -192,7 +210,8 @@ def check_against_nccl(group, device: torch.device, n: int, buckets, lr: float =
 
     # ---- per-step gradient all-reduce, fp32 and bf16 wire, bucket by bucket as the engine sends them
     for wire in (False, True):
-        buf = SymmetricBuffer(n * 4, device, group)
+        buf = SymmetricBuffer(n * 4, device, group, multicast=multicast)
+        out["nvls"] = bool(buf.mc_ptr)
         grad = buf.view(torch.float32, n)
         grad.copy_(torch.randn(n, device=device, generator=g) * 1e-2)
         ref = grad.clone()
@@ -211,7 +230,7 @@ def check_against_nccl(group, device: torch.device, n: int, buckets, lr: float =
             out["status"] = "mismatch"
         dist.barrier(group=group, device_ids=[device.index])
     # ---- DiLoCo outer sync
-    theta_buf = SymmetricBuffer(n * 4, device, group)
+    theta_buf = SymmetricBuffer(n * 4, device, group, multicast=multicast)
     theta = theta_buf.view(torch.float32, n)
     common = torch.Generator(device=device).manual_seed(seed)
     theta_g = torch.randn(n, device=device, generator=common)

@@ -40,10 +40,21 @@ class SymmetricBuffer:
     """``nbytes`` of device memory on every rank of ``group`` plus pointers to
     the peers' copies.  ``local`` is this rank's buffer as a uint8 tensor."""
 
-    def __init__(self, nbytes: int, device: torch.device, group=None, ranks: Optional[Sequence[int]] = None):
+    def __init__(self, nbytes: int, device: torch.device, group=None, ranks: Optional[Sequence[int]] = None,
+                 multicast: bool = False):
+        """``multicast``: also bind the replicas' buffers to an NVLink multicast object, so that kernels can
+        reduce and broadcast inside the NVSwitch through ``mc_ptr`` (``multimem`` instructions).  Such memory
+        comes from the driver's virtual-memory API; PyTorch's symmetric-memory allocator is used for that
+        plumbing (allocation, handle exchange, binding), the kernels on it are this library's.  ``mc_ptr`` is 0
+        when the replicas cannot form a multicast group (one replica, or no NVLS on the box)."""
         lib = cuda_lib()
         self.device = device
         self.nbytes = (nbytes + 255) // 256 * 256
+        self.mc_ptr = 0
+        self._symm_handle = None
+        if multicast and group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+            self._init_multicast(device, group)
+            return
         # Peers store into these buffers with plain pointers, and the sanitizer tools are closed on shared GPUs,
         # so every buffer sits between two guard zones filled with a fixed byte; check_canaries() (called when
         # the buffer is closed, and per step with DSWARM_CANARY_CHECK=1) tells whether a store went astray.
@@ -82,6 +93,33 @@ class SymmetricBuffer:
         self.R = R
         self._table = (ctypes.c_void_p * MAX_PEERS)(*[ctypes.c_void_p(x) for x in self.peer_ptrs])
 
+    def _init_multicast(self, device: torch.device, group) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+        total = self.nbytes + 2 * GUARD_BYTES
+        with torch.cuda.device(device):
+            whole = symm_mem.empty(total, dtype=torch.uint8, device=device)
+            whole.zero_()
+            hdl = symm_mem.rendezvous(whole, group)
+        self._symm_handle = hdl
+        self._whole = whole
+        self._base = whole.data_ptr()
+        self.ptr = self._base + GUARD_BYTES
+        self._imported = []
+        self._whole[:GUARD_BYTES].fill_(CANARY)
+        self._whole[GUARD_BYTES + self.nbytes:].fill_(CANARY)
+        self.local = self._whole[GUARD_BYTES:GUARD_BYTES + self.nbytes]
+        self.R = dist.get_world_size(group)
+        self.rank_in_group = dist.get_rank(group)
+        if self.R > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} replicas per stage")
+        self.peer_ptrs = [int(p) + GUARD_BYTES for p in hdl.buffer_ptrs]
+        assert self.peer_ptrs[self.rank_in_group] == self.ptr
+        mc = int(hdl.multicast_ptr or 0)                   # 0 where the replicas cannot form a multicast group
+        self.mc_ptr = mc + GUARD_BYTES if mc else 0
+        self._table = (ctypes.c_void_p * MAX_PEERS)(*[ctypes.c_void_p(x) for x in self.peer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group, device_ids=[device.index])      # every replica's guards and zeros are in place
+
     @property
     def table(self):
         """Host array of R device pointers in replica order (launcher argument)."""
@@ -113,7 +151,9 @@ class SymmetricBuffer:
                 self.check_canaries()
             finally:
                 self.local = self._whole = None
-                lib.dsw_symm_free(self._base)
+                if self._symm_handle is None:
+                    lib.dsw_symm_free(self._base)
+                self._symm_handle = None              # multicast-bound memory goes back with its tensor
                 self._base = self.ptr = 0
 
 

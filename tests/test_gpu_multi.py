@@ -73,6 +73,25 @@ def test_swarm_2x2_matches_pipeline_2x1():
     assert max(abs(a - b) for a, b in zip(pipe, swarm)) < 5e-3, (pipe, swarm)
 
 
+def test_nvls_collectives_match_single_gpu():
+    """The multimem variants of both stage-wide synchronisations (reduction and broadcast inside the NVSwitch)
+    on two replicas: plain SWARM with fp32 and bf16 wire reproduces the one-GPU curve, DiLoCo agrees with the
+    peer-load kernels.  On a box without NVLS the buffers come without a multicast address and the runs fall
+    back to the peer-load kernels, so the comparison still holds."""
+    _need(2)
+    one = _run("one_b", 1, 1)
+    two = _run("dp2_nvls", 2, 1, ["--swarm.collective", "nvls"])
+    assert max(abs(a - b) for a, b in zip(one, two)) < 5e-3, (one, two)
+    wire = _run("dp2_nvls_bf16", 2, 1, ["--swarm.collective", "nvls", "--swarm.grad_wire_dtype", "bfloat16"])
+    assert max(abs(a - b) for a, b in zip(one, wire)) < 2e-2, (one, wire)
+    extra = ["--train.outer_optimizer.type", "SGD", "--train.outer_optimizer.lr", "0.7",
+             "--train.outer_optimizer.nesterov", "true", "--swarm.sync_every_n_steps", "2", "--train.max_steps", "6"]
+    fused = _run("diloco_fused_b", 2, 1, extra)
+    nvls = _run("diloco_nvls", 2, 1, extra + ["--swarm.collective", "nvls"])
+    assert len(fused) == len(nvls) == 3
+    assert max(abs(a - b) for a, b in zip(fused, nvls)) < 5e-3, (fused, nvls)
+
+
 def test_copy_engine_transport_matches_nccl():
     """The two pipeline transports carry the same tensors in the same order: same loss curve."""
     _need(2)
