@@ -279,9 +279,18 @@ def run_ours(args) -> dict:
             one(resident)
         ms_sw, _, _ = timed(resident, k2)
         exposed = [p.get("grad_sync", 0.0) for p in sync_phases[first + 3:]]
+        # The phase runs from the end of a rank's last backward to the end of its last bucket's all-reduce.  On the
+        # replica that reaches its last backward last nobody is waited for, so its figure (the minimum over the
+        # ranks) is what the synchronisation itself leaves exposed; on the others the phase is mostly the wait
+        # for that replica (routing gives the replicas different loads), reported as the maximum.
+        mine = statistics.mean(exposed) if exposed else 0.0
+        t = torch.tensor([mine if R > 1 else 1e9], dtype=torch.float64, device=dev)
+        if world_size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
         swarm = {"swarm_tokens_per_s": args.batch * args.seq * k2 / (ms_sw / 1e3), "swarm_ms_per_step": ms_sw / k2,
                  "steps": k2, "warmup": 3,
-                 "grad_sync_exposed_ms": max_over_ranks(statistics.mean(exposed) if exposed else 0.0),
+                 "grad_sync_exposed_ms": float(t.item()) if R > 1 else 0.0,
+                 "grad_sync_incl_wait_for_slowest_replica_ms": max_over_ranks(mine),
                  "grad_wire_dtype": cfg2.swarm.grad_wire_dtype}
         tr2.logger.close()
         active[0] = tr
