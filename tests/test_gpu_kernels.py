@@ -86,7 +86,9 @@ def test_cross_entropy(M, V):
     loss2 = torch.zeros((), device=DEV)
     work2 = logits.clone()
     K.cross_entropy(work2, tg, mask, scale, loss2, cnt, write_grad=False)
-    assert torch.equal(work2, logits) and abs(loss2.item() - loss.item()) < 1e-6
+    # the rows' terms reach the loss through fp32 atomics, so two launches add them in different orders: the
+    # two sums of some 200 terms around 0.02 agree to a few units in the last place of 3.9, not bit for bit
+    assert torch.equal(work2, logits) and abs(loss2.item() - loss.item()) < 1e-5
 
 
 def test_adamw_and_clip():
