@@ -326,7 +326,10 @@ def run_ours(args) -> dict:
         "outer_sync_ms": outer_info["ms"],
         **(swarm or {}),
         "collective_check": check["status"], "collective_check_detail": check,
-        "vs_reference_measured_earlier": (value / REFERENCE_TOKENS_PER_S[N]) if N in REFERENCE_TOKENS_PER_S else None,
+        # only for the configuration the reference arm was measured on (GPT-2 small, default batch and topology)
+        "vs_reference_measured_earlier": (value / REFERENCE_TOKENS_PER_S[N])
+        if (N in REFERENCE_TOKENS_PER_S and args.model == "small" and args.batch == 512 and args.micro_batch == 16
+            and args.seq == 1024 and args.stages in (0, 1 if N == 1 else 2)) else None,
         "loss": float(loss_t.item()),
         "step_ms_rank0": {"device_resident_inputs": per_step[0], "e2e": per_step[1]},
         "cuda_mallocs_in_timed_regions_rank0": mallocs,

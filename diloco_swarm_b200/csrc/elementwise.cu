@@ -344,9 +344,23 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restri
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int col = blockIdx.x * 256 + cg * 8;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (col < N) {
-    for (int row = blockIdx.y * 8 + rl; row < M; row += gridDim.y * 8) {
-      if (!DSW_OK(col + 8 <= N && col + 8 <= ld)) continue;
+  if (col < N && DSW_OK(col + 8 <= N && col + 8 <= ld)) {
+    const int step = gridDim.y * 8;
+    int row = blockIdx.y * 8 + rl;
+    // four rows in flight per thread: the loads of one round are issued before any of them is added
+    for (; row + 3 * step < M; row += 4 * step) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(x + (long long)(row + u * step) * ld + col);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float v[8];
+        unpack8(q[u], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[j];
+      }
+    }
+    for (; row < M; row += step) {
       float v[8];
       load8(x + (long long)row * ld + col, v);
 #pragma unroll

@@ -306,7 +306,7 @@ class Trainer:
                     comm.send_backward(dx, op.prev)
         comm.end_step()
 
-    def _watch_step_deadline(self, step: int, deadline: float) -> None:
+    def _watch_step_deadline(self, step: int, deadline: float, what: str = "Train") -> None:
         """Step timeout on NCCL.  The reference warns and leaves its event loop when a step takes longer than
         ``train.step_timeout`` and still reaches the barrier (src/train.py:186,245).  Here the whole step is
         already queued on the device when the host gets here, and a posted NCCL transfer cannot be withdrawn, so
@@ -321,7 +321,7 @@ class Trainer:
             if time.time() > deadline:
                 self.step_timed_out = True
                 self.timeouts_seen += 1
-                self.logger.log_message(f"Train step {step} timed out", master=False, level=Level.WARNING)
+                self.logger.log_message(f"{what} step {step} timed out", master=False, level=Level.WARNING)
                 self.logger.log_message(f"Step {step}: waiting for the transfers already posted to drain",
                                         master=False, level=Level.WARNING)
                 break
@@ -434,6 +434,10 @@ class Trainer:
             else:
                 comm.send_forward(eng.forward(op.mb, ids, hidden, keep=False), op.next)
         comm.end_step()
+        if comm.device_async and w.world_size > 1:
+            # the reference's evaluation loop has no deadline at all (src/train.py:99); here a peer that is late
+            # gets the same warning as in training before the host blocks on the loss
+            self._watch_step_deadline(step, start + self.config.train.step_timeout, what=eval_type.capitalize())
         loss_val = float(loss_acc.item())
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
