@@ -413,35 +413,47 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 struct AttBwdSmem {
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + ATT_TILE_BYTES;
-  static constexpr int Q_OFF = V_OFF + ATT_TILE_BYTES;              // 2 stages
-  static constexpr int DO_OFF = Q_OFF + 2 * ATT_TILE_BYTES;         // 2 stages
-  static constexpr int P_OFF = DO_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
+  static constexpr int QSTAGES = 3;                                 // (Q_i, dO_i) pairs in flight
+  static constexpr int Q_OFF = V_OFF + ATT_TILE_BYTES;
+  static constexpr int DO_OFF = Q_OFF + QSTAGES * ATT_TILE_BYTES;
+  static constexpr int P_OFF = DO_OFF + QSTAGES * ATT_TILE_BYTES;   // 2 k-blocks
   static constexpr int DS_OFF = P_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
   static constexpr int DQ_OFF = DS_OFF + 2 * ATT_TILE_BYTES;        // fp32 [2 halves][128 rows][32], 128-byte swizzled
   static constexpr int BAR_OFF = DQ_OFF + 2 * ATT_TILE_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// D[bh, t] = sum_c dO[t, h*hs + c] * O[t, h*hs + c]; one warp per (row, head)
+// D[bh, t] = sum_c dO[t, h*hs + c] * O[t, h*hs + c], and dq_acc[t, :] = 0.  One warp per token row: 16-byte
+// loads, one head's hs columns lie in hs/8 neighbouring lanes (hs = 64 or 32), which a few shuffles add up.
 __global__ void __launch_bounds__(256)
 attention_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                          float* __restrict__ D, int B, int T, int nh, int hs) {
-  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int total = B * T * nh;
-  if (gw >= total) return;
-  const int row = gw / nh, h = gw - row * nh;
-  const long long off = (long long)row * nh * hs + h * hs + lane * 2;
-  float v = 0.f;
-  if (lane * 2 < hs) {
-    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(out + off));
-    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + off));
-    v = a.x * g.x + a.y * g.y;
-  }
+                          float* __restrict__ D, float* __restrict__ dq_acc, int B, int T, int nh, int hs) {
+  const int lane = threadIdx.x & 31;
+  const int d = nh * hs, chunks = d >> 3, lanes_per_head = hs >> 3;
+  const long long rows = (long long)B * T;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+    const int b = int(row / T), t = int(row - (long long)b * T);
+    const uint4* po = reinterpret_cast<const uint4*>(out + row * d);
+    const uint4* pg = reinterpret_cast<const uint4*>(dout + row * d);
+    float4* pz = reinterpret_cast<float4*>(dq_acc + row * d);
+    for (int u0 = 0; u0 < chunks; u0 += 32) {
+      const int u = u0 + lane;
+      float v = 0.f;
+      if (u < chunks) {
+        const uint4 a = po[u], g = pg[u];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  if (lane == 0) {
-    const int b = row / T, t = row - b * T;
-    D[((long long)b * nh + h) * T + t] = v;
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = unpack_bf16(aw[k]), y = unpack_bf16(gw[k]);
+          v += x.x * y.x + x.y * y.y;
+        }
+        pz[2 * u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        pz[2 * u + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      for (int o = lanes_per_head >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (u < chunks && (lane & (lanes_per_head - 1)) == 0) D[((long long)b * nh + u / lanes_per_head) * T + t] = v;
+    }
   }
 }
 
@@ -482,7 +494,7 @@ __device__ __forceinline__ void bwd_row_chunk(const uint32_t (&sv)[32], const ui
 }
 
 constexpr int ATT_BWD_ROW_WARPS = 8;     // two per TMEM lane quarter: each thread takes half of its row's columns
-constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 2);
+constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 3);    // + MMA issuer, TMA producer, dQ reducer
 
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
@@ -497,15 +509,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   // (g = steps done, w = items done).
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;            // K, V of the item loaded
-  uint64_t* q_full = bars + 1;         // 2 stages of (Q_i, dO_i)
-  uint64_t* q_empty = bars + 3;        // 2
-  uint64_t* sdp_full = bars + 5;       // S and dP ready
-  uint64_t* pds_full = bars + 6;       // P and dS in shared memory (8 warps arrive)
-  uint64_t* dq_full = bars + 7;        // dV/dK/dQ MMAs of this step done
-  uint64_t* dq_free = bars + 8;        // dQ read out of TMEM (8 warps arrive)
-  uint64_t* kv_empty = bars + 9;       // every MMA of the item done: K, V may be overwritten
-  uint64_t* dkv_free = bars + 10;      // dK, dV of the item read out of TMEM (8 warps arrive)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* q_full = bars + 1;         // QSTAGES stages of (Q_i, dO_i)
+  uint64_t* q_empty = bars + 4;        // QSTAGES
+  uint64_t* sdp_full = bars + 7;       // S and dP ready
+  uint64_t* pds_full = bars + 8;       // P and dS in shared memory (8 warps arrive)
+  uint64_t* dq_full = bars + 9;        // dV/dK/dQ MMAs of this step done
+  uint64_t* dq_free = bars + 10;       // dQ read out of TMEM (8 warps arrive)
+  uint64_t* kv_empty = bars + 11;      // every MMA of the item done: K, V may be overwritten
+  uint64_t* dkv_free = bars + 12;      // dK, dV of the item read out of TMEM (8 warps arrive)
+  uint64_t* sdp_read = bars + 13;      // S and dP of this step read out of TMEM (8 warps arrive)
+  uint64_t* dq_staged = bars + 14;     // dQ of this step staged in shared memory (8 warps arrive)
+  uint64_t* dq_stage_free = bars + 15; // the reduction of this step's dQ has read the staging tile
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -520,14 +535,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(kv_empty, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < L::QSTAGES; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
     mbar_init(sdp_full, 1); mbar_init(pds_full, ATT_BWD_ROW_WARPS); mbar_init(dq_full, 1);
     mbar_init(dq_free, ATT_BWD_ROW_WARPS); mbar_init(dkv_free, ATT_BWD_ROW_WARPS);
+    mbar_init(sdp_read, ATT_BWD_ROW_WARPS);
+    mbar_init(dq_staged, ATT_BWD_ROW_WARPS); mbar_init(dq_stage_free, 1);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
   }
-  constexpr int MMA_WARP = ATT_BWD_ROW_WARPS, TMA_WARP = ATT_BWD_ROW_WARPS + 1;
+  constexpr int MMA_WARP = ATT_BWD_ROW_WARPS, TMA_WARP = ATT_BWD_ROW_WARPS + 1, RED_WARP = ATT_BWD_ROW_WARPS + 2;
   if (warp == MMA_WARP) {
     tmem_alloc(tmem_holder, 512);
     tmem_relinquish();
@@ -558,8 +575,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
         att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
         for (int it = 0; it < steps; ++it, ++g) {
-          const int s = g & 1;
-          if (!mbar_wait(&q_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
+          const int s = g % L::QSTAGES;
+          if (!mbar_wait(&q_empty[s], ((g / L::QSTAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
           mbar_expect_tx(&q_full[s], 2 * ATT_TILE_BYTES);
           const int qrow = b * T + (j + it) * ATT_BQ;
           att_load_tile(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], hs, h, qrow);
@@ -590,10 +607,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         if (!att_item(r, cta, G, total, idx)) continue;
         const int steps = nq - idx / n_bh;
         if (!mbar_wait(kv_full, w & 1, abort_flag, status)) break;
-        // S = Q K^T and dP = dO V^T of global step gs (operands in stage gs & 1)
+        // S = Q K^T and dP = dO V^T of global step gs (operands in stage gs % QSTAGES); the row threads must have
+        // read the pair of the step before out of TMEM
         auto issue_sdp = [&](uint32_t gs) -> bool {
-          const int st = gs & 1;
-          if (!mbar_wait(&q_full[st], (gs >> 1) & 1, abort_flag, status)) return false;
+          const int st = gs % L::QSTAGES;
+          if (gs > 0 && !mbar_wait(sdp_read, (gs - 1) & 1, abort_flag, status)) return false;
+          if (!mbar_wait(&q_full[st], (gs / L::QSTAGES) & 1, abort_flag, status)) return false;
           tc_fence_after();
           const uint32_t q_km = smem_desc_lo(smem_u32(smem + L::Q_OFF + st * ATT_TILE_BYTES), 16);
           const uint32_t do_km = smem_desc_lo(smem_u32(smem + L::DO_OFF + st * ATT_TILE_BYTES), 16);
@@ -607,17 +626,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         };
         ok = issue_sdp(g);
         for (int it = 0; it < steps && ok; ++it, ++g) {
-          const int s = g & 1;
+          const int s = g % L::QSTAGES;
           const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
           const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
           const uint32_t q_mn = smem_desc_lo(sq, ATT_TILE_BYTES), do_mn = smem_desc_lo(sdo, ATT_TILE_BYTES);
-          if (!mbar_wait(pds_full, g & 1, abort_flag, status)) { ok = false; break; }
-          ATT_TRACE(tr, 256, tslot);          // P, dS ready
-          // The row threads have read S and dP of this step (they did before writing P / dS), so the next
-          // step's pair goes first: they turn it into P / dS in registers while the products below run.
+          // The next step's pair goes as soon as the row threads have S and dP of this one in registers, while
+          // they are still writing P / dS: they find it finished when they come back for it.
           // (Not across items: the next item's K and V replace the ones the dQ product below still reads.)
           if (it + 1 < steps && !issue_sdp(g + 1)) { ok = false; break; }
-          if (g > 0 && !mbar_wait(dq_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+          if (!mbar_wait(pds_full, g & 1, abort_flag, status)) { ok = false; break; }
+          ATT_TRACE(tr, 256, tslot);          // P, dS ready
           // a new item starts its dV / dK sums from zero: the previous item's must have been read out
           if (it == 0 && w > 0 && !mbar_wait(dkv_free, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
@@ -627,16 +645,54 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
             umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+          umma_commit(&q_empty[s]);         // Q_i and dO_i have their last readers queued: the stage reloads early
+          // the previous step's dQ has been read out of TMEM (the row threads do that right after their hand-over)
+          if (g > 0 && !mbar_wait(dq_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
             umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
           umma_commit(dq_full);
-          umma_commit(&q_empty[s]);
           if (it + 1 == steps) umma_commit(kv_empty);
           ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
         }
         ++w;
       }
+    }
+  } else if (warp == RED_WARP) {
+    // ------------------------------------------------------------ dQ reducer
+    // One TMA reduce-add per staged dQ tile into the fp32 dQ scratch.  Issuing a bulk reduction can hold the
+    // issuing thread for most of a microsecond while earlier reductions drain into L2, so a thread of its own
+    // does it: nothing on a row thread's path waits for global atomics.
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool ok = true;
+      for (int rr = 0; rr < rounds && ok; ++rr) {
+        int idx;
+        if (!att_item(rr, cta, G, total, idx)) continue;
+        const int j = idx / n_bh, bh = idx % n_bh;
+        const int b = bh / nh, h = bh - b * nh;
+        for (int i = j; i < nq; ++i, ++g) {
+          if (!mbar_wait(dq_staged, g & 1, abort_flag, status)) { ok = false; break; }
+          const int row_g = b * T + i * ATT_BQ;
+          if (hs == 64) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tmap_dq), "r"(h * ATT_HS + hh * 32), "r"(row_g),
+                             "r"(smem_u32(smem + L::DQ_OFF + hh * ATT_TILE_BYTES))
+                           : "memory");
+          } else {          // 32 columns per head: the first staging half is the whole dQ tile
+            asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                         ::"l"(&tmap_dq), "r"(0), "r"(h), "r"(row_g), "r"(smem_u32(smem + L::DQ_OFF))
+                         : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(dq_stage_free);
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
     }
   } else {
     // ------------------------------------------------------------ row threads
@@ -648,14 +704,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     bool ok = true;
     if (threadIdx.x != 0) tr = nullptr;
     uint8_t* sdq = smem + L::DQ_OFF + half * ATT_TILE_BYTES;     // this thread's half: [128 rows][32 fp32]
-    const bool elected = threadIdx.x == 0;
     uint32_t g = 0;
-    // dQ of global step gs (query rows from row_g, head h): TMEM -> registers -> swizzled shared tile -> one
-    // TMA reduce-add per half into the fp32 dQ scratch.  The bulk reduction runs asynchronously, so no
-    // thread waits on global atomics.
-    auto drain_dq = [&](uint32_t gs, int row_g, int h) -> bool {
+    // dQ of global step gs: TMEM -> registers -> swizzled shared tile, which the reducer warp adds into the
+    // fp32 dQ scratch.
+    auto drain_dq = [&](uint32_t gs) -> bool {
       if (!mbar_wait(dq_full, gs & 1, abort_flag, status)) return false;
       tc_fence_after();
+      ATT_TRACE(tr, 0, tslot);                // dQ product done
       uint32_t v[32];
       tmem_ld_32x32(tm_dq + lane_addr + half * 32, v);
       tmem_ld_wait();
@@ -663,28 +718,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
       // the previous reduction must have finished reading the staging tile
-      if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (gs > 0 && !mbar_wait(dq_stage_free, (gs - 1) & 1, abort_flag, status)) return false;
+      ATT_TRACE(tr, 0, tslot);                // the previous reduction has let go of the staging tile
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *reinterpret_cast<uint4*>(sdq + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
       fence_proxy_async();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (elected) {
-        if (hs == 64) {
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh)
-            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                         ::"l"(&tmap_dq), "r"(h * ATT_HS + hh * 32), "r"(row_g),
-                           "r"(smem_u32(smem + L::DQ_OFF + hh * ATT_TILE_BYTES))
-                         : "memory");
-        } else {          // 32 columns per head: the first staging half is the whole dQ tile
-          asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
-                       ::"l"(&tmap_dq), "r"(0), "r"(h), "r"(row_g), "r"(smem_u32(smem + L::DQ_OFF))
-                       : "memory");
-        }
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_staged);
+      ATT_TRACE(tr, 0, tslot);                // staged
       return true;
     };
     for (int rr = 0; rr < rounds && ok; ++rr) {
@@ -693,14 +735,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       const int j = idx / n_bh, bh = idx % n_bh;
       const int b = bh / nh, h = bh - b * nh;
       const int steps = nq - j;
+      float lse_next = 0.f, D_next = 0.f;
       for (int it = 0; it < steps && ok; ++it, ++g) {
         const int i = j + it;
         const long long stat = (long long)bh * T + i * ATT_BQ + r;
-        const float lse2 = lse[stat] * 1.4426950408889634f;
-        const float Dr = Dvec[stat];
+        // row statistics: loaded for the first step of an item, fetched one step ahead after that
+        const float lse2 = (it == 0 ? lse[stat] : lse_next) * 1.4426950408889634f;
+        const float Dr = it == 0 ? Dvec[stat] : D_next;
         ATT_TRACE(tr, 0, tslot);              // step start
         if (!mbar_wait(sdp_full, g & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
+        if (it + 1 < steps) { lse_next = lse[stat + ATT_BQ]; D_next = Dvec[stat + ATT_BQ]; }
         ATT_TRACE(tr, 0, tslot);              // S, dP arrived
         // P and dS of this thread's 64 columns, in registers: the previous step's products may still be
         // reading the shared P / dS tiles
@@ -715,17 +760,29 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           if (it == 0) bwd_row_chunk<true>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
           else         bwd_row_chunk<false>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_read);   // S and dP are in registers: the next pair may replace them
         ATT_TRACE(tr, 0, tslot);              // P, dS computed
-        // the previous step's MMAs must be done with P / dS before they are overwritten
+        // the previous step's products must be done with P / dS before they are overwritten (the last step of
+        // the item before was waited for when its dQ was taken out)
         if (it > 0 && !mbar_wait(dq_full, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
-            const uint32_t off = p_offset(r, half * 64 + cc * 32 + c);
             const int q = c >> 1;
-            *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk_p[cc][q], pk_p[cc][q + 1], pk_p[cc][q + 2], pk_p[cc][q + 3]);
-            *reinterpret_cast<uint4*>(sds + off) = make_uint4(pk_ds[cc][q], pk_ds[cc][q + 1], pk_ds[cc][q + 2], pk_ds[cc][q + 3]);
+            *reinterpret_cast<uint4*>(sds + p_offset(r, half * 64 + cc * 32 + c)) =
+                make_uint4(pk_ds[cc][q], pk_ds[cc][q + 1], pk_ds[cc][q + 2], pk_ds[cc][q + 3]);
+          }
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            const int q = c >> 1;
+            *reinterpret_cast<uint4*>(sp + p_offset(r, half * 64 + cc * 32 + c)) =
+                make_uint4(pk_p[cc][q], pk_p[cc][q + 1], pk_p[cc][q + 2], pk_p[cc][q + 3]);
           }
         }
         ATT_TRACE(tr, 0, tslot);              // P, dS written
@@ -735,10 +792,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         if (lane == 0) mbar_arrive(pds_full);
         // the previous step's dQ leaves after the hand-over, off the critical path (the next dQ product
         // waits for its read-out)
-        if (it > 0 && !drain_dq(g - 1, b * T + (i - 1) * ATT_BQ, h)) { ok = false; break; }
+        if (it > 0 && !drain_dq(g - 1)) { ok = false; break; }
       }
       // the last step's dQ; its barrier also says that every dV / dK product of the item is done
-      if (!ok || !drain_dq(g - 1, b * T + (nq - 1) * ATT_BQ, h)) { ok = false; break; }
+      if (!ok || !drain_dq(g - 1)) { ok = false; break; }
       // dV and dK rows of this kv tile (TMEM lane = kv row)
       __nv_bfloat16* row = dqkv + (long long)(b * T + j * ATT_BK + r) * 3 * d + h * hs;
       uint32_t vk[32], vv[32];
@@ -764,7 +821,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         }
       }
     }
-    if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
   }
 
   tc_fence_before();
@@ -846,10 +902,13 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
       return -2;
     attr_set = true;
   }
-  if (cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * T * d, st) != cudaSuccess) return -4;
-  const long long warps = (long long)B * T * nh;
-  attention_bwd_prep_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, B, T, nh, hs);
+  // D = rowsum(dO * O) per head, and the dQ accumulator zeroed in the same pass
+  {
+    const long long want = (rows * 32 + 255) / 256;
+    const int cap = att_num_sms() * 16;
+    attention_bwd_prep_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+        (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, Dvec, dq_acc, B, T, nh, hs);
+  }
   // persistent: one CTA per SM walks the work items
   const int total = (T / ATT_BK) * B * nh;
   const int G = total < att_num_sms() ? total : att_num_sms();
