@@ -498,8 +498,9 @@ constexpr int ATT_BWD_THREADS = 32 * (ATT_BWD_ROW_WARPS + 3);    // + MMA issuer
 
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
-                     const __grid_constant__ CUtensorMap tmap_dq, const float* __restrict__ lse,
-                     const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv, int T, int nh, int n_bh, int hs,
+                     const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ CUtensorMap tmap_dkv,
+                     const float* __restrict__ lse, const float* __restrict__ Dvec, __nv_bfloat16* __restrict__ dqkv,
+                     int T, int nh, int n_bh, int hs,
                      float scale, int* status, long long* trace) {
   using L = AttBwdSmem;
   extern __shared__ uint8_t smem_raw[];
@@ -520,7 +521,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   uint64_t* sdp_read = bars + 13;      // S and dP of this step read out of TMEM (8 warps arrive)
   uint64_t* dq_staged = bars + 14;     // dQ of this step staged in shared memory (8 warps arrive)
   uint64_t* dq_stage_free = bars + 15; // the reduction of this step's dQ has read the staging tile
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* dkv_staged = bars + 16;    // dK, dV of the item staged in the P buffer (8 warps arrive; hs = 64)
+  uint64_t* dkv_stored = bars + 17;    // their bulk stores have read the P buffer
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -540,6 +543,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     mbar_init(dq_free, ATT_BWD_ROW_WARPS); mbar_init(dkv_free, ATT_BWD_ROW_WARPS);
     mbar_init(sdp_read, ATT_BWD_ROW_WARPS);
     mbar_init(dq_staged, ATT_BWD_ROW_WARPS); mbar_init(dq_stage_free, 1);
+    mbar_init(dkv_staged, ATT_BWD_ROW_WARPS); mbar_init(dkv_stored, 1);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -574,6 +578,22 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
         att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
         att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
+        if (hs == 64) {
+          // the next item's K and V (and its first Q, dO) are asked into L2 now: their load, which can only
+          // start when this item's last product has let go of K and V, then finds them there
+          for (int r2 = r + 1; r2 < rounds; ++r2) {
+            int idx2;
+            if (!att_item(r2, cta, G, total, idx2)) continue;
+            const int j2 = idx2 / n_bh, bh2 = idx2 % n_bh;
+            const int b2 = bh2 / nh, h2 = bh2 - b2 * nh;
+            const int row2 = b2 * T + j2 * ATT_BK;
+            tma_prefetch_l2_2d(&tmap_qkv, (nh + h2) * 64, row2);
+            tma_prefetch_l2_2d(&tmap_qkv, (2 * nh + h2) * 64, row2);
+            tma_prefetch_l2_2d(&tmap_qkv, h2 * 64, row2);
+            tma_prefetch_l2_2d(&tmap_do, h2 * 64, row2);
+            break;
+          }
+        }
         for (int it = 0; it < steps; ++it, ++g) {
           const int s = g % L::QSTAGES;
           if (!mbar_wait(&q_empty[s], ((g / L::QSTAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
@@ -639,21 +659,30 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           // a new item starts its dV / dK sums from zero: the previous item's must have been read out
           if (it == 0 && w > 0 && !mbar_wait(dkv_free, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
+          const bool last = it + 1 == steps;
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
             umma_bf16_lohi(tm_dv, p_mn + k * MNSTEP, do_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+          auto issue_dk = [&]() {
 #pragma unroll
-          for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
-            umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
-          umma_commit(&q_empty[s]);         // Q_i and dO_i have their last readers queued: the stage reloads early
+            for (int k = 0; k < 8; ++k)     // dK += dS^T Q_i
+              umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+            umma_commit(&q_empty[s]);       // Q_i and dO_i have their last readers queued: the stage reloads early
+          };
+          // On the last step of an item dQ goes before dK: it is the last reader of K (V was done with the
+          // last dP), so the next item's K and V load while dK still runs.
+          if (!last) issue_dk();
           // the previous step's dQ has been read out of TMEM (the row threads do that right after their hand-over)
           if (g > 0 && !mbar_wait(dq_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
             umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
+          if (last) {
+            umma_commit(kv_empty);
+            issue_dk();
+          }
           umma_commit(dq_full);
-          if (it + 1 == steps) umma_commit(kv_empty);
           ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
         }
         ++w;
@@ -665,7 +694,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     // issuing thread for most of a microsecond while earlier reductions drain into L2, so a thread of its own
     // does it: nothing on a row thread's path waits for global atomics.
     if (lane == 0) {
-      uint32_t g = 0;
+      uint32_t g = 0, w = 0;
       bool ok = true;
       for (int rr = 0; rr < rounds && ok; ++rr) {
         int idx;
@@ -691,8 +720,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           mbar_arrive(dq_stage_free);
         }
+        if (ok && hs == 64) {
+          // dK and dV of the item: two [128 x 64] bf16 tiles staged in the P buffer, one bulk store each
+          if (!mbar_wait(dkv_staged, w & 1, abort_flag, status)) break;
+          const int kvrow = b * T + j * ATT_BK;
+#pragma unroll
+          for (int which = 0; which < 2; ++which)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(&tmap_dkv), "r"(((which + 1) * nh + h) * ATT_HS), "r"(kvrow),
+                           "r"(smem_u32(smem + L::P_OFF + which * ATT_TILE_BYTES))
+                         : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(dkv_stored);
+        }
+        ++w;
       }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions complete before exit
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // reductions and stores complete before exit
     }
   } else {
     // ------------------------------------------------------------ row threads
@@ -704,7 +748,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
     bool ok = true;
     if (threadIdx.x != 0) tr = nullptr;
     uint8_t* sdq = smem + L::DQ_OFF + half * ATT_TILE_BYTES;     // this thread's half: [128 rows][32 fp32]
-    uint32_t g = 0;
+    uint32_t g = 0, w = 0;
+    float lse_next = 0.f, D_next = 0.f;
     // dQ of global step gs: TMEM -> registers -> swizzled shared tile, which the reducer warp adds into the
     // fp32 dQ scratch.
     auto drain_dq = [&](uint32_t gs) -> bool {
@@ -735,17 +780,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       const int j = idx / n_bh, bh = idx % n_bh;
       const int b = bh / nh, h = bh - b * nh;
       const int steps = nq - j;
-      float lse_next = 0.f, D_next = 0.f;
+      // where the next item's first step finds its row statistics (-1: this is the CTA's last item)
+      int stat_after = -1;
+      for (int r2 = rr + 1; r2 < rounds; ++r2) {
+        int idx2;
+        if (att_item(r2, cta, G, total, idx2)) {
+          stat_after = (idx2 % n_bh) * T + (idx2 / n_bh) * ATT_BQ + r;
+          break;
+        }
+      }
       for (int it = 0; it < steps && ok; ++it, ++g) {
         const int i = j + it;
-        const long long stat = (long long)bh * T + i * ATT_BQ + r;
-        // row statistics: loaded for the first step of an item, fetched one step ahead after that
-        const float lse2 = (it == 0 ? lse[stat] : lse_next) * 1.4426950408889634f;
-        const float Dr = it == 0 ? Dvec[stat] : D_next;
+        const int stat = bh * T + i * ATT_BQ + r;       // < 2^31: the launcher checks B * nh * T
+        // row statistics: loaded for the CTA's first step, fetched one step ahead (across items too) after that
+        const float lse2 = (g == 0 ? lse[stat] : lse_next) * 1.4426950408889634f;
+        const float Dr = g == 0 ? Dvec[stat] : D_next;
         ATT_TRACE(tr, 0, tslot);              // step start
         if (!mbar_wait(sdp_full, g & 1, abort_flag, status)) { ok = false; break; }
         tc_fence_after();
-        if (it + 1 < steps) { lse_next = lse[stat + ATT_BQ]; D_next = Dvec[stat + ATT_BQ]; }
+        {
+          const int sn = it + 1 < steps ? stat + ATT_BQ : stat_after;
+          if (sn >= 0) { lse_next = lse[sn]; D_next = Dvec[sn]; }
+        }
         ATT_TRACE(tr, 0, tslot);              // S, dP arrived
         // P and dS of this thread's 64 columns, in registers: the previous step's products may still be
         // reading the shared P / dS tiles
@@ -767,6 +823,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         // the previous step's products must be done with P / dS before they are overwritten (the last step of
         // the item before was waited for when its dQ was taken out)
         if (it > 0 && !mbar_wait(dq_full, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
+        // ... and the bulk stores of the item before with the dK / dV tiles staged in the P buffer
+        if (it == 0 && w > 0 && hs == 64 && !mbar_wait(dkv_stored, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
@@ -805,7 +863,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dkv_free);          // the next item's first products may overwrite the sums
-      if (half * 32 < hs) {
+      if (hs == 64) {
+        // staged as two 128-byte-swizzled [128 x 64] bf16 tiles (dK, dV) in the P buffer, which nothing reads
+        // any more; the reducer warp stores them with one bulk copy each
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t* v = which == 0 ? vk : vv;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(sp + which * ATT_TILE_BYTES + r * 128 + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(
+                pack_bf16(__uint_as_float(v[8 * c]), __uint_as_float(v[8 * c + 1])),
+                pack_bf16(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3])),
+                pack_bf16(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5])),
+                pack_bf16(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7])));
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dkv_staged);
+      } else if (half * 32 < hs) {
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           __nv_bfloat16* dst = row + (which == 0 ? d : 2 * d) + half * 32;
@@ -820,6 +895,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           }
         }
       }
+      ++w;
     }
   }
 
@@ -880,17 +956,19 @@ extern "C" int dsw_attention_fwd(const void* qkv, void* out, float* lse, int B, 
 extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
                                  float* dq_acc, float* Dvec, int B, int T, int nh, int hs, float scale, int* status,
                                  cudaStream_t st) {
-  if ((hs != 64 && hs != 32) || T % ATT_BQ != 0) return -10;
+  if ((hs != 64 && hs != 32) || T % ATT_BQ != 0 || (long long)B * nh * T >= (1LL << 31)) return -10;
   const int d = nh * hs;
   const long long rows = (long long)B * T;
-  CUtensorMap tq, tdo, tdq;
+  CUtensorMap tq, tdo, tdq, tdkv;
   int rc;
   if (hs == 64) {
     rc = make_tmap_bf16_2d(&tq, qkv, 3LL * d, rows, 3LL * d, 64, 128);
+    if (!rc) rc = make_tmap_bf16_2d(&tdkv, dqkv, 3LL * d, rows, 3LL * d, 64, 128);
     if (!rc) rc = make_tmap_bf16_2d(&tdo, dout, d, rows, d, 64, 128);
     if (!rc) rc = make_tmap_f32_2d(&tdq, dq_acc, d, rows, d, 32, 128);
   } else {
     rc = make_tmap_3d(&tq, 0, qkv, hs, 3LL * nh, rows, 3LL * d, 64, 128);
+    tdkv = tq;            // not used with 32 columns per head: dK and dV are stored by the row threads
     if (!rc) rc = make_tmap_3d(&tdo, 0, dout, hs, nh, rows, d, 64, 128);
     if (!rc) rc = make_tmap_3d(&tdq, 1, dq_acc, hs, nh, rows, d, 32, 128);
   }
@@ -912,7 +990,7 @@ extern "C" int dsw_attention_bwd(const void* qkv, const void* out, const void* d
   // persistent: one CTA per SM walks the work items
   const int total = (T / ATT_BK) * B * nh;
   const int G = total < att_num_sms() ? total : att_num_sms();
-  attention_bwd_kernel<<<G, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, lse, Dvec, (__nv_bfloat16*)dqkv, T, nh,
+  attention_bwd_kernel<<<G, ATT_BWD_THREADS, AttBwdSmem::TOTAL, st>>>(tq, tdo, tdq, tdkv, lse, Dvec, (__nv_bfloat16*)dqkv, T, nh,
                                                                        B * nh, hs, scale, status, g_att_trace);
   attention_dq_convert_kernel<<<148 * 4, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, (long long)B * T, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

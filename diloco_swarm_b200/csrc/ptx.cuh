@@ -107,6 +107,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
+// Asks a 2-D tile into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 // 2-D tiled load, global -> this CTA's shared memory, completion on an mbarrier.
 // x is the innermost coordinate (must be a multiple of 16 bytes in elements).
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y) {
