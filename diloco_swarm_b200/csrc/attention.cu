@@ -411,10 +411,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 // dQ is accumulated across kv tiles with fp32 reductions into a scratch tensor
 // and converted to bf16 afterwards; dK and dV are written directly.
 struct AttBwdSmem {
-  static constexpr int K_OFF = 0;
+  static constexpr int KV_BYTES = 2 * ATT_TILE_BYTES;               // K_j then V_j
+  static constexpr int K_OFF = 0;                                   // 2 buffers (item parity) of (K, V)
   static constexpr int V_OFF = K_OFF + ATT_TILE_BYTES;
-  static constexpr int QSTAGES = 3;                                 // (Q_i, dO_i) pairs in flight
-  static constexpr int Q_OFF = V_OFF + ATT_TILE_BYTES;
+  static constexpr int QSTAGES = 2;                                 // (Q_i, dO_i) pairs in flight
+  static constexpr int Q_OFF = K_OFF + 2 * KV_BYTES;
   static constexpr int DO_OFF = Q_OFF + QSTAGES * ATT_TILE_BYTES;
   static constexpr int P_OFF = DO_OFF + QSTAGES * ATT_TILE_BYTES;   // 2 k-blocks
   static constexpr int DS_OFF = P_OFF + 2 * ATT_TILE_BYTES;         // 2 k-blocks
@@ -422,6 +423,7 @@ struct AttBwdSmem {
   static constexpr int BAR_OFF = DQ_OFF + 2 * ATT_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
+
 
 // D[bh, t] = sum_c dO[t, h*hs + c] * O[t, h*hs + c], and dq_acc[t, :] = 0.  One warp per token row: 16-byte
 // loads, one head's hs columns lie in hs/8 neighbouring lanes (hs = 64 or 32), which a few shuffles add up.
@@ -509,14 +511,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   // phase per step, kv_full / kv_empty / dkv_free one per item, counted over the life of the CTA
   // (g = steps done, w = items done).
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* kv_full = bars;            // K, V of the item loaded
-  uint64_t* q_full = bars + 1;         // QSTAGES stages of (Q_i, dO_i)
-  uint64_t* q_empty = bars + 4;        // QSTAGES
-  uint64_t* sdp_full = bars + 7;       // S and dP ready
-  uint64_t* pds_full = bars + 8;       // P and dS in shared memory (8 warps arrive)
-  uint64_t* dq_full = bars + 9;        // dV/dK/dQ MMAs of this step done
-  uint64_t* dq_free = bars + 10;       // dQ read out of TMEM (8 warps arrive)
-  uint64_t* kv_empty = bars + 11;      // every MMA of the item done: K, V may be overwritten
+  uint64_t* kv_full = bars;            // 2: K, V of the item loaded (buffer = item parity)
+  uint64_t* kv_empty = bars + 2;       // 2: every MMA of the item done: its K, V may be overwritten
+  uint64_t* q_full = bars + 4;         // QSTAGES stages of (Q_i, dO_i)
+  uint64_t* q_empty = bars + 6;        // QSTAGES
+  uint64_t* sdp_full = bars + 8;       // S and dP ready
+  uint64_t* pds_full = bars + 9;       // P and dS in shared memory (8 warps arrive)
+  uint64_t* dq_full = bars + 10;       // dV/dK/dQ MMAs of this step done
+  uint64_t* dq_free = bars + 11;       // dQ read out of TMEM (8 warps arrive)
   uint64_t* dkv_free = bars + 12;      // dK, dV of the item read out of TMEM (8 warps arrive)
   uint64_t* sdp_read = bars + 13;      // S and dP of this step read out of TMEM (8 warps arrive)
   uint64_t* dq_staged = bars + 14;     // dQ of this step staged in shared memory (8 warps arrive)
@@ -537,7 +539,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
   int tslot = 0;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(kv_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < L::QSTAGES; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
     mbar_init(sdp_full, 1); mbar_init(pds_full, ATT_BWD_ROW_WARPS); mbar_init(dq_full, 1);
     mbar_init(dq_free, ATT_BWD_ROW_WARPS); mbar_init(dkv_free, ATT_BWD_ROW_WARPS);
@@ -573,27 +575,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         const int j = idx / n_bh, bh = idx % n_bh;
         const int b = bh / nh, h = bh - b * nh;
         const int steps = nq - j;
-        if (w > 0 && !mbar_wait(kv_empty, (w - 1) & 1, abort_flag, status)) break;
+        // K and V of the item go into the buffer of its parity, free since the item two back finished: they
+        // are on their way while the item before still runs
+        const int kb = w & 1;
+        if (!mbar_wait(&kv_empty[kb], ((w >> 1) & 1) ^ 1, abort_flag, status)) break;
         const int kvrow = b * T + j * ATT_BK;
-        mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
-        att_load_tile(smem + L::K_OFF, &tmap_qkv, kv_full, hs, nh + h, kvrow);
-        att_load_tile(smem + L::V_OFF, &tmap_qkv, kv_full, hs, 2 * nh + h, kvrow);
-        if (hs == 64) {
-          // the next item's K and V (and its first Q, dO) are asked into L2 now: their load, which can only
-          // start when this item's last product has let go of K and V, then finds them there
-          for (int r2 = r + 1; r2 < rounds; ++r2) {
-            int idx2;
-            if (!att_item(r2, cta, G, total, idx2)) continue;
-            const int j2 = idx2 / n_bh, bh2 = idx2 % n_bh;
-            const int b2 = bh2 / nh, h2 = bh2 - b2 * nh;
-            const int row2 = b2 * T + j2 * ATT_BK;
-            tma_prefetch_l2_2d(&tmap_qkv, (nh + h2) * 64, row2);
-            tma_prefetch_l2_2d(&tmap_qkv, (2 * nh + h2) * 64, row2);
-            tma_prefetch_l2_2d(&tmap_qkv, h2 * 64, row2);
-            tma_prefetch_l2_2d(&tmap_do, h2 * 64, row2);
-            break;
-          }
-        }
+        mbar_expect_tx(&kv_full[kb], 2 * ATT_TILE_BYTES);
+        att_load_tile(smem + L::K_OFF + kb * L::KV_BYTES, &tmap_qkv, &kv_full[kb], hs, nh + h, kvrow);
+        att_load_tile(smem + L::V_OFF + kb * L::KV_BYTES, &tmap_qkv, &kv_full[kb], hs, 2 * nh + h, kvrow);
         for (int it = 0; it < steps; ++it, ++g) {
           const int s = g % L::QSTAGES;
           if (!mbar_wait(&q_empty[s], ((g / L::QSTAGES) & 1) ^ 1, abort_flag, status)) { ok = false; break; }
@@ -615,74 +604,80 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
       // (leading offset = one tile) step 16 rows of 128 bytes; the high word is the same for all.
       constexpr uint32_t KSTEP = 32 >> 4, MNSTEP = 2048 >> 4, TILE16 = ATT_TILE_BYTES >> 4;
       const uint32_t desc_hi = smem_desc_hi(1024);
-      const uint32_t k_km = smem_desc_lo(smem_u32(smem + L::K_OFF), 16), v_km = smem_desc_lo(smem_u32(smem + L::V_OFF), 16);
-      const uint32_t k_mn = smem_desc_lo(smem_u32(smem + L::K_OFF), ATT_TILE_BYTES);
+      // K and V descriptors of buffer 0; buffer 1 lies KVBUF16 further
+      const uint32_t k_km0 = smem_desc_lo(smem_u32(smem + L::K_OFF), 16), v_km0 = smem_desc_lo(smem_u32(smem + L::V_OFF), 16);
+      const uint32_t k_mn0 = smem_desc_lo(smem_u32(smem + L::K_OFF), ATT_TILE_BYTES);
+      constexpr uint32_t KVBUF16 = L::KV_BYTES >> 4;
       const uint32_t p_mn = smem_desc_lo(smem_u32(smem + L::P_OFF), ATT_TILE_BYTES);
       const uint32_t ds_mn = smem_desc_lo(smem_u32(smem + L::DS_OFF), ATT_TILE_BYTES);
       const uint32_t ds_km = smem_desc_lo(smem_u32(smem + L::DS_OFF), 16);
       uint32_t g = 0, w = 0;
       bool ok = true;
+      // S = Q K^T and dP = dO V^T of global step gs, which belongs to item wi (operands: Q/dO stage
+      // gs % QSTAGES, K/V buffer wi & 1).  The row threads must have read the pair of the step before out of
+      // TMEM; the first step of an item also waits for its K and V.
+      auto issue_sdp = [&](uint32_t gs, uint32_t wi, bool first_of_item) -> bool {
+        const int st = gs % L::QSTAGES, kb = wi & 1;
+        if (gs > 0 && !mbar_wait(sdp_read, (gs - 1) & 1, abort_flag, status)) return false;
+        if (first_of_item && !mbar_wait(&kv_full[kb], (wi >> 1) & 1, abort_flag, status)) return false;
+        if (!mbar_wait(&q_full[st], (gs / L::QSTAGES) & 1, abort_flag, status)) return false;
+        tc_fence_after();
+        const uint32_t q_km = smem_desc_lo(smem_u32(smem + L::Q_OFF + st * ATT_TILE_BYTES), 16);
+        const uint32_t do_km = smem_desc_lo(smem_u32(smem + L::DO_OFF + st * ATT_TILE_BYTES), 16);
+        const uint32_t k_km = k_km0 + kb * KVBUF16, v_km = v_km0 + kb * KVBUF16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_s, q_km + k * KSTEP, k_km + k * KSTEP, desc_hi, id_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_dp, do_km + k * KSTEP, v_km + k * KSTEP, desc_hi, id_s, k > 0);
+        umma_commit(sdp_full);
+        ATT_TRACE(tr, 256, tslot);          // S, dP issued
+        return true;
+      };
       for (int r = 0; r < rounds && ok; ++r) {
         int idx;
         if (!att_item(r, cta, G, total, idx)) continue;
         const int steps = nq - idx / n_bh;
-        if (!mbar_wait(kv_full, w & 1, abort_flag, status)) break;
-        // S = Q K^T and dP = dO V^T of global step gs (operands in stage gs % QSTAGES); the row threads must have
-        // read the pair of the step before out of TMEM
-        auto issue_sdp = [&](uint32_t gs) -> bool {
-          const int st = gs % L::QSTAGES;
-          if (gs > 0 && !mbar_wait(sdp_read, (gs - 1) & 1, abort_flag, status)) return false;
-          if (!mbar_wait(&q_full[st], (gs / L::QSTAGES) & 1, abort_flag, status)) return false;
-          tc_fence_after();
-          const uint32_t q_km = smem_desc_lo(smem_u32(smem + L::Q_OFF + st * ATT_TILE_BYTES), 16);
-          const uint32_t do_km = smem_desc_lo(smem_u32(smem + L::DO_OFF + st * ATT_TILE_BYTES), 16);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_s, q_km + k * KSTEP, k_km + k * KSTEP, desc_hi, id_s, k > 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16_lohi(tm_dp, do_km + k * KSTEP, v_km + k * KSTEP, desc_hi, id_s, k > 0);
-          umma_commit(sdp_full);
-          ATT_TRACE(tr, 256, tslot);          // S, dP issued
-          return true;
-        };
-        ok = issue_sdp(g);
+        bool more = false;                  // does this CTA have another item after this one?
+        for (int r2 = r + 1; r2 < rounds && !more; ++r2) {
+          int idx2;
+          more = att_item(r2, cta, G, total, idx2);
+        }
+        const int kb = w & 1;
+        const uint32_t k_mn = k_mn0 + kb * KVBUF16;
+        if (w == 0) ok = issue_sdp(0, 0, true);
         for (int it = 0; it < steps && ok; ++it, ++g) {
           const int s = g % L::QSTAGES;
           const uint32_t sq = smem_u32(smem + L::Q_OFF + s * ATT_TILE_BYTES);
           const uint32_t sdo = smem_u32(smem + L::DO_OFF + s * ATT_TILE_BYTES);
           const uint32_t q_mn = smem_desc_lo(sq, ATT_TILE_BYTES), do_mn = smem_desc_lo(sdo, ATT_TILE_BYTES);
           // The next step's pair goes as soon as the row threads have S and dP of this one in registers, while
-          // they are still writing P / dS: they find it finished when they come back for it.
-          // (Not across items: the next item's K and V replace the ones the dQ product below still reads.)
-          if (it + 1 < steps && !issue_sdp(g + 1)) { ok = false; break; }
+          // they are still writing P / dS: they find it finished when they come back for it.  Across items
+          // too: the next item's K and V sit in the other buffer.
+          if (it + 1 < steps) {
+            if (!issue_sdp(g + 1, w, false)) { ok = false; break; }
+          } else if (more) {
+            if (!issue_sdp(g + 1, w + 1, true)) { ok = false; break; }
+          }
           if (!mbar_wait(pds_full, g & 1, abort_flag, status)) { ok = false; break; }
           ATT_TRACE(tr, 256, tslot);          // P, dS ready
           // a new item starts its dV / dK sums from zero: the previous item's must have been read out
           if (it == 0 && w > 0 && !mbar_wait(dkv_free, (w - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
-          const bool last = it + 1 == steps;
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dV += P^T dO_i   (K = query rows, 16 per step)
             umma_bf16_lohi(tm_dv, p_mn + k * MNSTEP, do_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
-          auto issue_dk = [&]() {
 #pragma unroll
-            for (int k = 0; k < 8; ++k)     // dK += dS^T Q_i
-              umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
-            umma_commit(&q_empty[s]);       // Q_i and dO_i have their last readers queued: the stage reloads early
-          };
-          // On the last step of an item dQ goes before dK: it is the last reader of K (V was done with the
-          // last dP), so the next item's K and V load while dK still runs.
-          if (!last) issue_dk();
+          for (int k = 0; k < 8; ++k)       // dK += dS^T Q_i
+            umma_bf16_lohi(tm_dk, ds_mn + k * MNSTEP, q_mn + k * MNSTEP, desc_hi, id_t, (it > 0 || k > 0));
+          umma_commit(&q_empty[s]);         // Q_i and dO_i have their last readers queued: the stage reloads early
           // the previous step's dQ has been read out of TMEM (the row threads do that right after their hand-over)
           if (g > 0 && !mbar_wait(dq_free, (g - 1) & 1, abort_flag, status)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 8; ++k)       // dQ_i = dS K_j     (K = kv rows)
             umma_bf16_lohi(tm_dq, ds_km + (k >> 2) * TILE16 + (k & 3) * KSTEP, k_mn + k * MNSTEP, desc_hi, id_q, k > 0);
-          if (last) {
-            umma_commit(kv_empty);
-            issue_dk();
-          }
           umma_commit(dq_full);
+          if (it + 1 == steps) umma_commit(&kv_empty[kb]);
           ATT_TRACE(tr, 256, tslot);          // dV, dK, dQ issued
         }
         ++w;
