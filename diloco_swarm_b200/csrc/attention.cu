@@ -476,22 +476,25 @@ attention_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __r
 
 // 32 columns of one query row: P = exp2(S * scale_log2 - lse2), dS = P * (dP - D) * scale, both packed to bf16
 // pairs.  MASKED: columns past `r` (above the diagonal) give zero.
-template <bool MASKED>
-__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], uint32_t (&pk_p)[16],
-                                              uint32_t (&pk_ds)[16], int c0, int r, float scale_log2, float lse2,
+template <bool MASKED, int N>
+__device__ __forceinline__ void bwd_row_chunk(const uint32_t (&sv)[N], const uint32_t (&dpv)[N], uint32_t* pk_p,
+                                              uint32_t* pk_ds, int c0, int r, float scale_log2, float lse2,
                                               float Dr, float scale) {
+  // packed fp32 pairs: one instruction per two columns for everything but the exponentials and the packing
+  const f2 sc = f2_bcast(scale_log2), nl = f2_bcast(-lse2), s2 = f2_bcast(scale), nd = f2_bcast(-Dr * scale);
 #pragma unroll
-  for (int c = 0; c < 32; c += 2) {
-    float p0 = fast_exp2(__uint_as_float(sv[c]) * scale_log2 - lse2);
-    float p1 = fast_exp2(__uint_as_float(sv[c + 1]) * scale_log2 - lse2);
+  for (int c = 0; c < N; c += 2) {
+    const f2 x = f2_fma(f2_make(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc, nl);
+    float x0, x1;
+    f2_split(x, x0, x1);
+    float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
     if (MASKED) {
       p0 = c0 + c <= r ? p0 : 0.f;
       p1 = c0 + c + 1 <= r ? p1 : 0.f;
     }
-    const float d0 = p0 * (__uint_as_float(dpv[c]) - Dr) * scale;
-    const float d1 = p1 * (__uint_as_float(dpv[c + 1]) - Dr) * scale;
+    const f2 u = f2_fma(f2_make(__uint_as_float(dpv[c]), __uint_as_float(dpv[c + 1])), s2, nd);    // (dP - D) * scale
     pk_p[c >> 1] = pack_bf16(p0, p1);
-    pk_ds[c >> 1] = pack_bf16(d0, d1);
+    pk_ds[c >> 1] = pack_bf16_f2(f2_mul(f2_make(p0, p1), u));
   }
 }
 
@@ -801,15 +804,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
         // P and dS of this thread's 64 columns, in registers: the previous step's products may still be
         // reading the shared P / dS tiles
         uint32_t pk_p[2][16], pk_ds[2][16];
+        {
+          // all 64 columns of S and of dP leave TMEM in one go (a TMEM load takes a few hundred nanoseconds from
+          // issue to data, whatever its width: four loads in a row would cost four such waits)
+          uint32_t raw[4][2][16];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c0 = half * 64 + cc * 32;
-          uint32_t sv_[32], dpv[32];
-          tmem_ld_32x32(tm_s + lane_addr + c0, sv_);
-          tmem_ld_32x32(tm_dp + lane_addr + c0, dpv);
+          for (int q = 0; q < 4; ++q) {
+            tmem_ld_32x16(tm_s + lane_addr + half * 64 + q * 16, raw[q][0]);
+            tmem_ld_32x16(tm_dp + lane_addr + half * 64 + q * 16, raw[q][1]);
+          }
           tmem_ld_wait();
-          if (it == 0) bwd_row_chunk<true>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
-          else         bwd_row_chunk<false>(sv_, dpv, pk_p[cc], pk_ds[cc], c0, r, scale_log2, lse2, Dr, scale);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int c0 = half * 64 + q * 16;
+            uint32_t* op = &pk_p[q >> 1][(q & 1) * 8];
+            uint32_t* ods = &pk_ds[q >> 1][(q & 1) * 8];
+            if (it == 0) bwd_row_chunk<true, 16>(raw[q][0], raw[q][1], op, ods, c0, r, scale_log2, lse2, Dr, scale);
+            else         bwd_row_chunk<false, 16>(raw[q][0], raw[q][1], op, ods, c0, r, scale_log2, lse2, Dr, scale);
+          }
         }
         tc_fence_before();
         __syncwarp();
