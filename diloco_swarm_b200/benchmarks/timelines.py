@@ -91,14 +91,16 @@ def attention_timeline(B, T, nh):
     torch.cuda.synchronize()
     tr = torch.zeros(512, dtype=torch.int64, device="cuda")
 
-    def show(title, row_labels, mma_labels, mma_prefix=()):
+    def show(title, row_labels, mma_labels, row_first=None, mma_prefix=(), steps=5):
+        """Stamps of one CTA, labelled: ``row_first`` names the (shorter) first step of the row warp."""
         t = tr.cpu().tolist()
         row, mma = [x for x in t[:256] if x], [x for x in t[256:] if x]
         t0 = min(row + mma)
-        names = list(mma_prefix) + [mma_labels[i % len(mma_labels)] for i in range(len(mma_labels) * 4)]
+        rnames = list(row_first or row_labels) + [row_labels[i % len(row_labels)] for i in range(len(row_labels) * (steps - 1))]
+        mnames = list(mma_prefix) + [mma_labels[i % len(mma_labels)] for i in range(len(mma_labels) * steps)]
         print(title)
-        print("  row warp 0 :", " ".join(f"{row_labels[i % len(row_labels)]}={x - t0}" for i, x in enumerate(row[:len(row_labels) * 4])))
-        print("  MMA thread :", " ".join(f"{n}={x - t0}" for n, x in zip(names, mma)))
+        print("  row warp 0 :", " ".join(f"{n}={x - t0}" for n, x in zip(rnames, row)))
+        print("  MMA thread :", " ".join(f"{n}={x - t0}" for n, x in zip(mnames, mma)))
         print(f"  CTA span {max(row + mma) - t0} ns")
 
     set_trace(tr.data_ptr())
@@ -109,9 +111,13 @@ def attention_timeline(B, T, nh):
     tr.zero_()
     attention_bwd(dout, ctx)
     torch.cuda.synchronize()
+    # Row warp, per step: start, S and dP ready, P and dS in registers (S and dP released), P and dS written; from
+    # the second step on, the dQ of the step before follows: its product done, staging tile free, staged.
+    # MMA thread, per step: the next step's S/dP pair issued, P and dS ready, dV/dK/dQ issued.
     show("attention backward, CTA (0,0) (kv tile 0: all query tiles), ns since first stamp",
-         ["start", "S_dP_ready", "P_dS_in_regs", "P_dS_written"],
-         ["P_dS_ready", "next_S_dP_issued", "dV_dK_dQ_issued"], mma_prefix=["S_dP_issued"])
+         ["start", "S_dP_ready", "in_regs", "written", "dQ_done", "stage_free", "staged"],
+         ["next_S_dP_issued", "P_dS_ready", "dV_dK_dQ_issued"],
+         row_first=["start", "S_dP_ready", "in_regs", "written"], mma_prefix=["S_dP_issued"])
     set_trace(None)
 
 

@@ -415,9 +415,11 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
       load8(dx + (long long)row * d + col, v);
       long long id = ids[row];
       if (id < 0 || id >= V) id = 0;
-      float* w = dwte + id * d + col;
+      float* w = dwte + id * d + col;          // 32-byte aligned: two four-wide reductions instead of eight scalar ones
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { atomicAdd(w + j, v[j]); pos[j] += v[j]; }
+      for (int j = 0; j < 8; ++j) pos[j] += v[j];
     }
     float* p = dwpe + (long long)t * d + col;
 #pragma unroll
