@@ -508,32 +508,45 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lon
       for (int i = threadIdx.x; i < nv; i += blockDim.x) *reinterpret_cast<uint4*>(lr + i * 8) = make_uint4(0, 0, 0, 0);
     return;
   }
-  float mx = -INFINITY, sm = 0.f;
+  // Online maximum and sum in base 2 with packed fp32 pairs: e = 2^(v * log2(e) - max * log2(e)) is one packed
+  // multiply-add and two exponentials per pair; the running sum is rescaled only when the maximum grows.
+  constexpr float L2E = 1.4426950408889634f;
+  float mx = -INFINITY;
+  f2 acc = f2_bcast(0.f);
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     if (!DSW_OK(i * 8 + 8 <= V && V <= ld)) continue;
     float v[8];
     load8(lr + i * 8, v);
-    float m8 = v[0];
+    const float m8 = fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7])));
+    if (m8 > mx) {                       // rare after the first few chunks
+      acc = f2_mul(acc, f2_bcast(ex2_approx((mx - m8) * L2E)));      // mx = -inf: factor 0 on an empty sum
+      mx = m8;
+    }
+    const f2 nm = f2_bcast(-mx * L2E), l2 = f2_bcast(L2E);
 #pragma unroll
-    for (int j = 1; j < 8; ++j) m8 = fmaxf(m8, v[j]);
-    const float nm = fmaxf(mx, m8);
-    float s8 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) s8 += __expf(v[j] - nm);
-    sm = sm * __expf(mx - nm) + s8;
-    mx = nm;
+    for (int j = 0; j < 8; j += 2) {
+      float x0, x1;
+      f2_split(f2_fma(f2_make(v[j], v[j + 1]), l2, nm), x0, x1);
+      acc = f2_add(acc, f2_make(ex2_approx(x0), ex2_approx(x1)));
+    }
+  }
+  float sm;
+  {
+    float a0, a1;
+    f2_split(acc, a0, a1);
+    sm = a0 + a1;
   }
   // block reduce (max, sum)
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   // threads (and whole warps) that saw no element carry max = -inf, sum = 0: skip them
   float gm = warp_max(mx);
-  sm = warp_sum(mx == -INFINITY ? 0.f : sm * __expf(mx - gm));
+  sm = warp_sum(mx == -INFINITY ? 0.f : sm * ex2_approx((mx - gm) * L2E));
   if (lane == 0) { shm[w] = gm; shs[w] = sm; }
   __syncthreads();
   float bm = -INFINITY;
   for (int i = 0; i < nw; ++i) bm = fmaxf(bm, shm[i]);
   float bs = 0.f;
-  for (int i = 0; i < nw; ++i) bs += shm[i] == -INFINITY ? 0.f : shs[i] * __expf(shm[i] - bm);
+  for (int i = 0; i < nw; ++i) bs += shm[i] == -INFINITY ? 0.f : shs[i] * ex2_approx((shm[i] - bm) * L2E);
   long long tgt = targets[row];
   if (tgt < 0 || tgt >= V) { if (status && threadIdx.x == 0) atomicCAS(status, 0, ST_BAD_ARG); tgt = 0; }
   const float cnt = count ? fmaxf(count[0], 1.f) : 1.f;
@@ -545,15 +558,27 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lon
   if (!write_grad) return;
   __syncthreads();      // the target logit was read before anyone overwrites it
   const float inv = k / bs;
+  const int tgt_chunk = int(tgt >> 3), tgt_j = int(tgt & 7);
+  const f2 nm = f2_bcast(-bm * L2E), l2 = f2_bcast(L2E), sc = f2_bcast(inv);
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float v[8];
     load8(lr + i * 8, v);
+    uint32_t w[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float p = __expf(v[j] - bm) * inv;
-      v[j] = (i * 8 + j == tgt) ? p - k : p;
+    for (int j = 0; j < 8; j += 2) {
+      float x0, x1;
+      f2_split(f2_fma(f2_make(v[j], v[j + 1]), l2, nm), x0, x1);
+      const f2 pr = f2_mul(f2_make(ex2_approx(x0), ex2_approx(x1)), sc);
+      if (i == tgt_chunk && (tgt_j >> 1) == (j >> 1)) {          // the pair that holds the target: p - k there
+        float p0, p1;
+        f2_split(pr, p0, p1);
+        if (tgt_j & 1) p1 -= k; else p0 -= k;
+        w[j >> 1] = pack_bf16(p0, p1);
+      } else {
+        w[j >> 1] = pack_bf16_f2(pr);
+      }
     }
-    store8(lr + i * 8, v);
+    *reinterpret_cast<uint4*>(lr + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
