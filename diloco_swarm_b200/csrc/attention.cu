@@ -332,15 +332,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
         ATT_TRACE(tr, 0, tslot);              // output rows ready for the next product
         // probabilities -> shared memory (bf16, swizzled K-major), row sum
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        f2 sum2[2] = {f2_bcast(0.f), f2_bcast(0.f)};      // off the diagonal: packed pairs (two columns per instruction)
+        const f2 sc2 = f2_bcast(scale_log2), nm2 = f2_bcast(-m);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
           if (!diag) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float p0 = fast_exp2(__uint_as_float(v[c][i]) * scale_log2 - m);
-              const float p1 = fast_exp2(__uint_as_float(v[c][i + 1]) * scale_log2 - m);
-              sum4[i & 3] += p0; sum4[(i + 1) & 3] += p1;
+              float x0, x1;
+              f2_split(f2_fma(f2_make(__uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1])), sc2, nm2), x0, x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_make(p0, p1));
               pk[i >> 1] = pack_bf16(p0, p1);
             }
           } else {
@@ -356,7 +359,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
           for (int i = 0; i < 16; i += 4)
             *reinterpret_cast<uint4*>(sp + p_offset(r, c * 32 + 2 * i)) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
         }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        {
+          float a0, a1;
+          f2_split(f2_add(sum2[0], sum2[1]), a0, a1);
+          l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) + (a0 + a1);
+        }
         ATT_TRACE(tr, 0, tslot);              // P written
         fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
         tc_fence_before();            // orders the rescaled output rows before the product that follows the arrive
