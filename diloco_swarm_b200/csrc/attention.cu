@@ -415,8 +415,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 // The P / dS tiles are written once and read through two descriptors: K-major
 // (rows = queries) for dQ, and M-major (rows of the transposed operand = kv) for dV / dK;
 // the [128 x 64] Q_i, dO_i, K_j tiles likewise serve as K-major A and as N-major B.
-// dQ is accumulated across kv tiles with fp32 reductions into a scratch tensor
-// and converted to bf16 afterwards; dK and dV are written directly.
+// dQ is accumulated across kv tiles with fp32 bulk reductions into a scratch tensor
+// and converted to bf16 afterwards; dK and dV leave as two bulk stores per item.
+//
+// Eleven warps.  Row warps 0-7 (thread = query row, two threads per row, 64 columns each):
+// wait sdp_full, take S and dP out of TMEM in one load group, arrive sdp_read, compute P / dS
+// in registers, wait dq_full of the step before (its products read P / dS), write P / dS,
+// arrive pds_full, then stage the dQ of the step before for the reducer.  MMA warp (one
+// thread): issues the S / dP pair of step i+1 as soon as sdp_read of step i is complete (also
+// for the first step of the next work item: K and V are double-buffered by item parity),
+// then, on pds_full, dV, dK (releasing the Q / dO stage), dQ.  TMA warp (one thread): K / V
+// of the item into the buffer of its parity, Q / dO pairs into two stages.  Reducer warp (one
+// thread): one bulk reduce-add per staged dQ tile, two bulk stores per item for dK / dV
+// (staged by the row warps in the P buffer, head size 64; with 32 the row warps store them).
+// Every wait is bounded; a wait that runs out sets the CTA's abort flag and the status word.
 struct AttBwdSmem {
   static constexpr int KV_BYTES = 2 * ATT_TILE_BYTES;               // K_j then V_j
   static constexpr int K_OFF = 0;                                   // 2 buffers (item parity) of (K, V)
