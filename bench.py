@@ -79,6 +79,8 @@ def parse_args():
     ap.add_argument("--swarm-steps", type=int, default=-1,
                     help="timed steps of the plain-SWARM side measurement (default min(steps, 8); 0 skips it)")
     ap.add_argument("--no-collective-check", action="store_true")
+    ap.add_argument("--lm-head-chunks", type=int, default=1,
+                    help="slices of a microbatch's rows that the LM head and the cross-entropy run over")
     return ap.parse_args()
 
 
@@ -144,7 +146,7 @@ def build_config(args, S: int, no_outer=None, run_suffix: str = ""):
         model=model,
         data={"path": "synthetic:zipf", "seq_length": args.seq, "num_examples": args.batch * 2, "pin_memory": True},
         train={"micro_batch_size": args.micro_batch, "batch_size": args.batch, "max_steps": 10 ** 6,
-               "max_micro_batches": args.cap, "step_timeout": 600,
+               "max_micro_batches": args.cap, "step_timeout": 600, "lm_head_chunks": args.lm_head_chunks,
                "inner_optimizer": {"type": "AdamW", "lr": 6e-4},
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},

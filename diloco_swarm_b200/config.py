@@ -142,6 +142,10 @@ class TrainConfig(BaseConfig):
     max_norm: float = 1.0
     step_timeout: float = 60
     deterministic: bool = False  # (added) fixed order of additions in the gradient kernels (sorted embedding scatter, no split-K)
+    # (added) the LM head, the cross-entropy and the head's two gradient GEMMs run over this many slices of a
+    # microbatch's token rows, one after the other, so that only a slice of the [tokens, vocabulary] logits
+    # exists at a time (GPT-2 small, 16 x 1024 tokens: 1.65 GB for one slice, 0.41 GB for four); b200 engine
+    lm_head_chunks: int = 1
     inner_optimizer: OptimizerConfig
     outer_optimizer: OptimizerConfig
     scheduler: SchedulerConfig = SchedulerConfig()

@@ -64,6 +64,7 @@ class B200Engine:
                 "model.dropout > 0 is implemented by the autograd engine only (--engine torch); the sm_100a "
                 "kernels train without dropout, as every configuration and experiment of the reference does")
         K.set_deterministic(bool(getattr(config.train, "deterministic", False)))
+        self.head_chunks = max(1, int(getattr(config.train, "lm_head_chunks", 1)))
 
         # ---- flat layout ------------------------------------------------
         self.offsets: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
@@ -396,21 +397,53 @@ class B200Engine:
                         scale, loss, self.count_buf, write_grad=grad, status=self.status)
         return loss, (lnf, mu, rs, logits)
 
+    def _head_chunked(self, x: torch.Tensor, targets, mask, scale: float, grad: bool):
+        """The same head over ``train.lm_head_chunks`` slices of the token rows: logits, cross-entropy and (with
+        ``grad``) the head's weight and input gradients of one slice before the next slice's logits exist
+        (reference: the whole [tokens, vocabulary] tensor, src/model.py:146-147 and src/utils.py:184-193).
+        Returns (loss, lnf, mean, rstd, dlnf or None)."""
+        lnf, mu, rs = K.layernorm_fwd(x, self.lnf_w, self.lnf_b)
+        M, d = lnf.shape
+        V = self.head_w.shape[0]
+        rows = -(-M // self.head_chunks)
+        rows = -(-rows // 256) * 256                     # whole GEMM tiles per slice
+        tg = targets.reshape(-1).contiguous()
+        mk = mask.reshape(-1).contiguous() if mask is not None else None
+        loss = torch.zeros((), dtype=F32, device=x.device)
+        K.count_kept_rows(mk, M, self.count_buf)         # the mean is over the whole microbatch, not over a slice
+        dlnf = torch.empty_like(lnf) if grad else None
+        for r0 in range(0, M, rows):
+            r1 = min(M, r0 + rows)
+            logits = K.gemm(lnf[r0:r1], self.head_w, status=self.status)
+            K.cross_entropy(logits, tg[r0:r1], mk[r0:r1] if mk is not None else None, scale, loss, self.count_buf,
+                            write_grad=grad, status=self.status, count_ready=True)
+            if grad:
+                with self._fork(logits, lnf):
+                    K.gemm(logits, lnf[r0:r1], a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=self.dhead_w,
+                           split_k=K.wgrad_split(V, d, r1 - r0), status=self.status)
+                K.gemm(logits, self.head_w, b_t=False, out=dlnf[r0:r1], status=self.status)
+        return loss, lnf, mu, rs, dlnf
+
     def forward_backward(self, key: int, input_ids, hidden, targets, mask, scale: float, sync: bool = False):
         x, saved, B, T = self._body_fwd(input_ids, hidden, True)
-        loss, (lnf, mu, rs, dlogits) = self._head(x, targets, mask, scale, grad=True)
-        d = x.shape[1]
-        V = dlogits.shape[1]
-        with self._fork(dlogits, lnf):
-            K.gemm(dlogits, lnf, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=self.dhead_w,
-                   split_k=K.wgrad_split(V, d, x.shape[0]), status=self.status)
-        dlnf = K.gemm(dlogits, self.head_w, b_t=False, status=self.status)
+        if self.head_chunks > 1:
+            loss, lnf, mu, rs, dlnf = self._head_chunked(x, targets, mask, scale, grad=True)
+        else:
+            loss, (lnf, mu, rs, dlogits) = self._head(x, targets, mask, scale, grad=True)
+            d = x.shape[1]
+            V = dlogits.shape[1]
+            with self._fork(dlogits, lnf):
+                K.gemm(dlogits, lnf, a_t=True, b_t=False, mode=K.EPI_ATOMIC_F32, out=self.dhead_w,
+                       split_k=K.wgrad_split(V, d, x.shape[0]), status=self.status)
+            dlnf = K.gemm(dlogits, self.head_w, b_t=False, status=self.status)
         dx = K.layernorm_bwd(dlnf, x, self.lnf_w, mu, rs, self.dlnf_w, self.dlnf_b)
         return loss, self._body_bwd(saved, dx, input_ids, B, T, sync=self._want_overlap(sync))
 
     @torch.no_grad()
     def forward_loss(self, input_ids, hidden, targets, mask, scale: float) -> torch.Tensor:
         x, _, _, _ = self._body_fwd(input_ids, hidden, False)
+        if self.head_chunks > 1:
+            return self._head_chunked(x, targets, mask, scale, grad=False)[0]
         loss, _ = self._head(x, targets, mask, scale, grad=False)
         return loss
 

@@ -220,25 +220,33 @@ def embedding_bwd(ids: torch.Tensor, dx: torch.Tensor, dwte: torch.Tensor, dwpe:
                                        stream_ptr()), "dsw_embedding_bwd")
 
 
+def count_kept_rows(mask: Optional[torch.Tensor], M: int, count_buf: torch.Tensor) -> None:
+    """``count_buf[0]`` = number of rows the loss is averaged over (mask != 0, or all M without a mask)."""
+    if mask is not None:
+        assert mask.dtype == torch.long and mask.numel() == M
+        count_buf.zero_()
+        check(cuda_lib().dsw_mask_count(mask.data_ptr(), M, count_buf.data_ptr(), stream_ptr()), "dsw_mask_count")
+    else:
+        count_buf.fill_(float(M))
+
+
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, mask: Optional[torch.Tensor], scale: float,
                   loss_acc: torch.Tensor, count_buf: torch.Tensor, write_grad: bool = True,
-                  status: Optional[Status] = None) -> None:
+                  status: Optional[Status] = None, count_ready: bool = False) -> None:
     """Masked mean cross-entropy times ``scale`` added to ``loss_acc``; with
     ``write_grad`` the logits are overwritten by their gradient (reference:
-    filter_logits_targets + CrossEntropyLoss, src/utils.py:184-193)."""
+    filter_logits_targets + CrossEntropyLoss, src/utils.py:184-193).  With ``count_ready`` the
+    divisor already stands in ``count_buf`` (``count_kept_rows`` over all rows of the microbatch)
+    and ``logits`` may be a slice of its rows."""
     M, V = logits.shape
     assert logits.dtype == BF16 and logits.stride(1) == 1
     assert targets.dtype == torch.long and targets.numel() == M
     lib = cuda_lib()
-    cnt = None
     if mask is not None:
         assert mask.dtype == torch.long and mask.numel() == M
-        count_buf.zero_()
-        check(lib.dsw_mask_count(mask.data_ptr(), M, count_buf.data_ptr(), stream_ptr()), "dsw_mask_count")
-        cnt = count_buf.data_ptr()
-    else:
-        count_buf.fill_(float(M))
-        cnt = count_buf.data_ptr()
+    if not count_ready:
+        count_kept_rows(mask, M, count_buf)
+    cnt = count_buf.data_ptr()
     check(lib.dsw_cross_entropy(logits.data_ptr(), logits.stride(0), targets.data_ptr(), ptr(mask), cnt, scale,
                                 loss_acc.data_ptr(), M, V, 1 if write_grad else 0,
                                 status.ptr if status else None, stream_ptr()), "dsw_cross_entropy")

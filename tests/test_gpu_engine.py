@@ -164,3 +164,26 @@ def test_sgd_inner_optimizer_and_explicit_layer_split():
         first = first if first is not None else loss.item()
     eng.check_status()
     assert loss.item() < first
+
+
+def test_chunked_lm_head_matches_the_whole_one():
+    """train.lm_head_chunks = 4: logits, cross-entropy and the head's gradients over four slices of the token
+    rows give the loss and the gradients of the one-piece head (the divisor is the microbatch's kept-row count,
+    not a slice's)."""
+    _, whole, _ = _engines()
+    cfg4, sliced, _ = _engines(train={"lm_head_chunks": 4})
+    assert sliced.head_chunks == 4 and whole.head_chunks == 1
+    ids, tg, mask = _batch(cfg4, B=16, T=64)
+    l1, _ = whole.forward_backward(0, ids, None, tg, mask, 0.5)
+    l4, _ = sliced.forward_backward(0, ids, None, tg, mask, 0.5)
+    e1 = whole.forward_loss(ids, None, tg, mask, 0.5)
+    e4 = sliced.forward_loss(ids, None, tg, mask, 0.5)
+    torch.cuda.synchronize()
+    whole.check_status()
+    sliced.check_status()
+    assert abs(l1.item() - l4.item()) < 1e-4 * abs(l1.item())
+    assert abs(e1.item() - e4.item()) < 1e-4 * abs(e1.item())
+    for key, _, _ in whole.specs:
+        a, b = whole.g32(key).flatten(), sliced.g32(key).flatten()
+        assert torch.allclose(a, b, rtol=2e-2, atol=2e-3 * a.abs().max().item() + 1e-8), key
+        assert abs(a.norm().item() - b.norm().item()) <= 2e-3 * a.norm().item() + 1e-8, key
