@@ -79,6 +79,8 @@ def parse_args():
     ap.add_argument("--swarm-steps", type=int, default=-1,
                     help="timed steps of the plain-SWARM side measurement (default min(steps, 8); 0 skips it)")
     ap.add_argument("--no-collective-check", action="store_true")
+    ap.add_argument("--reserve-gb", type=float, default=0.0,
+                    help="device memory handed to the caching allocator in one piece at start (train.reserve_memory_gb)")
     ap.add_argument("--lm-head-chunks", type=int, default=1,
                     help="slices of a microbatch's rows that the LM head and the cross-entropy run over")
     return ap.parse_args()
@@ -146,7 +148,7 @@ def build_config(args, S: int, no_outer=None, run_suffix: str = ""):
         model=model,
         data={"path": "synthetic:zipf", "seq_length": args.seq, "num_examples": args.batch * 2, "pin_memory": True},
         train={"micro_batch_size": args.micro_batch, "batch_size": args.batch, "max_steps": 10 ** 6,
-               "max_micro_batches": args.cap, "step_timeout": 600, "lm_head_chunks": args.lm_head_chunks,
+               "max_micro_batches": args.cap, "step_timeout": 600, "lm_head_chunks": args.lm_head_chunks, "reserve_memory_gb": args.reserve_gb,
                "inner_optimizer": {"type": "AdamW", "lr": 6e-4},
                "outer_optimizer": outer,
                "scheduler": {"enable": True, "num_warmup_steps": 100, "type": "cosine"}},
@@ -318,7 +320,8 @@ def run_ours(args) -> dict:
                    "layers_per_stage": tr.config.swarm.layer_split if S > 1 else str(tr.config.model.n_layer),
                    "engine": args.engine,
                    "collective": args.collective, "p2p": type(tr.comm).__name__,
-                   "routing": args.routing, **({"timeline_steps": args.timeline_steps} if args.timeline_steps else {}),
+                   "routing": args.routing, "allocator_pool_gb": args.reserve_gb, "lm_head_chunks": args.lm_head_chunks,
+                   **({"timeline_steps": args.timeline_steps} if args.timeline_steps else {}),
                    "l2": "per-step working set (GBs) exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,

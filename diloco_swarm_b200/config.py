@@ -146,6 +146,10 @@ class TrainConfig(BaseConfig):
     # microbatch's token rows, one after the other, so that only a slice of the [tokens, vocabulary] logits
     # exists at a time (GPT-2 small, 16 x 1024 tokens: 1.65 GB for one slice, 0.41 GB for four); b200 engine
     lm_head_chunks: int = 1
+    # (added) GB of device memory taken from the driver in one piece when the trainer starts and handed to the
+    # caching allocator: later tensors are cut from it, so steps whose set of live tensors differs from every
+    # step before (other routing, another batch layout) do not stop for cudaMalloc; 0 = off
+    reserve_memory_gb: float = 0.0
     inner_optimizer: OptimizerConfig
     outer_optimizer: OptimizerConfig
     scheduler: SchedulerConfig = SchedulerConfig()

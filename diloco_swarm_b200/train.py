@@ -103,6 +103,10 @@ class Trainer:
         self._resolve_layer_split()
         self.engine = make_engine(config, w, self.device)
         self.comm = self._make_comm()
+        if self.device.type == "cuda" and tc.reserve_memory_gb > 0:
+            # one large block, freed at once: it stays with the caching allocator, which cuts later tensors from it
+            pool = torch.empty(int(tc.reserve_memory_gb * 2 ** 30), dtype=torch.uint8, device=self.device)
+            del pool
         if hasattr(self.engine, "warmup"):
             self.engine.warmup(self.mbs, self.seq)
         self.comm.warmup()
