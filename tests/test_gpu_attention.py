@@ -19,7 +19,10 @@ def _ref(qkv, B, T, nh):
     return o.transpose(1, 2).reshape(B * T, d), lse
 
 
-SHAPES = [(1, 128, 1, 64), (2, 256, 3, 64), (1, 1024, 2, 64), (1, 128, 1, 32), (2, 384, 4, 32), (1, 1024, 3, 32)]
+# The last three give every persistent CTA several work items (more items than SMs), which is where the
+# double-buffered K / V, the hand-over between items and the staged dK / dV stores are exercised.
+SHAPES = [(1, 128, 1, 64), (2, 256, 3, 64), (1, 1024, 2, 64), (1, 128, 1, 32), (2, 384, 4, 32), (1, 1024, 3, 32),
+          (4, 1024, 12, 64), (16, 256, 12, 64), (6, 512, 12, 32)]
 
 
 @pytest.mark.parametrize("B,T,nh,hs", SHAPES)
