@@ -81,6 +81,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// (or until the phase completes) instead of returning at once, so a waiting role issues fewer instructions.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory; once any role sets it,
 // every later wait of the CTA returns false at once so the CTA can unwind.
 constexpr long long WAIT_CYCLES_LIMIT = 4000000000LL;   // about 2 s
@@ -91,7 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_for(bar, parity, 2000)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > WAIT_CYCLES_LIMIT) {
