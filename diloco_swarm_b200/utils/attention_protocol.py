@@ -167,3 +167,117 @@ def run_attention_bwd(items: List[int], rng: random.Random, drop: Optional[str] 
     sim.add_role("rows", rows())
     sim.add_role("reducer", reducer())
     return sim.run()
+
+
+FWD_MUTATIONS = ("rows_wait_o_full", "mma_wait_s_free", "producer_wait_kv_empty", "producer_wait_q_empty",
+                 "rows_end_wait_o_full")
+# Implied by p_full of the next item's first tile, at which the softmax rows arrive only after they have read
+# the previous item's output rows.
+FWD_IMPLIED = ("mma_wait_o_free",)
+
+
+def run_attention_fwd(items: List[int], rng: random.Random, drop: Optional[str] = None) -> float:
+    """``attention_fwd_kernel`` (csrc/attention.cu): one CTA walks ``items`` (kv tiles per query tile).
+
+      producer  Q of item w (waits q_empty of the item before), then one (K, V) pair per kv tile into stage
+                g & 1 (waits kv_empty)
+      mma       S of tile g+1 as soon as the rows have read S of tile g (s_free), also the next item's first
+                (waits its q_full); q_empty is committed with an item's last S; on p_full: P V into the output
+                rows (waits o_free of the item before on an item's first tile), commit o_full and kv_empty
+      rows      wait s_full, read S, arrive s_free, row maximum; from the item's second tile on wait o_full of
+                the tile before (its product reads P and accumulates onto the rows that a rescale would touch),
+                write P, arrive p_full; after an item: wait o_full of the last tile, read the output rows,
+                arrive o_free
+    """
+    assert drop is None or drop in FWD_MUTATIONS + FWD_IMPLIED
+    sim = Sim()
+    B: Dict[str, Barrier] = {n: Barrier(n, 1) for n in (
+        "q_full", "q_empty", "kv_full0", "kv_full1", "kv_empty0", "kv_empty1", "s_full", "s_free", "p_full", "o_full",
+        "o_free")}
+
+    def lat(lo: float, hi: float) -> float:
+        return rng.uniform(lo, hi)
+
+    t_mma = lat(15, 70)
+    t_issue = lat(30, 60)
+    n_items = len(items)
+
+    def producer():
+        g = 0
+        for w, n_kv in enumerate(items):
+            if w > 0 and drop != "producer_wait_q_empty":
+                yield ("wait", B["q_empty"], (w - 1) & 1)
+            yield ("copy", [], [("Q", w)], lat(300, 2500), B["q_full"], None)
+            for _ in range(n_kv):
+                s = g & 1
+                if drop != "producer_wait_kv_empty":
+                    yield ("wait", B[f"kv_empty{s}"], ((g >> 1) & 1) ^ 1)
+                yield ("copy", [], [(f"KV{s}", g)], lat(300, 2500), B[f"kv_full{s}"], None)
+                g += 1
+
+    def issue_s(gt: int, wi: int, first: bool, last: bool):
+        if first:
+            yield ("wait", B["q_full"], wi & 1)
+        yield ("wait", B[f"kv_full{gt & 1}"], (gt >> 1) & 1)
+        yield ("mma", [("Q", wi), (f"KV{gt & 1}", gt)], [("S", gt)], 4 * t_mma)
+        yield ("commit", B["s_full"])
+        if last:
+            yield ("commit", B["q_empty"])
+        yield ("delay", 4 * t_issue)
+
+    def mma():
+        g = 0
+        for w, n_kv in enumerate(items):
+            nxt = items[w + 1] if w + 1 < n_items else 0
+            if g == 0:
+                yield from issue_s(0, 0, True, n_kv == 1)
+            for j in range(n_kv):
+                s = g & 1
+                more = j + 1 < n_kv
+                if more or nxt > 0:
+                    if drop != "mma_wait_s_free":
+                        yield ("wait", B["s_free"], g & 1)
+                    if more:
+                        yield from issue_s(g + 1, w, False, j + 2 == n_kv)
+                    else:
+                        yield from issue_s(g + 1, w + 1, True, nxt == 1)
+                yield ("wait", B["p_full"], g & 1)
+                if j == 0 and w > 0 and drop != "mma_wait_o_free":
+                    yield ("wait", B["o_free"], (w - 1) & 1)
+                yield ("mma", [("P", g), (f"KV{s}", g)], [("O", g)], 8 * t_mma)
+                yield ("commit", B["o_full"])
+                yield ("commit", B[f"kv_empty{s}"])
+                yield ("delay", 8 * t_issue)
+                g += 1
+
+    def rows():
+        g = 0
+        for w, n_kv in enumerate(items):
+            for j in range(n_kv):
+                yield ("wait", B["s_full"], g & 1)
+                yield ("read", ("S", g))
+                yield ("delay", lat(100, 400))
+                yield ("arrive", B["s_free"])
+                yield ("delay", lat(100, 500))              # row maximum
+                if j > 0:
+                    if drop != "rows_wait_o_full":
+                        yield ("wait", B["o_full"], (g - 1) & 1)
+                    if rng.random() < 0.3:                    # the running maximum grew: rescale the output rows
+                        yield ("read", ("O", g - 1))
+                        yield ("write", ("O", g - 1))
+                        yield ("delay", lat(100, 400))
+                yield ("write", ("P", g))
+                yield ("delay", lat(400, 1500))
+                yield ("arrive", B["p_full"])
+                g += 1
+            if drop != "rows_end_wait_o_full":
+                yield ("wait", B["o_full"], (g - 1) & 1)
+            yield ("read", ("O", g - 1))
+            yield ("delay", lat(50, 300))
+            yield ("arrive", B["o_free"])
+            yield ("delay", lat(100, 800))                    # normalise and store the rows
+
+    sim.add_role("producer", producer())
+    sim.add_role("mma", mma())
+    sim.add_role("rows", rows())
+    return sim.run()
