@@ -612,6 +612,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_
           const int qrow = b * T + (j + it) * ATT_BQ;
           att_load_tile(smem + L::Q_OFF + s * ATT_TILE_BYTES, &tmap_qkv, &q_full[s], hs, h, qrow);
           att_load_tile(smem + L::DO_OFF + s * ATT_TILE_BYTES, &tmap_do, &q_full[s], hs, h, qrow);
+          // The pair two steps on is asked into L2 now: its load can only start when its stage is released, and
+          // the time from there to the data is on the issuing thread's path.
+          if (hs == 64 && it + 2 < steps) {
+            tma_prefetch_l2_2d(&tmap_qkv, h * 64, qrow + 2 * ATT_BQ);
+            tma_prefetch_l2_2d(&tmap_do, h * 64, qrow + 2 * ATT_BQ);
+          }
         }
         ++w;
       }
