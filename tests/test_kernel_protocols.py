@@ -114,3 +114,15 @@ def test_gemm_a_missing_wait_is_noticed(drop):
         except (Hazard, Deadlock):
             seen += 1
     assert seen > 0, f"leaving out {drop} went unnoticed in 200 random runs"
+
+
+def test_step_time_model_of_the_attention_backward():
+    """benchmarks/attention_bwd_model: with the measured latencies the model gives the step time seen on the
+    GPU (2.4-2.6 us), and shorter reloads or cheaper MMA issue shorten it while faster row algebra hardly does."""
+    from diloco_swarm_b200.benchmarks.attention_bwd_model import MEASURED, step_time
+    items = [8, 5, 5, 2, 2, 7, 7, 4, 4, 1, 1]
+    base = step_time(items, dict(MEASURED))
+    assert 2300 < base < 2800
+    assert step_time(items, {**MEASURED, "tma": 600.0}) < 0.93 * base
+    assert step_time(items, {**MEASURED, "t_issue": 26.0, "t_mma": 30.0}) < 0.9 * base
+    assert step_time(items, {**MEASURED, "compute": 600.0}) > 0.95 * base
