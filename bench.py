@@ -42,7 +42,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 TOPOLOGY = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
-# The unmodified reference (gloo + host staging) on this pool's B200s, same config, tokens/s as measured by an
+# The unmodified reference (gloo + host staging) on the same kind of B200 box, same config, tokens/s as measured by an
 # earlier driver run of `bench.py --impl reference`; the reference publishes no throughput (so vs_baseline is null).
 REFERENCE_TOKENS_PER_S = {1: 483165.0, 2: 136634.0, 4: 200694.0, 8: 300112.0}
 SMI_QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"

@@ -5,8 +5,8 @@ The kernels of ``csrc/attention.cu`` and ``csrc/gemm_kernels.cuh`` are sets of s
 producer, an MMA issuer, row or epilogue warps, a reducer) that hand buffers to one another through
 mbarriers.  A wrong parity, a missing wait or a barrier that nobody arrives at does not show as a wrong
 number on the GPU; it shows as a wait that runs out, or as a race that the next timing change uncovers.
-This module replays such a protocol on the CPU with randomised latencies and checks two things that no
-tool on the pool checks: every role runs to its end (no deadlock), and no buffer is written while an
+This module replays such a protocol on the CPU with randomised latencies and checks two things that a
+run on the GPU does not: every role runs to its end (no deadlock), and no buffer is written while an
 earlier reader or writer of it is still outstanding (no hazard).  The reference has no counterpart (it
 ships no kernels).
 
